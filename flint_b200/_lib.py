@@ -1,0 +1,94 @@
+"""ctypes binding of libflintb200.so (the C ABI declared in include/flint_b200.h).
+
+There is no fallback: if the shared library is missing or a symbol cannot be resolved, import of the
+product path fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libflintb200.so")
+
+FB_OK, FB_ERR_ARG, FB_ERR_SHAPE, FB_ERR_CUDA, FB_ERR_STATE, FB_ERR_TIMEOUT, FB_ERR_RANGE = range(7)
+ERR_NAMES = {0: "FB_OK", 1: "FB_ERR_ARG", 2: "FB_ERR_SHAPE", 3: "FB_ERR_CUDA", 4: "FB_ERR_STATE",
+             5: "FB_ERR_TIMEOUT", 6: "FB_ERR_RANGE"}
+
+
+class FlintError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"{what}: {ERR_NAMES.get(code, code)}")
+        self.code = code
+
+
+class Caps(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("device", "sm_count", "cc_major", "cc_minor", "smem_per_block_optin",
+                                              "l2_bytes", "cooperative_launch", "regs_decode_kernel")] + \
+               [("total_mem_bytes", ctypes.c_int64)]
+
+
+class ModelDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("n_layer", "dim", "n_head", "n_kv_head", "head_dim", "ffn", "vocab",
+                                              "has_zeros")] + \
+               [(n, ctypes.c_float) for n in ("rms_eps", "rope_base", "attn_scale", "resid_mult", "emb_mult",
+                                              "logits_scaling")]
+
+
+WEIGHT_FIELDS = ("qkv_q", "qkv_s", "qkv_z", "o_q", "o_s", "o_z", "gu_q", "gu_s", "gu_z", "d_q", "d_s", "d_z",
+                 "lm_q", "lm_s", "lm_z", "n1", "n2", "nf", "embed")
+
+
+class WeightPtrs(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in WEIGHT_FIELDS]
+
+
+class Status(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("code", "cuda_error", "where", "layer", "block", "expected", "seen")]
+
+
+# every symbol include/flint_b200.h declares, with its prototype
+_PROTOS = {
+    "fb_query": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Caps)]),
+    "fb_ctx_create": (ctypes.c_int, [ctypes.POINTER(ModelDesc), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]),
+    "fb_ctx_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "fb_last_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Status)]),
+    "fb_bind_weights": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(WeightPtrs), ctypes.c_void_p]),
+    "fb_bind_kv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]),
+    "fb_decode": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32,
+                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_stream_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
+    "fb_repack": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
+                                 ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_dequant": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                  ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_gemv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                               ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                               ctypes.c_void_p]),
+    "fb_set_option": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64]),
+}
+EXPORTED_SYMBOLS = tuple(_PROTOS)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library and bind every prototype; raises if the CUDA extension has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m flint_b200.csrc.build` "
+                          "(nvcc, sm_100a); there is no CPU fallback")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _PROTOS.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str):
+    if code != FB_OK:
+        raise FlintError(code, what)

@@ -1,0 +1,366 @@
+// extern "C" boundary of libflintb200.so: context management, weight re-layout and the launches.
+// No torch types, no CPU fallback: a failed CUDA call or an unsupported shape is an error code.
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "../../include/flint_b200.h"
+#include "fb_decode.cuh"
+
+using namespace fb;
+
+struct fb_ctx {
+  fb_model_desc d;
+  int device, sm_count, kernel_id, rgqa;
+  uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
+  const void *n1, *n2, *nf, *embed;
+  float* invf;
+  uint16_t *h, *qbuf, *ao, *act;
+  float *pm, *pd, *pacc, *cand_val;
+  int* cand_idx;
+  unsigned* bar_ctr;
+  DevStatus* status;
+  void *kc, *vc;
+  int max_seq, maxchunks;
+  unsigned bar_base, spin_limit;
+  bool weights_bound;
+  int last_cuda_error;
+  int force_chunks;
+  long long* prof;
+};
+
+namespace {
+
+typedef void (*decode_fn_t)(const DecodeParams);
+
+struct KernelEntry {
+  int dim, ffn, head_dim, rgqa, hz;
+  const void* fn;
+};
+
+#define FB_DECODE_ENTRY(KD, KF, HD, R)                                                      \
+  {KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>},                 \
+  {KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>}
+
+const KernelEntry kDecodeKernels[] = {
+    FB_DECODE_ENTRY(K512, K1408, 64, 4),      // tiny test decoder
+    FB_DECODE_ENTRY(K2560, K8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
+    FB_DECODE_ENTRY(K2560, K8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
+    FB_DECODE_ENTRY(K4096, K14336, 128, 4),   // 8B-class
+};
+constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
+
+int find_kernel(const fb_model_desc& d) {
+  if (d.n_kv_head <= 0 || d.n_head % d.n_kv_head) return -1;
+  for (int i = 0; i < kNumDecodeKernels; i++) {
+    const KernelEntry& e = kDecodeKernels[i];
+    if (e.dim == d.dim && e.ffn == d.ffn && e.head_dim == d.head_dim && e.rgqa == d.n_head / d.n_kv_head &&
+        e.hz == (d.has_zeros ? 1 : 0))
+      return i;
+  }
+  return -1;
+}
+
+int cuda_fail(fb_ctx* c, cudaError_t e) {
+  if (c) c->last_cuda_error = (int)e;
+  return FB_ERR_CUDA;
+}
+
+#define FB_CUDA(c, call)                                   \
+  do {                                                     \
+    cudaError_t e__ = (call);                              \
+    if (e__ != cudaSuccess) return cuda_fail((c), e__);    \
+  } while (0)
+
+template <class T>
+cudaError_t dmalloc(T** p, size_t n) { return cudaMalloc(reinterpret_cast<void**>(p), n); }
+
+struct DeviceGuard {
+  int prev;
+  bool ok;
+  explicit DeviceGuard(int dev) : prev(0), ok(false) {
+    if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+  }
+  ~DeviceGuard() { if (ok) cudaSetDevice(prev); }
+};
+
+int chunks_for(const fb_ctx* c, int T) {
+  if (c->force_chunks > 0) return c->force_chunks < c->maxchunks ? c->force_chunks : c->maxchunks;
+  if (T <= 512) return 1;
+  int n = (T + 255) / 256;
+  return n < c->maxchunks ? n : c->maxchunks;
+}
+
+template <class KC>
+int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
+  cudaError_t e;
+  if (hz) {
+    e = cudaFuncSetAttribute(gemv_stream<KC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    gemv_stream<KC, true><<<grid, kThreads, kSmemBytes, st>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(gemv_stream<KC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    gemv_stream<KC, false><<<grid, kThreads, kSmemBytes, st>>>(p);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int fb_query(int device, fb_caps* out) {
+  if (!out) return FB_ERR_ARG;
+  cudaDeviceProp p;
+  if (cudaGetDeviceProperties(&p, device) != cudaSuccess) return FB_ERR_CUDA;
+  memset(out, 0, sizeof(*out));
+  out->device = device;
+  out->sm_count = p.multiProcessorCount;
+  out->cc_major = p.major;
+  out->cc_minor = p.minor;
+  out->smem_per_block_optin = (int32_t)p.sharedMemPerBlockOptin;
+  out->l2_bytes = p.l2CacheSize;
+  out->cooperative_launch = p.cooperativeLaunch;
+  out->total_mem_bytes = (int64_t)p.totalGlobalMem;
+  cudaFuncAttributes fa;
+  if (cudaFuncGetAttributes(&fa, kDecodeKernels[2].fn) == cudaSuccess) out->regs_decode_kernel = fa.numRegs;
+  return FB_OK;
+}
+
+int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
+  if (!desc || !out) return FB_ERR_ARG;
+  *out = nullptr;
+  const fb_model_desc& d = *desc;
+  if (d.n_layer <= 0 || d.vocab <= 0 || d.dim % 128 || d.ffn % 128 || d.n_head * d.head_dim != d.dim) return FB_ERR_SHAPE;
+  const int kid = find_kernel(d);
+  if (kid < 0) return FB_ERR_SHAPE;
+  DeviceGuard g(device);
+  if (!g.ok) return FB_ERR_CUDA;
+  cudaDeviceProp p;
+  if (cudaGetDeviceProperties(&p, device) != cudaSuccess) return FB_ERR_CUDA;
+  if (p.major < 10 || !p.cooperativeLaunch || (int)p.sharedMemPerBlockOptin < kSmemBytes) return FB_ERR_SHAPE;
+  fb_ctx* c = new (std::nothrow) fb_ctx();
+  if (!c) return FB_ERR_ARG;
+  memset(c, 0, sizeof(*c));
+  c->d = d;
+  c->device = device;
+  c->sm_count = p.multiProcessorCount;
+  c->kernel_id = kid;
+  c->rgqa = d.n_head / d.n_kv_head;
+  c->spin_limit = 4000000u;
+  c->maxchunks = c->sm_count / d.n_kv_head;
+  if (c->maxchunks < 1) c->maxchunks = 1;
+  if (c->maxchunks > 64) c->maxchunks = 64;
+  // result buffer of a CTA must hold its rows of the widest phase
+  {
+    const int G = c->sm_count;
+    const int ksD = d.dim == 4096 ? 2 : 1;
+    const long long lm_rows = ((long long)d.vocab + G - 1) / G + 1, gu_rows = (2LL * d.ffn + G - 1) / G + 2;
+    if (lm_rows * ksD > kResFloats || gu_rows * ksD > kResFloats) { delete c; return FB_ERR_SHAPE; }
+  }
+  const int QD = d.n_head * d.head_dim;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+  A(dmalloc(&c->invf, sizeof(float) * (d.head_dim / 2)));
+  A(dmalloc(&c->h, 2 * (size_t)d.dim));
+  A(dmalloc(&c->qbuf, 2 * (size_t)QD));
+  A(dmalloc(&c->ao, 2 * (size_t)QD));
+  A(dmalloc(&c->act, 2 * (size_t)d.ffn));
+  A(dmalloc(&c->pm, 4 * (size_t)d.n_head * c->maxchunks));
+  A(dmalloc(&c->pd, 4 * (size_t)d.n_head * c->maxchunks));
+  A(dmalloc(&c->pacc, 4 * (size_t)d.n_head * c->maxchunks * d.head_dim));
+  A(dmalloc(&c->cand_val, 4 * (size_t)c->sm_count));
+  A(dmalloc(&c->cand_idx, 4 * (size_t)c->sm_count));
+  A(dmalloc(&c->bar_ctr, 256));
+  A(dmalloc(&c->status, sizeof(DevStatus)));
+  if (e == cudaSuccess) {
+    float invf[128];
+    for (int i = 0; i < d.head_dim / 2; i++) invf[i] = (float)pow((double)d.rope_base, -2.0 * i / d.head_dim);
+    A(cudaMemcpy(c->invf, invf, sizeof(float) * (d.head_dim / 2), cudaMemcpyHostToDevice));
+    A(cudaMemset(c->bar_ctr, 0, 256));
+    A(cudaMemset(c->status, 0, sizeof(DevStatus)));
+    A(cudaFuncSetAttribute(kDecodeKernels[kid].fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  }
+  if (e != cudaSuccess) {
+    fb_ctx_destroy(c);
+    return FB_ERR_CUDA;
+  }
+  *out = c;
+  return FB_OK;
+}
+
+int fb_ctx_destroy(fb_ctx* c) {
+  if (!c) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
+                  c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  delete c;
+  return FB_OK;
+}
+
+int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
+  if (!c) return FB_ERR_ARG;
+  if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
+  if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
+  if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[16 * n_layer] phase stamps, 0 = off
+  return FB_ERR_ARG;
+}
+
+int fb_last_status(fb_ctx* c, fb_status* out) {
+  if (!c || !out) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  DevStatus s;
+  cudaError_t e = cudaMemcpy(&s, c->status, sizeof(s), cudaMemcpyDeviceToHost);
+  memset(out, 0, sizeof(*out));
+  out->cuda_error = c->last_cuda_error;
+  if (e != cudaSuccess) {
+    out->code = FB_ERR_CUDA;
+    out->cuda_error = (int)e;
+    return FB_ERR_CUDA;
+  }
+  out->code = s.code;
+  out->where = s.where;
+  out->layer = s.layer;
+  out->block = s.block;
+  out->expected = s.expected;
+  out->seen = s.seen;
+  if (s.code != 0) {   // a launch gave up: the barrier counter is at an arbitrary value, start over
+    cudaMemset(c->bar_ctr, 0, 256);
+    cudaMemset(c->status, 0, sizeof(DevStatus));
+    c->bar_base = 0;
+  }
+  return FB_OK;
+}
+
+size_t fb_stream_bytes(int32_t rows, int32_t k, int32_t has_zeros) {
+  if (rows < 0 || k <= 0 || k % 128) return 0;
+  return (size_t)rows * rec_bytes_of(k, has_zeros);
+}
+
+int fb_repack(const void* d_q, const void* d_s, const void* d_z, int32_t rows, int32_t k, int32_t order, int32_t order_arg,
+              int32_t order_rows, void* d_out, void* stream) {
+  if (!d_q || !d_s || !d_out || rows <= 0 || k <= 0 || k % 128 || order < 0 || order > 2) return FB_ERR_ARG;
+  if (order == 1 && (order_arg <= 0 || order_arg % 2 || order_rows % order_arg || order_rows > rows)) return FB_ERR_ARG;
+  if (order == 2 && (order_arg * 2 != rows)) return FB_ERR_ARG;
+  repack_rows<<<dim3(rows, 1), 128, 0, (cudaStream_t)stream>>>((const uint32_t*)d_q, (const uint16_t*)d_s,
+                                                             (const uint16_t*)d_z, rows, k, order, order_arg, order_rows,
+                                                             (uint8_t*)d_out);
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+}
+
+int fb_dequant(const void* d_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
+               int32_t order_rows, float* d_out, void* stream) {
+  if (!d_in || !d_out || rows <= 0 || k <= 0 || k % 128 || order < 0 || order > 2) return FB_ERR_ARG;
+  dequant_rows<<<rows, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)d_in, rows, k, has_zeros, order, order_arg,
+                                                      order_rows, d_out);
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+}
+
+int fb_gemv(const void* d_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
+            int32_t order_rows, const void* d_x, float* d_y, void* d_status, void* stream) {
+  if (!d_in || !d_x || !d_y || !d_status || rows <= 0) return FB_ERR_ARG;
+  if (((uintptr_t)d_in & 15) || ((uintptr_t)d_x & 15)) return FB_ERR_ARG;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return FB_ERR_CUDA;
+  GemvParams p{(const uint8_t*)d_in, (const uint16_t*)d_x, d_y, (DevStatus*)d_status, rows, order, order_arg, order_rows,
+               4000000u};
+  const bool hz = has_zeros != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  int e;
+  switch (k) {
+    case 512: e = launch_gemv_k<K512>(hz, p, sms, st); break;
+    case 1408: e = launch_gemv_k<K1408>(hz, p, sms, st); break;
+    case 2560: e = launch_gemv_k<K2560>(hz, p, sms, st); break;
+    case 4096: e = launch_gemv_k<K4096>(hz, p, sms, st); break;
+    case 8192: e = launch_gemv_k<K8192>(hz, p, sms, st); break;
+    case 14336: e = launch_gemv_k<K14336>(hz, p, sms, st); break;
+    default: return FB_ERR_SHAPE;
+  }
+  return e == 0 ? FB_OK : FB_ERR_CUDA;
+}
+
+int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
+  if (!c || !w) return FB_ERR_ARG;
+  const fb_model_desc& d = c->d;
+  const bool hz = d.has_zeros != 0;
+  const void* need[] = {w->qkv_q, w->qkv_s, w->o_q, w->o_s, w->gu_q, w->gu_s, w->d_q, w->d_s, w->lm_q, w->lm_s,
+                        w->n1, w->n2, w->nf};   /* embed may be NULL when every step supplies its own residual */
+  for (const void* p : need)
+    if (!p) return FB_ERR_ARG;
+  if (hz && (!w->qkv_z || !w->o_z || !w->gu_z || !w->d_z || !w->lm_z)) return FB_ERR_ARG;
+  if (((uintptr_t)w->n1 & 15) || ((uintptr_t)w->n2 & 15) || ((uintptr_t)w->nf & 15)) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int L = d.n_layer, D = d.dim, FF = d.ffn, HD = d.head_dim;
+  const int QKV = (d.n_head + 2 * d.n_kv_head) * HD, QD = d.n_head * HD;
+  struct M { uint8_t** dst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
+  M ms[] = {
+      {&c->w_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
+      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
+      {&c->w_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
+      {&c->w_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
+      {&c->w_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
+  };
+  for (M& m : ms) {
+    const size_t bytes = (size_t)m.layers * m.rows * rec_bytes_of(m.k, hz);
+    if (*m.dst) { cudaFree(*m.dst); *m.dst = nullptr; }
+    FB_CUDA(c, dmalloc(m.dst, bytes + 16));
+    repack_rows<<<dim3(m.rows, m.layers), 128, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s,
+                                                        hz ? (const uint16_t*)m.z : nullptr, m.rows, m.k, m.order, m.arg,
+                                                        m.orows, *m.dst);
+    FB_CUDA(c, cudaGetLastError());
+  }
+  c->n1 = w->n1; c->n2 = w->n2; c->nf = w->nf; c->embed = w->embed;
+  c->weights_bound = true;
+  return FB_OK;
+}
+
+int fb_bind_kv(fb_ctx* c, void* d_k, void* d_v, int32_t max_seq) {
+  if (!c || !d_k || !d_v || max_seq <= 0) return FB_ERR_ARG;
+  if (((uintptr_t)d_k & 15) || ((uintptr_t)d_v & 15)) return FB_ERR_ARG;
+  c->kc = d_k; c->vc = d_v; c->max_seq = max_seq;
+  return FB_OK;
+}
+
+int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32_t pos, float* d_logits, int32_t* d_next,
+              void* stream) {
+  if (!c) return FB_ERR_ARG;
+  if (!c->weights_bound || !c->kc) return FB_ERR_STATE;
+  const fb_model_desc& d = c->d;
+  if (pos < 0 || pos >= c->max_seq) return FB_ERR_RANGE;
+  if (!d_token && !d_h && (token < 0 || token >= d.vocab)) return FB_ERR_RANGE;
+  if (!d_h && !c->embed) return FB_ERR_STATE;
+  if (d_h && ((uintptr_t)d_h & 1)) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  DecodeParams P;
+  memset(&P, 0, sizeof(P));
+  P.w_qkv = c->w_qkv; P.w_o = c->w_o; P.w_gu = c->w_gu; P.w_d = c->w_d; P.w_lm = c->w_lm;
+  P.n1 = (const uint16_t*)c->n1; P.n2 = (const uint16_t*)c->n2; P.nf = (const uint16_t*)c->nf;
+  P.embed = (const uint16_t*)c->embed; P.invf = c->invf;
+  P.kc = (uint16_t*)c->kc; P.vc = (uint16_t*)c->vc;
+  P.h = c->h; P.qbuf = c->qbuf; P.ao = c->ao; P.act = c->act;
+  P.pm = c->pm; P.pd = c->pd; P.pacc = c->pacc; P.cand_val = c->cand_val; P.cand_idx = c->cand_idx;
+  P.bar_ctr = c->bar_ctr; P.status = c->status;
+  P.d_token = d_token; P.d_h = (uint16_t*)d_h; P.d_logits = d_logits; P.d_next = d_next;
+  P.token = token; P.pos = pos; P.max_seq = c->max_seq;
+  P.n_layer = d.n_layer; P.dim = d.dim; P.n_head = d.n_head; P.n_kv = d.n_kv_head; P.ffn = d.ffn; P.vocab = d.vocab;
+  P.nchunks = chunks_for(c, pos + 1);
+  P.bar_base = c->bar_base; P.spin_limit = c->spin_limit;
+  P.eps = d.rms_eps; P.attn_scale = d.attn_scale; P.resid = d.resid_mult; P.emb_mult = d.emb_mult;
+  P.logits_scaling = d.logits_scaling;
+  P.prof = c->prof;
+  const unsigned nbar = 1u + (unsigned)d.n_layer * (5u + (P.nchunks > 1 ? 1u : 0u)) + 1u;
+  void* args[] = {&P};
+  FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn, dim3(c->sm_count), dim3(kThreads), args,
+                                         (size_t)kSmemBytes, (cudaStream_t)stream));
+  c->bar_base += nbar * (unsigned)c->sm_count;
+  return FB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+"""Host side of the decode path: the context object and the reference-shaped launch functions.
+
+`decode_mega_launch(...)` takes the same positional arguments and returns the same tensor as the reference's
+pybind11 function (reference: kernels/megakernel_decode.cu:204-237), so the loops in chat.py / spec_mega.py
+(reference: chat.py:71-74, spec_mega.py:46-49) run unchanged; `DecodeEngine` is the explicit form that also
+does the embedding lookup and the argmax on the device. PyTorch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import _lib
+from .config import ModelArgs
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def query(device: int = 0) -> Dict[str, int]:
+    caps = _lib.Caps()
+    _lib.check(_lib.load().fb_query(device, ctypes.byref(caps)), "fb_query")
+    return {n: getattr(caps, n) for n, _ in caps._fields_}
+
+
+class DecodeEngine:
+    """One model bound to one GPU: streaming-layout weights, scratch, a KV cache and the megakernel launches."""
+
+    def __init__(self, cfg: ModelArgs, packed: Dict[str, torch.Tensor], max_seq: Optional[int] = None,
+                 device: Optional[torch.device] = None, kc: Optional[torch.Tensor] = None,
+                 vc: Optional[torch.Tensor] = None):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("flint_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.cfg = cfg
+        self.device = torch.device(device if device is not None else packed["qkv_q"].device)
+        if self.device.type != "cuda":
+            raise ValueError("packed weights must live on the GPU that runs the kernels")
+        self.dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.has_zeros = "qkv_z" in packed
+        self.max_seq = int(max_seq or cfg.block_size)
+        d = _lib.ModelDesc(cfg.n_layer, cfg.dim, cfg.n_head, cfg.n_local_heads, cfg.head_dim, cfg.ffn_padded,
+                           cfg.vocab_size, int(self.has_zeros), cfg.norm_eps, float(cfg.rope_base),
+                           float(cfg.attn_scale), float(cfg.residual_multiplier), float(cfg.embedding_multiplier),
+                           float(cfg.logits_scaling))
+        self._ctx = ctypes.c_void_p()
+        _lib.check(self.lib.fb_ctx_create(ctypes.byref(d), self.dev_index, ctypes.byref(self._ctx)), "fb_ctx_create")
+        # keep-alive: the norms and the embedding table stay caller-side tensors
+        self._keep = {k: packed[k].contiguous() for k in ("n1", "n2", "nf") if k in packed}
+        if "embed" in packed and packed["embed"] is not None:
+            self._keep["embed"] = packed["embed"].contiguous()
+        w = _lib.WeightPtrs()
+        for name in _lib.WEIGHT_FIELDS:
+            t = self._keep.get(name, packed.get(name))
+            if t is not None:
+                if t.device != self.device or not t.is_contiguous():
+                    raise ValueError(f"{name}: must be a contiguous tensor on {self.device}")
+                setattr(w, name, t.data_ptr())
+        _lib.check(self.lib.fb_bind_weights(self._ctx, ctypes.byref(w), _stream_ptr(self.device)), "fb_bind_weights")
+        torch.cuda.synchronize(self.device)
+        shape = (cfg.n_layer, self.max_seq, cfg.n_local_heads, cfg.head_dim)
+        self.kc = kc if kc is not None else torch.zeros(shape, dtype=torch.bfloat16, device=self.device)
+        self.vc = vc if vc is not None else torch.zeros(shape, dtype=torch.bfloat16, device=self.device)
+        self.bind_kv(self.kc, self.vc)
+        self._logits = torch.empty(cfg.vocab_size, dtype=torch.float32, device=self.device)
+        self._next = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ plumbing
+    def bind_kv(self, kc: torch.Tensor, vc: torch.Tensor):
+        want = (self.cfg.n_layer, kc.shape[1], self.cfg.n_local_heads, self.cfg.head_dim)
+        for t in (kc, vc):
+            if tuple(t.shape) != want or t.dtype != torch.bfloat16 or not t.is_contiguous() or t.device != self.device:
+                raise ValueError(f"KV cache must be contiguous bf16 {want} on {self.device}")
+        self.kc, self.vc, self.max_seq = kc, vc, kc.shape[1]
+        _lib.check(self.lib.fb_bind_kv(self._ctx, _ptr(kc), _ptr(vc), self.max_seq), "fb_bind_kv")
+
+    def set_option(self, what: int, value: int):
+        _lib.check(self.lib.fb_set_option(self._ctx, what, value), "fb_set_option")
+
+    def status(self) -> Dict[str, int]:
+        """Synchronises, then returns the device status of the launches so far (code 0 = clean)."""
+        torch.cuda.synchronize(self.device)
+        st = _lib.Status()
+        _lib.check(self.lib.fb_last_status(self._ctx, ctypes.byref(st)), "fb_last_status")
+        return {n: getattr(st, n) for n, _ in st._fields_}
+
+    def check(self):
+        st = self.status()
+        if st["code"] != 0:
+            raise _lib.FlintError(st["code"], f"device status {st}")
+
+    def close(self):
+        if getattr(self, "_ctx", None) is not None and self._ctx.value:
+            self.lib.fb_ctx_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ launches (asynchronous on the current stream)
+    def decode(self, token: int, pos: int, logits: Optional[torch.Tensor] = None,
+               next_token: Optional[torch.Tensor] = None, want_logits: bool = True) -> torch.Tensor:
+        """One step from a host token id. Returns the f32 [vocab] logits tensor (a reused buffer unless given)."""
+        lg = logits if logits is not None else (self._logits if want_logits else None)
+        nx = next_token if next_token is not None else self._next
+        _lib.check(self.lib.fb_decode(self._ctx, int(token), None, None, int(pos), _ptr(lg), _ptr(nx),
+                                      _stream_ptr(self.device)), "fb_decode")
+        return lg
+
+    def decode_chained(self, token_dev: torch.Tensor, pos: int, next_token: torch.Tensor,
+                       logits: Optional[torch.Tensor] = None):
+        """One step whose input token is read from device memory (the previous step's argmax): no host sync."""
+        _lib.check(self.lib.fb_decode(self._ctx, 0, _ptr(token_dev), None, int(pos), _ptr(logits), _ptr(next_token),
+                                      _stream_ptr(self.device)), "fb_decode")
+
+    def decode_h(self, h: torch.Tensor, pos: int, logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One step from an already multiplied embedding h bf16 [dim] (clobbered, as the reference does)."""
+        lg = logits if logits is not None else torch.empty(self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        _lib.check(self.lib.fb_decode(self._ctx, 0, None, _ptr(h), int(pos), _ptr(lg), _ptr(self._next),
+                                      _stream_ptr(self.device)), "fb_decode")
+        return lg
+
+    @property
+    def next_token(self) -> torch.Tensor:
+        return self._next
+
+
+# --------------------------------------------------------------------------------------------------
+# Reference-shaped launch function. The reference infers every dimension from tensor sizes
+# (reference: kernels/megakernel_decode.cu:210-211) and so does this wrapper; the context is cached on the
+# identity of the weight and cache tensors, so weights are re-laid out once, not per call.
+# --------------------------------------------------------------------------------------------------
+_engines: Dict[tuple, DecodeEngine] = {}
+
+
+def _engine_for(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h_dim, kc, vc,
+                scale, rope_base, resid, logits_scaling) -> DecodeEngine:
+    key = (Wqkv.data_ptr(), Wo.data_ptr(), Wgu.data_ptr(), Wd.data_ptr(), Wlm.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+           float(scale), float(rope_base), float(resid), float(logits_scaling))
+    eng = _engines.get(key)
+    if eng is not None:
+        return eng
+    n_layer, max_seq, n_kv, hd = kc.shape
+    dim = int(h_dim)
+    cfg = ModelArgs(block_size=max_seq, vocab_size=Wlm.shape[0], n_layer=n_layer, n_head=dim // hd, dim=dim,
+                    intermediate_size=Wd.shape[2] * 8, n_local_heads=n_kv, rope_base=rope_base,
+                    attention_multiplier=float(scale), residual_multiplier=float(resid),
+                    logits_scaling=float(logits_scaling))
+    packed = dict(qkv_q=Wqkv, qkv_s=s_qkv, o_q=Wo, o_s=s_o, n1=n1, gu_q=Wgu, gu_s=s_gu, d_q=Wd, d_s=s_d, n2=n2, nf=nf,
+                  lm_q=Wlm, lm_s=s_lm)
+    eng = DecodeEngine(cfg, packed, max_seq=max_seq, kc=kc, vc=vc)
+    _engines[key] = eng
+    return eng
+
+
+def decode_mega_launch(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h, kc, vc, pos,
+                       scale, rope_base, resid, logits_scaling) -> torch.Tensor:
+    """Drop-in for the reference's `decode_mega_launch`: same arguments, returns a new f32 [vocab] logits tensor;
+    `h` is clobbered and rows `pos` of kc/vc are written, as in the reference."""
+    eng = _engine_for(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h.shape[0], kc, vc,
+                      scale, rope_base, resid, logits_scaling)
+    return eng.decode_h(h, int(pos))
+
+
+def decode_occupancy():
+    """[registers/thread, blocks/SM, #SMs, warps/SM, total warps] (reference: kernels/megakernel_decode.cu:239-245)."""
+    c = query(torch.cuda.current_device())
+    return [c["regs_decode_kernel"], 1, c["sm_count"], 17, 17 * c["sm_count"]]

@@ -1,0 +1,127 @@
+/*
+ * flint_b200 -- C ABI of the B200 (sm_100a) batch-1 int4 decode engine.
+ *
+ * Plain pointers and sizes only: every `d_*` argument is a device pointer owned by the caller, `stream` is a
+ * cudaStream_t passed as void* (NULL = default stream). Every entry point returns an int status, 0 = FB_OK.
+ * Launches are asynchronous on `stream`; FB_ERR_TIMEOUT and friends are reported by fb_last_status() after the
+ * stream has been synchronised. Nothing here falls back to the CPU.
+ *
+ * Each declaration names the reference interface it replaces (paths inside the reference project).
+ */
+#ifndef FLINT_B200_H_
+#define FLINT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FB_OK = 0,
+  FB_ERR_ARG = 1,          /* NULL pointer, misaligned pointer, bad size */
+  FB_ERR_SHAPE = 2,        /* model shape this build has no kernel for */
+  FB_ERR_CUDA = 3,         /* a CUDA runtime call failed; fb_last_status() carries the cudaError_t */
+  FB_ERR_STATE = 4,        /* weights / KV cache not bound yet, or context poisoned by an earlier device error */
+  FB_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out (grid barrier, copy barrier, peer flag) */
+  FB_ERR_RANGE = 6         /* pos / M / token outside the bound cache or vocabulary */
+};
+
+/* Device facts the host side sizes things by. Replaces decode_occupancy()/verify_occupancy()
+ * (reference: kernels/megakernel_decode.cu:239-245, kernels/verify_mega.cu:285-293). */
+typedef struct fb_caps {
+  int32_t device, sm_count, cc_major, cc_minor;
+  int32_t smem_per_block_optin, l2_bytes, cooperative_launch, regs_decode_kernel;
+  int64_t total_mem_bytes;
+} fb_caps;
+int fb_query(int device, fb_caps* out);
+
+/* Model shape and scalar multipliers: the module globals of the reference front-end
+ * (reference: chat.py:19-21) and the trailing scalar arguments of decode_mega_launch
+ * (reference: kernels/megakernel_decode.cu:204-211). ffn must be a multiple of 128 (pad with zero weights). */
+typedef struct fb_model_desc {
+  int32_t n_layer, dim, n_head, n_kv_head, head_dim, ffn, vocab;
+  int32_t has_zeros;       /* 0: (nib-8)*s  (reference: chat.py:23-30); 1: (nib-8)*s+z (reference: engine/quantize.py:138-155) */
+  float rms_eps, rope_base, attn_scale, resid_mult, emb_mult, logits_scaling;
+} fb_model_desc;
+
+/* The 13 weight tensors of the reference boundary in the reference's own layout
+ * (reference: chat.py:32-52, kernels/megakernel_decode.cu:204-208): q int32 [L, OUT, IN/8],
+ * s (and z) bf16 [L, OUT, IN/128]; lm_* have no layer dimension; norms bf16; embed bf16 [vocab, dim].
+ * *_z may be NULL when has_zeros == 0. */
+typedef struct fb_weight_ptrs {
+  const void *qkv_q, *qkv_s, *qkv_z;
+  const void *o_q, *o_s, *o_z;
+  const void *gu_q, *gu_s, *gu_z;
+  const void *d_q, *d_s, *d_z;
+  const void *lm_q, *lm_s, *lm_z;
+  const void *n1, *n2, *nf;
+  const void *embed;
+} fb_weight_ptrs;
+
+typedef struct fb_ctx fb_ctx;
+
+typedef struct fb_status {
+  int32_t code;            /* FB_* */
+  int32_t cuda_error;      /* last cudaError_t seen by the host side, 0 if none */
+  int32_t where;           /* device side: phase id that gave up */
+  int32_t layer, block, expected, seen;
+} fb_status;
+
+/* Context: scratch, barrier words and status buffer on `device`. Replaces the per-call torch::empty scratch
+ * allocations and occupancy queries of the reference launcher (reference: kernels/megakernel_decode.cu:213-223). */
+int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out);
+int fb_ctx_destroy(fb_ctx* ctx);
+int fb_last_status(fb_ctx* ctx, fb_status* out);
+
+/* Re-lays the caller's int4 tensors out into the context's streaming layout (one pass on the GPU, once).
+ * The caller's tensors are not referenced afterwards, except n1/n2/nf/embed which must stay alive.
+ * Replaces load_packed's stacked tensors as kernel operands (reference: chat.py:32-52). */
+int fb_bind_weights(fb_ctx* ctx, const fb_weight_ptrs* w, void* stream);
+
+/* Caller-owned KV cache, bf16 [n_layer, max_seq, n_kv_head, head_dim], dimension 1 = position
+ * (reference: chat.py:68-69; the cache is indexed by position from Python in spec_tree.py:126-128). */
+int fb_bind_kv(fb_ctx* ctx, void* d_k, void* d_v, int32_t max_seq);
+
+/* One decode step in one cooperative launch: embedding (or a caller-supplied residual), all layers, final norm,
+ * LM head, argmax. Replaces decode_mega_launch (reference: kernels/megakernel_decode.cu:204-237) plus the
+ * host-side embedding lookup and argmax around it (reference: chat.py:71-77).
+ *   token     : used when d_token == NULL and d_h == NULL
+ *   d_token   : device int32, read by the kernel (lets step t+1 consume step t's d_next without a host sync)
+ *   d_h       : bf16 [dim], the already multiplied embedding, as the reference boundary takes it; it receives the
+ *               final residual stream (the reference clobbers its h argument too); NULL to use the token
+ *   d_logits  : f32 [vocab] or NULL
+ *   d_next    : int32 argmax (first index of the maximum) or NULL */
+int fb_decode(fb_ctx* ctx, int32_t token, const int32_t* d_token, void* d_h, int32_t pos, float* d_logits,
+              int32_t* d_next, void* stream);
+
+/* Stand-alone slices of the same path, on the streaming layout (unit-test granularity; they replace the
+ * reference's GEMV family, reference: kernels/int4_gemv.cu:384-424).
+ *   fb_stream_bytes : bytes of the streaming layout for one [rows, k] matrix
+ *   fb_repack       : caller layout -> streaming layout (order: 0 plain, 1 RoPE pair interleave with head_dim,
+ *                     2 gate/up interleave)
+ *   fb_dequant      : streaming layout -> f32 [rows, k] in ORIGINAL row order: (nib-8)*s+z, bit for bit
+ *   fb_gemv         : y f32 [rows] (original row order) = W x, x bf16 [k]; d_status is a zeroed 32-byte device
+ *                     buffer (int32[8]) whose first word becomes FB_ERR_TIMEOUT if a bounded wait ran out */
+size_t fb_stream_bytes(int32_t rows, int32_t k, int32_t has_zeros);
+int fb_repack(const void* d_q, const void* d_s, const void* d_z, int32_t rows, int32_t k, int32_t order,
+              int32_t order_arg, int32_t order_rows, void* d_stream_out, void* stream);
+int fb_dequant(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
+               int32_t order_rows, float* d_out, void* stream);
+int fb_gemv(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
+            int32_t order_rows, const void* d_x, float* d_y, void* d_status, void* stream);
+
+/* Tuning / test knobs (no reference counterpart: the reference has no bounded waits and a fixed split).
+ *   what 0: iteration limit of every device-side wait (default 4000000); a tiny value makes a launch give up
+ *           with FB_ERR_TIMEOUT, which is how the time-out path is tested without hanging a GPU
+ *   what 1: force the number of attention chunks per kv head (0 = choose from the cached length)
+ *   what 2: value = device pointer to int64[16 * n_layer] (0 = off): SM-clock stamps of CTA 0 at the phase
+ *           boundaries of every layer, the run-time replacement of the reference's -DNOSYNC/-DNOATTN diagnostic
+ *           builds (reference: kernels/megakernel_decode.cu:15-24) */
+int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLINT_B200_H_ */

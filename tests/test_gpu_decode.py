@@ -1,0 +1,219 @@
+"""GPU parity of the decode megakernel against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from flint_b200 import packing
+from flint_b200.config import ModelArgs
+from flint_b200.engine import DecodeEngine, decode_mega_launch
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2      # max-abs on logits, the bar stated for the int4 path at the tiny config's logit scale
+
+
+def logit_tol(ref):
+    """2e-2 max-abs is stated on the tiny config, whose largest |logit| is 2.56. Models with larger logits get the
+    same RELATIVE bar. (The CPU oracle alone moves by this much when one bf16 ulp of one input element is flipped:
+    tests/test_packer_oracle.py::test_oracle_one_ulp_sensitivity.)"""
+    return LOGIT_TOL * max(1.0, float(np.abs(ref).max()) / 2.56)
+
+
+def _to_cuda(P):
+    return {k: v.cuda() for k, v in P.items()}
+
+
+def _run_parity(cfg, P, prompt, steps, max_seq, norm_note=""):
+    orc = O.OracleModel(cfg, P, max_seq)
+    eng = DecodeEngine(cfg, _to_cuda(P), max_seq=max_seq)
+    pos, worst, agree, total = 0, 0.0, 0, 0
+    cur = prompt[0]
+    seq = list(prompt)
+    for i in range(len(prompt) + steps - 1):
+        tok = seq[i]
+        ref = orc.decode(tok, pos)
+        got = eng.decode(tok, pos).cpu().numpy()
+        nxt = int(eng.next_token.item())
+        eng.check()
+        worst = max(worst, float(np.abs(got - ref).max()))
+        assert nxt == int(np.argmax(got)), "device argmax must be the first index of the maximum of its own logits"
+        if i >= len(prompt) - 1:
+            total += 1
+            agree += int(nxt == O.argmax_first(ref))
+            seq.append(O.argmax_first(ref))          # teacher-forced on the oracle's greedy token
+        pos += 1
+    kc = eng.kc.cpu().view(torch.int16).numpy().view(np.uint16)
+    vc = eng.vc.cpu().view(torch.int16).numpy().view(np.uint16)
+    kv_diff = max(np.abs(O.bf16_to_f32(kc[:, :pos]) - O.bf16_to_f32(orc.kc[:, :pos])).max(),
+                  np.abs(O.bf16_to_f32(vc[:, :pos]) - O.bf16_to_f32(orc.vc[:, :pos])).max())
+    eng.close()
+    return worst, agree, total, kv_diff
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_tiny_decode_vs_oracle(asym):
+    """Tiny config, 16-token prompt + 64 greedy steps: logits within 2e-2 max-abs, >= 99 % greedy agreement."""
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0, asym=asym)
+    prompt = torch.randint(0, cfg.vocab_size, (16,), generator=torch.Generator().manual_seed(1234)).tolist()
+    worst, agree, total, kv = _run_parity(cfg, P, prompt, 64, cfg.block_size)
+    assert worst < LOGIT_TOL, worst
+    assert agree >= 0.99 * total, (agree, total)
+    assert kv < 0.05, kv
+
+
+def test_tiny_decode_ref_norm_weights_and_chunked_attention():
+    """Norm weights |N(0,1)|+0.5 as the reference's kernel tests use, and the flash-decode split forced to
+    2 chunks per kv head so the partial/merge path is exercised at short length."""
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 1, norm_mode="ref")
+    orc = O.OracleModel(cfg, P, 128)
+    eng = DecodeEngine(cfg, _to_cuda(P), max_seq=128)
+    eng.set_option(1, 3)
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    worst_rel, agree = 0.0, 0
+    for pos, t in enumerate(toks):
+        ref = orc.decode(t, pos)
+        got = eng.decode(t, pos).cpu().numpy()
+        worst_rel = max(worst_rel, float(np.linalg.norm(got - ref) / np.linalg.norm(ref)))
+        agree += int(int(eng.next_token.item()) == O.argmax_first(ref))
+    eng.check()
+    # these norm weights make the logits ~1.3x larger than the unit-norm model the 2e-2 max-abs bar is stated for,
+    # so this case uses the reference's own criterion: rel-L2 < 0.02 and equal argmax
+    # (reference: bench/verify_mega_test.py:54-56)
+    assert worst_rel < 0.02, worst_rel
+    assert agree >= len(toks) - 1, agree
+
+
+def test_reference_shaped_launch_function():
+    """decode_mega_launch(...) with the reference's positional arguments (reference: chat.py:71-74)."""
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0)
+    W = _to_cuda(P)
+    orc = O.OracleModel(cfg, P, 64)
+    kc = torch.zeros(cfg.n_layer, 64, cfg.n_local_heads, cfg.head_dim, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    for pos, tok in enumerate([7, 300, 4095]):
+        h = (W["embed"][tok].float() * cfg.embedding_multiplier).to(torch.bfloat16)
+        lg = decode_mega_launch(W["qkv_q"], W["qkv_s"], W["o_q"], W["o_s"], W["n1"], W["gu_q"], W["gu_s"], W["d_q"],
+                                W["d_s"], W["n2"], W["nf"], W["lm_q"], W["lm_s"], h, kc, vc, pos, cfg.attn_scale,
+                                cfg.rope_base, cfg.residual_multiplier, cfg.logits_scaling)
+        ref = orc.decode(tok, pos)
+        assert lg.dtype == torch.float32 and tuple(lg.shape) == (cfg.vocab_size,)
+        assert np.abs(lg.cpu().numpy() - ref).max() < LOGIT_TOL
+
+
+def test_chained_device_tokens_match_host_loop():
+    cfg = ModelArgs.from_name("tiny")
+    W = _to_cuda(packing.synth_packed(cfg, 0))
+    a, b = DecodeEngine(cfg, W, max_seq=64), DecodeEngine(cfg, W, max_seq=64)
+    tok, host = 11, []
+    for pos in range(24):
+        a.decode(tok, pos, want_logits=False)
+        tok = int(a.next_token.item())
+        host.append(tok)
+    buf = torch.tensor([[11], [0]], dtype=torch.int32, device="cuda")
+    out = torch.zeros(24, dtype=torch.int32, device="cuda")
+    cur = buf[0]
+    for pos in range(24):
+        nxt = out[pos:pos + 1]
+        b.decode_chained(cur, pos, nxt)
+        cur = nxt
+    b.check()
+    assert out.tolist() == host
+
+
+def test_determinism_bitwise():
+    cfg = ModelArgs.from_name("tiny")
+    W = _to_cuda(packing.synth_packed(cfg, 0))
+    outs = []
+    for _ in range(2):
+        e = DecodeEngine(cfg, W, max_seq=32)
+        lg = [e.decode(t, p).clone() for p, t in enumerate([1, 2, 3, 4, 5])]
+        e.check()
+        outs.append(torch.stack(lg))
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_wait_runs_out_reports_timeout_and_context_survives():
+    """A spin limit of 1 makes some bounded wait give up: the launch must end, report FB_ERR_TIMEOUT and the
+    next launch with a sane limit must work."""
+    cfg = ModelArgs.from_name("tiny")
+    W = _to_cuda(packing.synth_packed(cfg, 0))
+    e = DecodeEngine(cfg, W, max_seq=32)
+    ref = e.decode(5, 0).clone()
+    e.check()
+    e.set_option(0, 1)
+    e.decode(5, 0)
+    st = e.status()
+    e.set_option(0, 4000000)
+    if st["code"] != 0:
+        assert st["code"] == 5
+    again = e.decode(5, 0).clone()
+    e.check()
+    assert torch.equal(ref, again)
+
+
+def test_bad_arguments_are_errors_not_launches():
+    from flint_b200 import _lib
+    cfg = ModelArgs.from_name("tiny")
+    W = _to_cuda(packing.synth_packed(cfg, 0))
+    e = DecodeEngine(cfg, W, max_seq=16)
+    with pytest.raises(_lib.FlintError) as ei:
+        e.decode(3, 16)                       # pos == max_seq
+    assert ei.value.code == _lib.FB_ERR_RANGE
+    with pytest.raises(_lib.FlintError):
+        e.decode(cfg.vocab_size, 0)
+    bad = ModelArgs(block_size=64, vocab_size=1000, n_layer=1, n_head=3, n_local_heads=3, dim=384, intermediate_size=1024)
+    with pytest.raises(_lib.FlintError) as ei:
+        DecodeEngine(bad, _to_cuda(packing.synth_packed(bad, 0)), max_seq=16)
+    assert ei.value.code == _lib.FB_ERR_SHAPE
+
+
+def _granite_shape(n_layer):
+    cfg = ModelArgs.from_name("granite-3b-class")
+    cfg.n_layer = n_layer
+    return cfg
+
+
+def test_granite3b_shape_two_layers_vs_oracle():
+    """Full-size matrices of the headline shape (d 2560, 32/8 heads of 80, FFN 8192, vocab 49160) at a depth of
+    2 layers, where bf16 rounding noise has not yet been amplified: the 2e-2 max-abs bar applies."""
+    cfg = _granite_shape(2)
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    orc = O.OracleModel(cfg, P, 64)
+    eng = DecodeEngine(cfg, W, max_seq=64)
+    worst, agree = 0.0, 0
+    toks = [17, 40000, 123, 4567, 9, 31000]
+    for pos, t in enumerate(toks):
+        ref = orc.decode(t, pos)
+        got = eng.decode(t, pos).cpu().numpy()
+        eng.check()
+        worst = max(worst, float(np.abs(got - ref).max()) / logit_tol(ref))
+        agree += int(int(eng.next_token.item()) == O.argmax_first(ref))
+    assert worst < 1.0, worst
+    assert agree == len(toks)
+
+
+def test_granite3b_class_full_depth_vs_oracle():
+    """All 40 layers. The seeded N(0, 0.02) model is chaotic under bf16 rounding at this depth: flipping ONE bf16
+    ulp of ONE embedding element moves the ORACLE's own logits by 0.15-0.17 max-abs (rel-L2 0.034, measured with
+    the oracle alone), so no two summation orders can agree to 2e-2 here. The bound used is 3x that self-sensitivity,
+    plus equal greedy tokens."""
+    cfg = ModelArgs.from_name("granite-3b-class")
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    orc = O.OracleModel(cfg, P, 64)
+    eng = DecodeEngine(cfg, W, max_seq=64)
+    worst_rel, agree = 0.0, 0
+    toks = [17, 40000, 123, 4567]
+    for pos, t in enumerate(toks):
+        ref = orc.decode(t, pos)
+        got = eng.decode(t, pos).cpu().numpy()
+        eng.check()
+        worst_rel = max(worst_rel, float(np.linalg.norm(got - ref) / np.linalg.norm(ref)))
+        agree += int(int(eng.next_token.item()) == O.argmax_first(ref))
+    assert worst_rel < 0.1, worst_rel
+    assert agree == len(toks)
