@@ -9,7 +9,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libflintb200.so")
+LIB_PATH = os.environ.get("FLINT_B200_LIB", os.path.join(HERE, "libflintb200.so"))
 
 FB_OK, FB_ERR_ARG, FB_ERR_SHAPE, FB_ERR_CUDA, FB_ERR_STATE, FB_ERR_TIMEOUT, FB_ERR_RANGE = range(7)
 ERR_NAMES = {0: "FB_OK", 1: "FB_ERR_ARG", 2: "FB_ERR_SHAPE", 3: "FB_ERR_CUDA", 4: "FB_ERR_STATE",

@@ -7,7 +7,7 @@
 #include <new>
 
 #include "../../include/flint_b200.h"
-#include "fb_decode.cuh"
+#include "fb_decode2.cuh"
 
 using namespace fb;
 
@@ -29,6 +29,12 @@ struct fb_ctx {
   int last_cuda_error;
   int force_chunks;
   long long* prof;
+  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll;   // tagged vectors of the data-flow kernel
+  unsigned* cnt;
+  uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
+  unsigned tag_base;
+  int max_fly;
+  int version;                                                      // 2: data-flow kernel (default), 1: grid-barrier kernel
 };
 
 namespace {
@@ -37,12 +43,15 @@ typedef void (*decode_fn_t)(const DecodeParams);
 
 struct KernelEntry {
   int dim, ffn, head_dim, rgqa, hz;
-  const void* fn;
+  const void* fn;     // grid-barrier kernel
+  const void* fn2;    // data-flow kernel
 };
 
 #define FB_DECODE_ENTRY(KD, KF, HD, R)                                                      \
-  {KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>},                 \
-  {KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>}
+  {KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>,                  \
+   (const void*)decode_mega2<KD, KF, HD, R, false>},                                         \
+  {KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>,                   \
+   (const void*)decode_mega2<KD, KF, HD, R, true>}
 
 const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(K512, K1408, 64, 4),      // tiny test decoder
@@ -88,8 +97,14 @@ struct DeviceGuard {
 
 int chunks_for(const fb_ctx* c, int T) {
   if (c->force_chunks > 0) return c->force_chunks < c->maxchunks ? c->force_chunks : c->maxchunks;
-  if (T <= 512) return 1;
-  int n = (T + 255) / 256;
+  if (c->version == 1) {
+    if (T <= 512) return 1;
+    const int n1 = (T + 255) / 256;
+    return n1 < c->maxchunks ? n1 : c->maxchunks;
+  }
+  // data-flow kernel: spread every kv head over as many CTAs as there are (one sweep of 16 warps covers 32 positions)
+  int n = (T + 15) / 16;
+  if (n < 1) n = 1;
   return n < c->maxchunks ? n : c->maxchunks;
 }
 
@@ -151,6 +166,9 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   c->kernel_id = kid;
   c->rgqa = d.n_head / d.n_kv_head;
   c->spin_limit = 4000000u;
+  c->version = 2;
+  c->max_fly = 4;
+  c->tag_base = 8;
   c->maxchunks = c->sm_count / d.n_kv_head;
   if (c->maxchunks < 1) c->maxchunks = 1;
   if (c->maxchunks > 64) c->maxchunks = 64;
@@ -176,6 +194,20 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   A(dmalloc(&c->cand_idx, 4 * (size_t)c->sm_count));
   A(dmalloc(&c->bar_ctr, 256));
   A(dmalloc(&c->status, sizeof(DevStatus)));
+  const size_t hp = d.head_dim / 2;
+  const size_t ll_words[7] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
+                              (size_t)d.ffn / 2, 2 * (size_t)c->sm_count};
+  uint64_t** ll_ptrs[7] = {&c->h_ll, &c->q_ll, &c->k_ll, &c->v_ll, &c->ao_ll, &c->act_ll, &c->cand_ll};
+  for (int i = 0; i < 7; i++) {
+    A(dmalloc(ll_ptrs[i], 8 * ll_words[i] + 16));
+    if (e == cudaSuccess) A(cudaMemset(*ll_ptrs[i], 0, 8 * ll_words[i] + 16));
+  }
+  A(dmalloc(&c->cnt, 256));
+  if (e == cudaSuccess) A(cudaMemset(c->cnt, 0, 256));
+  A(dmalloc(&c->flags, 3 * 256 * 4));
+  if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
+  if (c->sm_count > 256) e = cudaErrorInvalidValue;
+  if ((d.dim / 2 + c->sm_count - 1) / c->sm_count * 2 + 2 > kMaxOwnRows || (2 * d.ffn) % 4) e = cudaErrorInvalidValue;
   if (e == cudaSuccess) {
     float invf[128];
     for (int i = 0; i < d.head_dim / 2; i++) invf[i] = (float)pow((double)d.rope_base, -2.0 * i / d.head_dim);
@@ -183,6 +215,7 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
     A(cudaMemset(c->bar_ctr, 0, 256));
     A(cudaMemset(c->status, 0, sizeof(DevStatus)));
     A(cudaFuncSetAttribute(kDecodeKernels[kid].fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    A(cudaFuncSetAttribute(kDecodeKernels[kid].fn2, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   }
   if (e != cudaSuccess) {
     fb_ctx_destroy(c);
@@ -196,7 +229,8 @@ int fb_ctx_destroy(fb_ctx* c) {
   if (!c) return FB_ERR_ARG;
   DeviceGuard g(c->device);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
-                  c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status};
+                  c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll,
+                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -207,7 +241,9 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (!c) return FB_ERR_ARG;
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
-  if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[16 * n_layer] phase stamps, 0 = off
+  if (what == 4) { if (value < 1 || value > kStages) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
+  if (what == 3) { if (value != 1 && value != 2) return FB_ERR_ARG; c->version = (int)value; return FB_OK; }
+  if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
 }
 
@@ -232,6 +268,7 @@ int fb_last_status(fb_ctx* c, fb_status* out) {
   if (s.code != 0) {   // a launch gave up: the barrier counter is at an arbitrary value, start over
     cudaMemset(c->bar_ctr, 0, 256);
     cudaMemset(c->status, 0, sizeof(DevStatus));
+    cudaMemset(c->cnt, 0, 256);
     c->bar_base = 0;
   }
   return FB_OK;
@@ -338,6 +375,31 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   if (!d_h && !c->embed) return FB_ERR_STATE;
   if (d_h && ((uintptr_t)d_h & 1)) return FB_ERR_ARG;
   DeviceGuard g(c->device);
+  if (c->version == 2) {
+    Decode2Params Q;
+    memset(&Q, 0, sizeof(Q));
+    Q.w_qkv = c->w_qkv; Q.w_o = c->w_o; Q.w_gu = c->w_gu; Q.w_d = c->w_d; Q.w_lm = c->w_lm;
+    Q.n1 = (const uint16_t*)c->n1; Q.n2 = (const uint16_t*)c->n2; Q.nf = (const uint16_t*)c->nf;
+    Q.embed = (const uint16_t*)c->embed; Q.invf = c->invf;
+    Q.kc = (uint16_t*)c->kc; Q.vc = (uint16_t*)c->vc;
+    Q.h_ll = c->h_ll; Q.q_ll = c->q_ll; Q.k_ll = c->k_ll; Q.v_ll = c->v_ll; Q.ao_ll = c->ao_ll; Q.act_ll = c->act_ll;
+    Q.h_flags = c->flags; Q.act_flags = c->flags + 256; Q.ao_flags = c->flags + 512;
+    Q.cand_ll = c->cand_ll; Q.pm = c->pm; Q.pd = c->pd; Q.pacc = c->pacc; Q.cnt = c->cnt; Q.status = c->status;
+    Q.d_token = d_token; Q.d_h = (uint16_t*)d_h; Q.d_logits = d_logits; Q.d_next = d_next;
+    Q.token = token; Q.pos = pos; Q.max_seq = c->max_seq;
+    Q.n_layer = d.n_layer; Q.dim = d.dim; Q.n_head = d.n_head; Q.n_kv = d.n_kv_head; Q.ffn = d.ffn; Q.vocab = d.vocab;
+    Q.nchunks = chunks_for(c, pos + 1);
+    const unsigned span = (unsigned)(d.n_layer + 1) * 8u;
+    if (c->tag_base > 0xffffffffu - 2 * span) c->tag_base = 8;      // tags never reach 0 (the value of fresh buffers)
+    Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
+    Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
+    Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly;
+    void* args2[] = {&Q};
+    FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn2, dim3(c->sm_count), dim3(kThreads), args2,
+                                           (size_t)kSmemBytes, (cudaStream_t)stream));
+    c->tag_base += span;
+    return FB_OK;
+  }
   DecodeParams P;
   memset(&P, 0, sizeof(P));
   P.w_qkv = c->w_qkv; P.w_o = c->w_o; P.w_gu = c->w_gu; P.w_d = c->w_d; P.w_lm = c->w_lm;
@@ -355,6 +417,7 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   P.eps = d.rms_eps; P.attn_scale = d.attn_scale; P.resid = d.resid_mult; P.emb_mult = d.emb_mult;
   P.logits_scaling = d.logits_scaling;
   P.prof = c->prof;
+  P.max_fly = (unsigned)c->max_fly;
   const unsigned nbar = 1u + (unsigned)d.n_layer * (5u + (P.nchunks > 1 ? 1u : 0u)) + 1u;
   void* args[] = {&P};
   FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn, dim3(c->sm_count), dim3(kThreads), args,

@@ -9,9 +9,16 @@
 namespace fb {
 
 // ------------------------------------------------------------------------------------------------ constants
-constexpr int kConsumerWarps = 16;                 // 4 groups of 4 warps; group g consumes weight tiles t with t % 4 == g
-constexpr int kGroups = 4;
+#ifndef FB_CW
+#define FB_CW 16
+#endif
+#ifndef FB_DOT
+#define FB_DOT 0      // 0: bf16 pairs + fma.rn.f32.bf16 (activations packed bf16 in registers)
+#endif                // 1: prmt -> fp32 weights + fma.rn.f32 (activations fp32 in registers)
+constexpr int kConsumerWarps = FB_CW;              // groups of 4 warps; group g consumes weight tiles t with t % kGroups == g
 constexpr int kWarpsPerGroup = 4;
+constexpr int kGroups = kConsumerWarps / kWarpsPerGroup;
+static_assert(kConsumerWarps % kWarpsPerGroup == 0, "consumer warps come in groups of 4");
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;    // + one producer warp (lane 0 issues the bulk copies)
 constexpr int kStages = 8;                         // ring depth: 8 x 22 KB = 176 KB of weights in flight per SM
@@ -19,7 +26,9 @@ constexpr int kStageBytes = 23040;              // largest tile: 3 rows of K=143
 constexpr int kScratchBytes = 40960;               // x staging (<= 14336 bf16) + per-phase results; attention merge area
 constexpr int kXBytes = 28672;
 constexpr int kResFloats = (kScratchBytes - kXBytes) / 4;   // 3072 row results per CTA per phase
-constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + 1024;
+constexpr int kTailBytes = 2048;                   // mbarriers, flags, reduction scratch, slice partials, owned residual rows
+constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + kTailBytes;
+constexpr int kMaxOwnRows = 64;                    // rows of the residual stream one CTA may own
 
 // named barriers (0 is __syncthreads)
 constexpr int kBarConsumers = 1;                   // all 512 consumer threads
@@ -43,6 +52,11 @@ __device__ __forceinline__ float bfhi(uint32_t p) { return __uint_as_float(p & 0
 __device__ __forceinline__ uint16_t f2bf(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
 __device__ __forceinline__ float rbf(float f) { return bf2f(f2bf(f)); }   // round an fp32 value to bf16 precision
 
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -186,12 +200,29 @@ using K1408 = KCfg<1408, 1, 2, 3, 4, 28>;
 using K2560 = KCfg<2560, 1, 2, 5, 4, 16>;
 using K4096 = KCfg<4096, 2, 4, 2, 4, 8>;
 using K8192 = KCfg<8192, 4, 4, 2, 4, 4>;
-using K14336 = KCfg<14336, 4, 4, 4, 3, 3>;
+using K14336 = KCfg<14336, 4, 4, 4, 2, 2>;   // even blocks: epilogues pair rows (2i, 2i+1)
+// Same K, finer work units for phases that give a CTA only ~20 rows (QKV, O, down): blocks of 2 rows and small
+// tiles keep all consumer warps busy and shorten the tail that the next phase has to wait for.
+using K512S = KCfg<512, 1, 2, 1, 2, 16>;
+using K1408S = KCfg<1408, 1, 2, 3, 2, 8>;
+using K2560S = KCfg<2560, 1, 2, 5, 2, 8>;
+using K4096S = KCfg<4096, 2, 4, 2, 2, 4>;
+using K8192S = KCfg<8192, 4, 4, 2, 2, 2>;
+template <class KC> struct SmallOf { using type = KC; };
+template <> struct SmallOf<K512> { using type = K512S; };
+template <> struct SmallOf<K1408> { using type = K1408S; };
+template <> struct SmallOf<K2560> { using type = K2560S; };
+template <> struct SmallOf<K4096> { using type = K4096S; };
+template <> struct SmallOf<K8192> { using type = K8192S; };
 
-// activations of one lane: packed bf16 pairs for its units + the fp32 sum of every unit (for the offset trick below)
+// activations of one lane for its units + the fp32 sum of every unit (for the offset trick below)
 template <class KC>
 struct XRegs {
-  uint32_t p[KC::NI][KC::U * 4];
+#if FB_DOT == 0
+  uint32_t p[KC::NI][KC::U * 4];     // packed bf16 pairs
+#else
+  float p[KC::NI][KC::U * 8];        // fp32
+#endif
   float sum[KC::NI];
 };
 
@@ -207,7 +238,12 @@ __device__ __forceinline__ void load_x_slice(const uint16_t* x_s, int slice, int
 #pragma unroll
     for (int w = 0; w < KC::U; w++) {
       uint4 v = ok ? src[w] : make_uint4(0, 0, 0, 0);
+#if FB_DOT == 0
       x.p[i][4 * w + 0] = v.x; x.p[i][4 * w + 1] = v.y; x.p[i][4 * w + 2] = v.z; x.p[i][4 * w + 3] = v.w;
+#else
+      x.p[i][8 * w + 0] = bflo(v.x); x.p[i][8 * w + 1] = bfhi(v.x); x.p[i][8 * w + 2] = bflo(v.y); x.p[i][8 * w + 3] = bfhi(v.y);
+      x.p[i][8 * w + 4] = bflo(v.z); x.p[i][8 * w + 5] = bfhi(v.z); x.p[i][8 * w + 6] = bflo(v.w); x.p[i][8 * w + 7] = bfhi(v.w);
+#endif
       s += bflo(v.x); s += bfhi(v.x); s += bflo(v.y); s += bfhi(v.y);
       s += bflo(v.z); s += bfhi(v.z); s += bflo(v.w); s += bfhi(v.w);
     }
@@ -215,13 +251,18 @@ __device__ __forceinline__ void load_x_slice(const uint16_t* x_s, int slice, int
   }
 }
 
-// One packed word (8 nibbles) against 8 activations: acc += sum_k (128 + nib_k) * x_k, exact products, fp32 adds.
-// (w >> 4j) & 0x000F000F | 0x43004300 is the bf16 pair (128 + nib_j, 128 + nib_{j+4}); fma.rn.f32.bf16 multiplies two
-// bf16 scalars into an fp32 accumulator in one instruction. The caller removes the offset: sum_k (nib_k - 8) x_k =
-// acc - 136 * sum_k x_k.
+#if FB_DOT == 0
+// One packed word (8 nibbles) against 8 activations: acc += sum_k (1 + nib_k/16) * x_k, exact products, fp32 adds.
+// ((w >> (4j-3)) & 0x00780078) | 0x3F803F80 is the bf16 pair (1 + nib_j/16, 1 + nib_{j+4}/16): the nibble sits in the
+// top four mantissa bits. fma.rn.f32.bf16 multiplies two bf16 scalars into an fp32 accumulator in one instruction.
+// The caller removes the offset: sum_k (nib_k - 8) x_k = 16 * (acc - 1.5 * sum_k x_k). (Putting the nibble in the LOW
+// mantissa bits saves one shift but makes the offset 136 instead of 1.5, and the cancellation then costs ~7 bits of
+// the fp32 sum: enough to flip bf16 roundings downstream.)
+constexpr float kDotOffset = 1.5f;
+constexpr float kDotScale = 16.f;
 __device__ __forceinline__ void dot_word(uint32_t w, const uint32_t* x, float& a0, float& a1) {
-  const uint32_t M = 0x000F000Fu, C = 0x43004300u;
-  const uint32_t t0 = (w & M) | C, t1 = ((w >> 4) & M) | C, t2 = ((w >> 8) & M) | C, t3 = ((w >> 12) & M) | C;
+  const uint32_t M = 0x00780078u, C = 0x3F803F80u;
+  const uint32_t t0 = ((w << 3) & M) | C, t1 = ((w >> 1) & M) | C, t2 = ((w >> 5) & M) | C, t3 = ((w >> 9) & M) | C;
   asm("{ .reg .b16 tl, th, xl, xh, yl, yh;\n"
       "mov.b32 {tl,th}, %2; mov.b32 {xl,xh}, %6; mov.b32 {yl,yh}, %8;\n"
       "fma.rn.f32.bf16 %0, tl, xl, %0; fma.rn.f32.bf16 %1, th, yl, %1;\n"
@@ -234,12 +275,36 @@ __device__ __forceinline__ void dot_word(uint32_t w, const uint32_t* x, float& a
       : "+f"(a0), "+f"(a1)
       : "r"(t0), "r"(t1), "r"(t2), "r"(t3), "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]));
 }
+constexpr int kXPerWord = 4;
+#else
+// One packed word against 8 fp32 activations. Byte b of ((w << 3) & 0x78787878) | 0x80808080 is 0x80 | nib_{2b} << 3;
+// one PRMT drops it under 0x3F into bits 16..23 of a float: 0x3F800000 | nib << 19 = 1 + nib/16 exactly. So
+// acc += sum_k (1 + nib_k/16) x_k and the caller uses sum_k (nib_k - 8) x_k = 16 * (acc - 1.5 * sum_k x_k).
+constexpr float kDotOffset = 1.5f;
+constexpr float kDotScale = 16.f;
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ void dot_word(uint32_t w, const float* x, float& a0, float& a1) {
+  const uint32_t e = ((w << 3) & 0x78787878u) | 0x80808080u, o = ((w >> 1) & 0x78787878u) | 0x80808080u;
+#pragma unroll
+  for (int b = 0; b < 4; b++) {
+    const float fe = __uint_as_float(prmt(e, 0x3F000000u, 0x7044u | (b << 8)));
+    const float fo = __uint_as_float(prmt(o, 0x3F000000u, 0x7044u | (b << 8)));
+    a0 = fmaf(fe, x[2 * b], a0);
+    a1 = fmaf(fo, x[2 * b + 1], a1);
+  }
+}
+constexpr int kXPerWord = 8;
+#endif
 
 // RB rows of one tile against the lane's activations: acc[r] += sum over the lane's units of s*(dot) [+ z*sum x].
 // `rows` are byte offsets of the RB records inside the tile (clamped by the caller for ragged tails).
-template <class KC, bool HZ>
+template <class KC, bool HZ, class XR>
 __device__ __forceinline__ void rowblock_dot(const uint8_t* tile, const int (&rows)[KC::RB], int slice, int lane,
-                                             const XRegs<KC>& x, float (&acc)[KC::RB]) {
+                                             const XR& x, float (&acc)[KC::RB]) {
   constexpr int K = KC::K;
 #pragma unroll
   for (int i = 0; i < KC::NI; i++) {
@@ -247,6 +312,7 @@ __device__ __forceinline__ void rowblock_dot(const uint8_t* tile, const int (&ro
     const bool ok = !KC::PRED || unit < KC::UNITS;
     const int word = slice * KC::SLICE_WORDS + (ok ? unit : 0) * KC::U;
     const int g = word >> 4;
+    const float off = kDotOffset * x.sum[i];
 #pragma unroll
     for (int r = 0; r < KC::RB; r++) {
       const uint8_t* rec = tile + rows[r];
@@ -254,16 +320,16 @@ __device__ __forceinline__ void rowblock_dot(const uint8_t* tile, const int (&ro
       if (KC::U == 2) {
         const uint2 w = *reinterpret_cast<const uint2*>(rec + 4 * word);
         dot_word(w.x, &x.p[i][0], p0, p1);
-        dot_word(w.y, &x.p[i][4], p0, p1);
+        dot_word(w.y, &x.p[i][kXPerWord], p0, p1);
       } else {
         const uint4 w = *reinterpret_cast<const uint4*>(rec + 4 * word);
         dot_word(w.x, &x.p[i][0], p0, p1);
-        dot_word(w.y, &x.p[i][4], p0, p1);
-        dot_word(w.z, &x.p[i][8], p0, p1);
-        dot_word(w.w, &x.p[i][12], p0, p1);
+        dot_word(w.y, &x.p[i][kXPerWord], p0, p1);
+        dot_word(w.z, &x.p[i][2 * kXPerWord], p0, p1);
+        dot_word(w.w, &x.p[i][3 * kXPerWord], p0, p1);
       }
-      const float s = bf2f(*reinterpret_cast<const uint16_t*>(rec + K / 2 + 2 * g));
-      const float t = fmaf(-136.f, x.sum[i], p0 + p1);
+      const float s = bf2f(*reinterpret_cast<const uint16_t*>(rec + K / 2 + 2 * g)) * kDotScale;
+      const float t = (p0 + p1) - off;
       acc[r] = fmaf(s, t, acc[r]);
       if (HZ) {
         const float z = bf2f(*reinterpret_cast<const uint16_t*>(rec + K / 2 + K / 64 + 2 * g));

@@ -12,7 +12,8 @@ struct Pipe {
   uint8_t* stages;
   uint64_t* full;
   uint64_t* empty;
-  uint32_t it;     // running tile counter; producer and consumers walk the same sequence
+  uint32_t it;       // running tile counter; producer and consumers walk the same sequence
+  uint32_t max_fly;  // producer only: bulk copies allowed in flight at once (<= kStages)
 };
 
 struct Smem {
@@ -25,6 +26,8 @@ struct Smem {
   volatile int* s_abort;
   float* red;          // 32 floats for block reductions
   int* misc;           // 32 ints
+  float* part;         // [groups][2][4 warps][4] slice partials of sliced-K phases
+  float* hown;         // [kMaxOwnRows] this CTA's rows of the residual stream
 };
 
 __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
@@ -38,7 +41,9 @@ __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
   s.empty = s.full + kStages;
   s.s_abort = reinterpret_cast<volatile int*>(tail + 128);
   s.red = reinterpret_cast<float*>(tail + 256);
-  s.misc = reinterpret_cast<int*>(tail + 512);
+  s.misc = reinterpret_cast<int*>(tail + 384);
+  s.part = reinterpret_cast<float*>(tail + 512);
+  s.hown = reinterpret_cast<float*>(tail + 1024);
   return s;
 }
 
@@ -58,6 +63,12 @@ __device__ __forceinline__ bool produce_rows(Pipe& p, const uint8_t* src, int nr
     const int s = p.it % kStages;
     const uint32_t ph = (p.it / kStages) & 1;
     if (!mbar_wait(&p.empty[s], ph ^ 1, wc, W_EMPTY, layer)) return false;   // p.it counts issued tiles only
+    // Keep the memory system's queues short: with the whole ring in flight (27 MB over 148 SMs) every small
+    // latency-critical access of the consumers (flags, tagged words) waits microseconds behind bulk weight traffic.
+    if (p.it >= p.max_fly) {
+      const uint32_t j = p.it - p.max_fly;
+      if (!mbar_wait(&p.full[j % kStages], (j / kStages) & 1, wc, W_FULL, layer)) return false;
+    }
     mbar_expect_tx(&p.full[s], bytes);
     bulk_g2s(p.stages + (size_t)s * kStageBytes, src + (size_t)r * rec, bytes, &p.full[s]);
     p.it++;
@@ -93,7 +104,7 @@ __device__ __forceinline__ void consume_rows(Pipe& p, int nrows, const XRegs<KC>
   const int ntiles = (nrows + TR - 1) / TR;
   for (int t = 0; t < ntiles; t++) {
     const uint32_t it = p.it + t;
-    if ((int)(it & 3) != grp) continue;
+    if ((int)(it % kGroups) != grp) continue;
     const int s = it % kStages;
     const uint32_t ph = (it / kStages) & 1;
     const bool ok = mbar_wait(&p.full[s], ph, wc, W_FULL, layer);
@@ -137,20 +148,27 @@ __device__ __forceinline__ void stage_x_plain(const uint16_t* gx, int K, uint16_
   named_bar_sync(kBarConsumers, kConsumerThreads);
 }
 
-// xn = bf16( (float(h) * r) * float(w) ), r = 1/sqrt(mean(h^2) + eps); one 8-value chunk per thread (dim <= 4096)
+// xn = bf16( (float(h) * r) * float(w) ), r = 1/sqrt(mean(h^2) + eps); up to 2 eight-value chunks per thread
 __device__ __forceinline__ void stage_x_norm(const uint16_t* gh, const uint16_t* gw, int D, float eps, uint16_t* x_s,
                                              float* red, int tid_c) {
   const int n16 = D / 8;
-  const bool has = tid_c < n16;
-  uint4 hv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
-  if (has) {
-    hv = ld_cg_v4(reinterpret_cast<const uint4*>(gh) + tid_c);
-    wv = __ldg(reinterpret_cast<const uint4*>(gw) + tid_c);
-  }
-  float hf[8] = {bflo(hv.x), bfhi(hv.x), bflo(hv.y), bfhi(hv.y), bflo(hv.z), bfhi(hv.z), bflo(hv.w), bfhi(hv.w)};
+  uint4 hv[2], wv[2];
   float ss = 0.f;
 #pragma unroll
-  for (int e = 0; e < 8; e++) ss = fmaf(hf[e], hf[e], ss);
+  for (int c = 0; c < 2; c++) {
+    const int j = tid_c + c * kConsumerThreads;
+    hv[c] = make_uint4(0, 0, 0, 0); wv[c] = make_uint4(0, 0, 0, 0);
+    if (j < n16) {
+      hv[c] = ld_cg_v4(reinterpret_cast<const uint4*>(gh) + j);
+      wv[c] = __ldg(reinterpret_cast<const uint4*>(gw) + j);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 2; c++) {
+    const float hf[8] = {bflo(hv[c].x), bfhi(hv[c].x), bflo(hv[c].y), bfhi(hv[c].y), bflo(hv[c].z), bfhi(hv[c].z), bflo(hv[c].w), bfhi(hv[c].w)};
+#pragma unroll
+    for (int e = 0; e < 8; e++) ss = fmaf(hf[e], hf[e], ss);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((tid_c & 31) == 0) red[tid_c >> 5] = ss;
@@ -159,15 +177,20 @@ __device__ __forceinline__ void stage_x_norm(const uint16_t* gh, const uint16_t*
 #pragma unroll
   for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
   const float r = 1.0f / sqrtf(tot / (float)D + eps);
-  if (has) {
-    const float wf[8] = {bflo(wv.x), bfhi(wv.x), bflo(wv.y), bfhi(wv.y), bflo(wv.z), bfhi(wv.z), bflo(wv.w), bfhi(wv.w)};
-    uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-      const uint32_t lo = f2bf(hf[2 * e] * r * wf[2 * e]), hi = f2bf(hf[2 * e + 1] * r * wf[2 * e + 1]);
-      o[e] = lo | (hi << 16);
+  for (int c = 0; c < 2; c++) {
+    const int j = tid_c + c * kConsumerThreads;
+    if (j < n16) {
+      const float hf[8] = {bflo(hv[c].x), bfhi(hv[c].x), bflo(hv[c].y), bfhi(hv[c].y), bflo(hv[c].z), bfhi(hv[c].z), bflo(hv[c].w), bfhi(hv[c].w)};
+      const float wf[8] = {bflo(wv[c].x), bfhi(wv[c].x), bflo(wv[c].y), bfhi(wv[c].y), bflo(wv[c].z), bfhi(wv[c].z), bflo(wv[c].w), bfhi(wv[c].w)};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t lo = f2bf(hf[2 * e] * r * wf[2 * e]), hi = f2bf(hf[2 * e + 1] * r * wf[2 * e + 1]);
+        o[e] = lo | (hi << 16);
+      }
+      reinterpret_cast<uint4*>(x_s)[j] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    reinterpret_cast<uint4*>(x_s)[tid_c] = make_uint4(o[0], o[1], o[2], o[3]);
   }
   named_bar_sync(kBarConsumers, kConsumerThreads);
 }
@@ -372,7 +395,8 @@ struct DecodeParams {
   int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks;
   unsigned bar_base, spin_limit;
   float eps, attn_scale, resid, emb_mult, logits_scaling;
-  long long* prof;                                      // optional: clock64 stamps of CTA 0, 16 per layer
+  long long* prof;                                      // optional phase stamps
+  unsigned max_fly;
 };
 
 template <class KD, class KF, int HD, int R, bool HZ>
@@ -388,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega(const DecodeParams P)
   }
   __syncthreads();
   WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
-  Pipe pipe{sm.stages, sm.full, sm.empty, 0u};
+  Pipe pipe{sm.stages, sm.full, sm.empty, 0u, P.max_fly};
 
   const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
   const int QKV = (P.n_head + 2 * P.n_kv) * HD;
@@ -433,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega(const DecodeParams P)
     grid_barrier(gb, wc, tid_c, -1);
 
     XRegs<KD> xd;
-#define FB_STAMP(i) do { if (P.prof && b == 0 && tid_c == 0) P.prof[l * 16 + (i)] = clock64(); } while (0)
+#define FB_STAMP(i) do { if (P.prof && tid_c == 0) P.prof[((size_t)b * L + l) * 16 + (i)] = (long long)globaltimer_ns(); } while (0)
     for (int l = 0; l < L; l++) {
       uint16_t* kcl = P.kc + (size_t)l * P.max_seq * P.n_kv * HD;
       uint16_t* vcl = P.vc + (size_t)l * P.max_seq * P.n_kv * HD;
@@ -598,7 +622,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream(const GemvParams P) {
   }
   __syncthreads();
   WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
-  Pipe pipe{sm.stages, sm.full, sm.empty, 0u};
+  Pipe pipe{sm.stages, sm.full, sm.empty, 0u, (uint32_t)kStages};
   const int rec = rec_bytes_of(KC::K, HZ);
   int r0, r1;
   cta_rows(P.rows, 1, blockIdx.x, gridDim.x, r0, r1);

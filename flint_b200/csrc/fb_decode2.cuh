@@ -1,0 +1,730 @@
+// Decode megakernel, data-flow synchronisation.
+//
+// Phases of one token are chained by DATA, not by grid barriers: every vector that crosses CTAs (residual h, q / new
+// k / new v, attention output, SwiGLU activations, arg-max candidates) lives in global memory as 8-byte words that
+// carry their payload (two bf16 values or one fp32/int32) together with a 32-bit tag unique to (launch, layer,
+// phase). A producer stores the word once; a consumer polls the word itself until the tag matches, so the value
+// arrives with the same L2 round trip that a barrier would only have announced. Each hop costs about one L2 round
+// trip instead of three (barrier arrive, barrier poll, data fetch).
+//
+// Why single buffers are enough: every phase consumes a vector that ALL CTAs contributed to, so a CTA can only be
+// one full phase ahead of the slowest one; a buffer is rewritten two phases after its last reader at the earliest.
+#pragma once
+#include "fb_decode.cuh"
+
+namespace fb {
+
+// ------------------------------------------------------------------------------------------------ tagged words
+__device__ __forceinline__ void ll_store(uint64_t* p, uint32_t payload, uint32_t tag) {
+  const uint64_t v = ((uint64_t)tag << 32) | payload;
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void ll_load2(const uint64_t* p, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ uint64_t ll_load1(const uint64_t* p) {
+  uint64_t a;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+
+// Poll `nwords` (even, 16-byte aligned base) tagged words into 32-bit payloads dst[0..nwords). Threads
+// tid, tid+nthreads, ... each own word pairs; all of a thread's loads are issued before any is checked.
+template <int MAXP>
+__device__ __forceinline__ void ll_gather(const uint64_t* src, int nwords, uint32_t tag, uint32_t* dst, int tid,
+                                          int nthreads, const WaitCtl& wc, int layer) {
+  const int npairs = nwords >> 1;
+  uint32_t pending = 0;
+#pragma unroll
+  for (int k = 0; k < MAXP; k++)
+    if (tid + k * nthreads < npairs) pending |= 1u << k;
+  for (unsigned spin = 0; pending; spin++) {
+    uint64_t a[MAXP], b[MAXP];
+#pragma unroll
+    for (int k = 0; k < MAXP; k++)
+      if (pending & (1u << k)) ll_load2(src + 2 * (size_t)(tid + k * nthreads), a[k], b[k]);
+#pragma unroll
+    for (int k = 0; k < MAXP; k++)
+      if (pending & (1u << k)) {
+        if ((uint32_t)(a[k] >> 32) == tag && (uint32_t)(b[k] >> 32) == tag) {
+          const int j = 2 * (tid + k * nthreads);
+          dst[j] = (uint32_t)a[k];
+          dst[j + 1] = (uint32_t)b[k];
+          pending &= ~(1u << k);
+        }
+      }
+    if (pending) {
+      if (*wc.s_abort) break;
+      if (spin > 16) __nanosleep(40);
+      if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+      if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, -1); break; }
+    }
+  }
+}
+
+// Arrival flags: polling the tagged data words directly from 75 000 threads floods the few L2 lines that hold a
+// vector, so a CTA first waits (one warp, a handful of coalesced loads per round) until every producer CTA has posted
+// its arrival flag, and only then gathers the words. The flag is posted without a fence, so the tags in the words
+// stay the correctness check: a word that lags behind its flag is simply polled again.
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// flags are posted with an atomic exchange: it is performed at L2 at once instead of waiting in the SM's store path
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+}
+// all consumer threads call; warp 0 polls flags[0..n) until each equals tag
+__device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
+                                           int layer) {
+  if (cw == 0) {
+    for (unsigned spin = 0;; spin++) {
+      // all loads of a round are issued before any is compared (n <= 256: at most 8 per lane)
+      uint32_t v[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
+      bool ok = true;
+#pragma unroll
+      for (int j = 0; j < 8; j++) ok = ok && (v[j] == tag);
+      if (__all_sync(0xffffffffu, ok)) break;
+      int stop = 0;
+      if (lane == 0) {
+        if (*wc.s_abort) stop = 1;
+        else if ((spin & 63) == 63 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; stop = 1; }
+        else if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, n); stop = 1; }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) break;
+    }
+  }
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+// a warp that has finished its part of a phase calls this; the CTA's last warp posts the flag
+__device__ __forceinline__ void post_when_cta_done(int* s_done, uint32_t* flag, uint32_t tag, int lane,
+                                                   long long* dbg = nullptr) {
+  __syncwarp();
+  if (lane == 0) {
+    const int old = atomicAdd(s_done, 1);
+    if (old == kConsumerWarps - 1) {
+      *s_done = 0;
+      st_relaxed_u32(flag, tag);
+      if (dbg) dbg[12] = (long long)globaltimer_ns();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ GEMV with a warp epilogue
+// Like consume_rows, but every finished block of RB rows is handed to `epi(row0_local, c, nvalid)` by the whole warp
+// (lane r<<3 holds the total of row r in c), so results leave the CTA as soon as they exist. For KS > 1 the slice
+// partials of a block meet in shared memory after the tile's group barrier and the slice-0 warp runs the epilogue.
+template <class KC, bool HZ, class XR, class Epi>
+__device__ __forceinline__ void consume_rows_epi(Pipe& p, int nrows, const XR& x, float* part_s, int cw, int lane,
+                                                 const WaitCtl& wc, int layer, Epi epi) {
+  constexpr int RB = KC::RB, TR = KC::TILE_ROWS;
+  static_assert(KC::KS == 1 || TR <= RB * KC::NSUB, "a warp sees at most one block per tile when K is sliced");
+  const int grp = cw >> 2, wg = cw & 3;
+  const int slice = wg % KC::KS, sub = wg / KC::KS;
+  const int rec = rec_bytes_of(KC::K, HZ);
+  const int ntiles = (nrows + TR - 1) / TR;
+  int mine = 0;   // tiles this group has processed (parity selects the partial buffer)
+  for (int t = 0; t < ntiles; t++) {
+    const uint32_t it = p.it + t;
+    if ((int)(it % kGroups) != grp) continue;
+    const int s = it % kStages;
+    const uint32_t ph = (it / kStages) & 1;
+    const bool ok = mbar_wait(&p.full[s], ph, wc, W_FULL, layer);
+    const int row0 = t * TR;
+    const int tr = min(TR, nrows - row0);
+    const uint8_t* tile = p.stages + (size_t)s * kStageBytes;
+    float* part = part_s + ((grp * 2 + (mine & 1)) * kWarpsPerGroup) * 4;   // [wg][4]
+    float keep = 0.f;
+    int keep_b = -1;
+    if (ok) {
+      for (int b = sub; b * RB < tr; b += KC::NSUB) {
+        int rows[RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) rows[r] = min(b * RB + r, tr - 1) * rec;
+        float acc[RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) acc[r] = 0.f;
+        rowblock_dot<KC, HZ>(tile, rows, slice, lane, x, acc);
+        const float c = reduce_rows<RB>(acc, lane);
+        if (KC::KS == 1) {
+          epi(row0 + b * RB, c, min(RB, tr - b * RB));
+        } else {
+          if ((lane & 7) == 0) part[wg * 4 + (lane >> 3)] = c;
+          keep = c;
+          keep_b = b;
+        }
+      }
+    }
+    named_bar_sync(kBarGroup0 + grp, kWarpsPerGroup * 32);   // the group's 4 warps are done with this tile
+    if (ok && wg == 0 && lane == 0) mbar_arrive(&p.empty[s]);
+    if (KC::KS > 1 && ok && slice == 0 && keep_b >= 0) {
+      float c = keep;
+#pragma unroll
+      for (int sl = 1; sl < KC::KS; sl++) c += part[(wg + sl) * 4 + (lane >> 3)];
+      epi(row0 + keep_b * RB, c, min(RB, tr - keep_b * RB));
+    }
+    mine++;
+  }
+  p.it += ntiles;
+}
+
+// ------------------------------------------------------------------------------------------------ staging from tagged vectors
+// xn = bf16( (float(h) * r) * float(w) ) from the tagged residual vector (dim/2 words)
+template <int MAXP>
+__device__ __forceinline__ void stage_norm_ll(const uint64_t* hll, const uint32_t* flags, int nflags, uint32_t tag,
+                                              const uint16_t* gw, int D, float eps, uint16_t* x_s, float* red, int tid_c,
+                                              const WaitCtl& wc, int layer, long long* dbg = nullptr) {
+  uint32_t* xs32 = reinterpret_cast<uint32_t*>(x_s);
+  const int npairs = D / 4;
+  uint2 wv[MAXP];                       // norm weights do not depend on the wait: fetch them first
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    wv[k] = pr < npairs ? __ldg(reinterpret_cast<const uint2*>(gw) + pr) : make_uint2(0, 0);
+  }
+  wait_flags(flags, nflags, tag, tid_c >> 5, tid_c & 31, wc, layer);
+  if (dbg && tid_c == 0) dbg[10] = (long long)globaltimer_ns();
+  ll_gather<MAXP>(hll, D / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
+  if (dbg && tid_c == 0) dbg[11] = (long long)globaltimer_ns();
+  // each thread squares the pairs it gathered itself: no barrier needed before this
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    if (pr < npairs) {
+      const uint32_t a = xs32[2 * pr], b = xs32[2 * pr + 1];
+      ss = fmaf(bflo(a), bflo(a), ss); ss = fmaf(bfhi(a), bfhi(a), ss);
+      ss = fmaf(bflo(b), bflo(b), ss); ss = fmaf(bfhi(b), bfhi(b), ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid_c & 31) == 0) red[tid_c >> 5] = ss;
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
+  const float r = 1.0f / sqrtf(tot / (float)D + eps);
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    if (pr < npairs) {
+      const uint32_t a = xs32[2 * pr], b = xs32[2 * pr + 1];
+      const uint32_t o0 = (uint32_t)f2bf(bflo(a) * r * bflo(wv[k].x)) | ((uint32_t)f2bf(bfhi(a) * r * bfhi(wv[k].x)) << 16);
+      const uint32_t o1 = (uint32_t)f2bf(bflo(b) * r * bflo(wv[k].y)) | ((uint32_t)f2bf(bfhi(b) * r * bfhi(wv[k].y)) << 16);
+      xs32[2 * pr] = o0;
+      xs32[2 * pr + 1] = o1;
+    }
+  }
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
+template <int MAXP>
+__device__ __forceinline__ void stage_plain_ll(const uint64_t* src, const uint32_t* flags, int nflags, uint32_t tag, int K,
+                                               uint16_t* x_s, int tid_c, const WaitCtl& wc, int layer) {
+  wait_flags(flags, nflags, tag, tid_c >> 5, tid_c & 31, wc, layer);
+  ll_gather<MAXP>(src, K / 2, tag, reinterpret_cast<uint32_t*>(x_s), tid_c, kConsumerThreads, wc, layer);
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
+// ------------------------------------------------------------------------------------------------ attention (tagged in/out)
+// q and the new k live in "pair-major" tagged words: word (head*HD/2 + p) = (x[p], x[p + HD/2]), which is what one
+// RoPE thread produces. A lane owns pairs 4*sl .. 4*sl+3, i.e. dims {4sl..4sl+3} and {HD/2+4sl..+3}.
+struct Attn2Args {
+  const uint64_t* q_ll;     // [NH * HD/2]
+  const uint64_t* k_ll;     // [NKV * HD/2] new key of this step, pair-major
+  const uint64_t* v_ll;     // [NKV * HD/2] new value, natural order: word w = (v[2w], v[2w+1])
+  uint64_t* ao_ll;          // [NH * HD/2] natural order
+  const uint16_t* kc;       // layer base: bf16 [max_seq, NKV, HD]
+  const uint16_t* vc;
+  float *pm, *pd, *pacc;    // chunk partials
+  unsigned* cnt;            // [NKV] arrival counters of the chunk merge
+  uint32_t* ao_flags;       // [NKV] arrival flags of the attention output
+  int nkv, pos, nchunks;
+  float scale;
+  uint32_t tag_in, tag_out;
+};
+
+template <int HD, int R>
+__device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch, int* misc, int cw, int lane, int tid_c,
+                                            const WaitCtl& wc, int layer) {
+  using C = AttnCfg<HD, R>;
+  constexpr int HP = HD / 2;
+  float* wacc = reinterpret_cast<float*>(scratch);                 // [CW][R][HD]  (dims in lane order, see below)
+  float* wm = wacc + kConsumerWarps * R * HD;                      // [CW][R]
+  float* wd = wm + kConsumerWarps * R;                             // [CW][R]
+  uint32_t* qs = reinterpret_cast<uint32_t*>(wd + kConsumerWarps * R);   // [R*HP] q pairs, then [HP] k pairs, [HP] v words
+  const int T = a.pos + 1;
+  const int items = a.nkv * a.nchunks;
+  const int chunk_len = (T + a.nchunks - 1) / a.nchunks;
+  const int seg = lane / C::SEG, sl = lane % C::SEG;
+  const bool active = sl < C::LPR;
+  for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    const int kvh = item / a.nchunks, c = item % a.nchunks;
+    const int t0 = c * chunk_len, t1 = min(T, t0 + chunk_len);
+    const bool has_new = (a.pos >= t0 && a.pos < t1);     // the chunk that contains this step's own position
+    // ---- gather q (R heads) and, for the last chunk, the new k / v ----
+    {
+      const int nq = R * HP;
+      const int total = nq + (has_new ? 2 * HP : 0);
+      // one pass: every thread owns at most one word pair of each source
+      uint32_t pending = 0;
+      const int pr = tid_c;
+      if (2 * pr < total) pending = 1;
+      for (unsigned spin = 0; pending; spin++) {
+        const int w = 2 * pr;
+        const uint64_t* src = w < nq ? a.q_ll + (size_t)kvh * R * HP + w
+                            : (w < nq + HP ? a.k_ll + (size_t)kvh * HP + (w - nq) : a.v_ll + (size_t)kvh * HP + (w - nq - HP));
+        uint64_t u, v;
+        ll_load2(src, u, v);
+        if ((uint32_t)(u >> 32) == a.tag_in && (uint32_t)(v >> 32) == a.tag_in) {
+          qs[w] = (uint32_t)u; qs[w + 1] = (uint32_t)v;
+          pending = 0;
+        } else {
+          if (*wc.s_abort) break;
+          if (spin > 16) __nanosleep(40);
+          if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+          if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)a.tag_in, -2); break; }
+        }
+      }
+    }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    float q[R][8];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t u = active ? qs[r * HP + 4 * sl + e] : 0u;
+        q[r][e] = bflo(u);        // dim 4sl+e
+        q[r][4 + e] = bfhi(u);    // dim HP+4sl+e
+      }
+    float m[R], den[R], acc[R][8];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+      m[r] = -1e30f; den[r] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
+    }
+    constexpr int BATCH = 2;
+    const int stride = kConsumerWarps * C::PPW;
+    for (int tb = t0 + cw * C::PPW; tb < t1; tb += BATCH * stride) {
+      uint2 klo[BATCH], khi[BATCH], vlo[BATCH], vhi[BATCH];
+      bool valid[BATCH];
+#pragma unroll
+      for (int j = 0; j < BATCH; j++) {
+        const int t = tb + j * stride + seg;
+        valid[j] = t < t1;
+        klo[j] = khi[j] = vlo[j] = vhi[j] = make_uint2(0, 0);
+        if (valid[j] && active) {
+          if (t == a.pos) {      // this step's own k / v: from the tagged words (the cache row is for later steps)
+            const uint32_t* kp = qs + R * HP + 4 * sl;
+            const uint32_t* vp = qs + R * HP + HP;
+            klo[j] = make_uint2((kp[0] & 0xffffu) | (kp[1] << 16), (kp[2] & 0xffffu) | (kp[3] << 16));
+            khi[j] = make_uint2((kp[0] >> 16) | (kp[1] & 0xffff0000u), (kp[2] >> 16) | (kp[3] & 0xffff0000u));
+            vlo[j] = make_uint2(vp[2 * sl], vp[2 * sl + 1]);
+            vhi[j] = make_uint2(vp[HP / 2 + 2 * sl], vp[HP / 2 + 2 * sl + 1]);
+          } else {
+            const size_t off = ((size_t)t * a.nkv + kvh) * HD + 4 * sl;
+            klo[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off));
+            khi[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off + HP));
+            vlo[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off));
+            vhi[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off + HP));
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < BATCH; j++) {
+        if (tb + j * stride >= t1) break;     // warp-uniform
+        const float kf[8] = {bflo(klo[j].x), bfhi(klo[j].x), bflo(klo[j].y), bfhi(klo[j].y),
+                             bflo(khi[j].x), bfhi(khi[j].x), bflo(khi[j].y), bfhi(khi[j].y)};
+        const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
+                             bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          float s = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
+#pragma unroll
+          for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          s *= a.scale;
+          if (valid[j]) {
+            const float m2 = fmaxf(m[r], s);
+            const float corr = __expf(m[r] - m2), w = __expf(s - m2);
+            den[r] = den[r] * corr + w;
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[r][e] = acc[r][e] * corr + w * vf[e];
+            m[r] = m2;
+          }
+        }
+      }
+    }
+    // merge the warp's segments
+#pragma unroll
+    for (int off = C::SEG; off < 32; off <<= 1) {
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m[r], off);
+        const float dn = __shfl_xor_sync(0xffffffffu, den[r], off);
+        const float gm = fmaxf(m[r], mo);
+        const float wa = __expf(m[r] - gm), wb = __expf(mo - gm);
+        den[r] = den[r] * wa + dn * wb;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          const float ao_ = __shfl_xor_sync(0xffffffffu, acc[r][e], off);
+          acc[r][e] = acc[r][e] * wa + ao_ * wb;
+        }
+        m[r] = gm;
+      }
+    }
+    if (seg == 0 && active) {
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        float* dst = wacc + ((size_t)cw * R + r) * HD;
+#pragma unroll
+        for (int e = 0; e < 4; e++) { dst[4 * sl + e] = acc[r][e]; dst[HP + 4 * sl + e] = acc[r][4 + e]; }
+        if (sl == 0) { wm[cw * R + r] = m[r]; wd[cw * R + r] = den[r]; }
+      }
+    }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    // ---- merge the CTA's warps; one thread per (head, dim pair) ----
+    for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
+      const int r = o / HP, d = 2 * (o % HP);
+      float gm = -1e30f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; w++) gm = fmaxf(gm, wm[w * R + r]);
+      float Dn = 0.f, A0 = 0.f, A1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; w++) {
+        const float e = __expf(wm[w * R + r] - gm);
+        Dn += wd[w * R + r] * e;
+        A0 += wacc[((size_t)w * R + r) * HD + d] * e;
+        A1 += wacc[((size_t)w * R + r) * HD + d + 1] * e;
+      }
+      const int qh = kvh * R + r;
+      if (a.nchunks == 1) {
+        ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
+      } else {
+        float* pa = a.pacc + ((size_t)qh * a.nchunks + c) * HD + d;
+        pa[0] = A0; pa[1] = A1;
+        if (d == 0) { a.pm[qh * a.nchunks + c] = gm; a.pd[qh * a.nchunks + c] = Dn; }
+      }
+    }
+    bool published = (a.nchunks == 1);
+    if (a.nchunks > 1) {
+      // last chunk of this kv head to arrive merges the partials of its R heads
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      if (tid_c == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(a.cnt + kvh, 1u);
+        const int last = (old == (unsigned)(a.nchunks - 1));
+        if (last) { a.cnt[kvh] = 0; __threadfence(); }
+        misc[16] = last;
+      }
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      if (misc[16]) {
+        for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
+          const int r = o / HP, d = 2 * (o % HP);
+          const int qh = kvh * R + r;
+          float gm = -1e30f;
+          for (int cc = 0; cc < a.nchunks; cc++) gm = fmaxf(gm, ld_cg_f32(a.pm + qh * a.nchunks + cc));
+          float Dn = 0.f, A0 = 0.f, A1 = 0.f;
+          for (int cc = 0; cc < a.nchunks; cc++) {
+            const float e = __expf(ld_cg_f32(a.pm + qh * a.nchunks + cc) - gm);
+            Dn += ld_cg_f32(a.pd + qh * a.nchunks + cc) * e;
+            const float* pa = a.pacc + ((size_t)qh * a.nchunks + cc) * HD + d;
+            A0 += ld_cg_f32(pa) * e;
+            A1 += ld_cg_f32(pa + 1) * e;
+          }
+          ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
+        }
+        published = true;
+      }
+    }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    if (published && tid_c == 0) st_relaxed_u32(a.ao_flags + kvh, a.tag_out);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ kernel
+struct Decode2Params {
+  const uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
+  const uint16_t *n1, *n2, *nf, *embed;
+  const float* invf;
+  uint16_t *kc, *vc;
+  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll;   // tagged vectors
+  float *pm, *pd, *pacc;
+  unsigned* cnt;
+  uint32_t *h_flags, *act_flags, *ao_flags;                          // arrival flags: [G], [G], [NKV]
+  DevStatus* status;
+  const int32_t* d_token;
+  uint16_t* d_h;
+  float* d_logits;
+  int32_t* d_next;
+  int32_t token, pos, max_seq;
+  int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks;
+  unsigned tag_base, spin_limit;
+  float eps, attn_scale, resid, emb_mult, logits_scaling;
+  long long* prof;
+  unsigned max_fly;
+};
+
+// tags: phase ids inside a layer
+enum { PH_QKV = 1, PH_ATT = 2, PH_O = 3, PH_GU = 4, PH_DOWN = 5, PH_LM = 6 };
+__device__ __forceinline__ uint32_t mk_tag(unsigned base, int layer, int ph) { return base + (unsigned)(layer * 8 + ph); }
+
+template <class KD, class KF, int HD, int R, bool HZ>
+__global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params P) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Smem sm = carve_smem(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = gridDim.x, b = blockIdx.x;
+  if (tid == 0) {
+    for (int s = 0; s < kStages; s++) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    *sm.s_abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
+  Pipe pipe{sm.stages, sm.full, sm.empty, 0u, P.max_fly};
+  constexpr int HP = HD / 2;
+  using KDS = typename SmallOf<KD>::type;     // QKV and O: few rows per CTA
+  using KFS = typename SmallOf<KF>::type;     // down projection
+  const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
+  const int QKV = (P.n_head + 2 * P.n_kv) * HD;
+  const int recD = rec_bytes_of(KD::K, HZ), recF = rec_bytes_of(KF::K, HZ);
+  int q0, q1, o0, o1, g0, g1, l0, l1;
+  cta_rows(QKV, 2, b, G, q0, q1);
+  cta_rows(D, 2, b, G, o0, o1);          // the same rows of h belong to this CTA in the O and the down phase
+  cta_rows(2 * FF, 4, b, G, g0, g1);     // (g_i, u_i, g_i+1, u_i+1) stay together: one tagged word of activations
+  cta_rows(V, 1, b, G, l0, l1);
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int l = 0; l < L && ok; l++) {
+        ok = produce_rows(pipe, P.w_qkv + ((size_t)l * QKV + q0) * recD, q1 - q0, KDS::TILE_ROWS, recD, wc, l) &&
+             produce_rows(pipe, P.w_o + ((size_t)l * D + o0) * recD, o1 - o0, KDS::TILE_ROWS, recD, wc, l) &&
+             produce_rows(pipe, P.w_gu + ((size_t)l * 2 * FF + g0) * recD, g1 - g0, KD::TILE_ROWS, recD, wc, l) &&
+             produce_rows(pipe, P.w_d + ((size_t)l * D + o0) * recF, o1 - o0, KFS::TILE_ROWS, recF, wc, l);
+      }
+      if (ok) produce_rows(pipe, P.w_lm + (size_t)l0 * recD, l1 - l0, KD::TILE_ROWS, recD, wc, L);
+      producer_drain(pipe, wc);
+    }
+  } else {
+    const int cw = warp, tid_c = tid;
+    const int wg = cw & 3;
+    float* part_s = sm.part;                                    // [groups][2][4 warps][4] slice partials
+    float* hown = sm.hown;                                      // this CTA's rows of the residual stream (exact bf16 values)
+    int* s_done = sm.misc + 20;                                 // warps of this CTA that finished the current producing phase
+    if (tid_c == 0) *s_done = 0;
+    constexpr int MAXP_D = (KD::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    constexpr int MAXP_F = (KF::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    // ---- residual stream at layer 0: every CTA reads the embedding row (or the caller's h) itself ----
+    {
+      int tok = P.d_token ? (int)ld_cg_u32(P.d_token) : P.token;
+      if ((unsigned)tok >= (unsigned)V) {
+        tok = 0;
+        if (tid_c == 0 && b == 0) atomicCAS(&P.status->code, 0, 6 /*FB_ERR_RANGE*/);
+      }
+      for (int i = tid_c; i < D; i += kConsumerThreads) {
+        const uint16_t v = P.d_h ? ld_cg_u16(P.d_h + i) : f2bf(bf2f(__ldg(P.embed + (size_t)tok * D + i)) * P.emb_mult);
+        sm.x_s[i] = v;
+        if (i >= o0 && i < o1) hown[i - o0] = bf2f(v);
+      }
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+    }
+    XRegs<KD> xd;
+#define FB_STAMP(i) do { if (P.prof && tid_c == 0) P.prof[((size_t)b * L + l) * 16 + (i)] = (long long)globaltimer_ns(); } while (0)
+    for (int l = 0; l < L; l++) {
+      uint16_t* kcl = P.kc + (size_t)l * P.max_seq * P.n_kv * HD;
+      uint16_t* vcl = P.vc + (size_t)l * P.max_seq * P.n_kv * HD;
+      const uint32_t tg_qkv = mk_tag(P.tag_base, l, PH_QKV), tg_att = mk_tag(P.tag_base, l, PH_ATT),
+                     tg_o = mk_tag(P.tag_base, l, PH_O), tg_gu = mk_tag(P.tag_base, l, PH_GU),
+                     tg_dn = mk_tag(P.tag_base, l, PH_DOWN);
+      // ================= QKV: norm1 -> GEMV -> RoPE -> tagged q / new k / new v, cache append =================
+      FB_STAMP(0);
+      if (l == 0) {
+        // x_s holds the raw residual: normalise in place (same arithmetic as stage_norm_ll)
+        float ss = 0.f;
+        for (int i = tid_c; i < D; i += kConsumerThreads) { const float v = bf2f(sm.x_s[i]); ss = fmaf(v, v, ss); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sm.red[cw] = ss;
+        named_bar_sync(kBarConsumers, kConsumerThreads);
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; w++) tot += sm.red[w];
+        const float r = 1.0f / sqrtf(tot / (float)D + P.eps);
+        for (int i = tid_c; i < D; i += kConsumerThreads)
+          sm.x_s[i] = f2bf(bf2f(sm.x_s[i]) * r * bf2f(__ldg(P.n1 + i)));
+        named_bar_sync(kBarConsumers, kConsumerThreads);
+      } else {
+        stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
+                              sm.x_s, sm.red, tid_c, wc, l, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
+      }
+      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
+      named_bar_sync(kBarConsumers, kConsumerThreads);          // x_s may be rewritten only after everyone has its slice
+      FB_STAMP(1);
+      consume_rows_epi<KDS, HZ>(pipe, q1 - q0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+        // lanes 0/8/16/24 hold rows row0..row0+3: two RoPE pairs (or four v dims)
+        const float c1 = __shfl_down_sync(0xffffffffu, c, 8);
+        if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
+          const int rs = q0 + row0 + (lane >> 3);              // stream row of the pair's first element (even)
+          const int head = rs / HD, within = rs % HD;
+          if (head < P.n_head + P.n_kv) {
+            const int i = within >> 1;
+            const float x0 = rbf(c), x1 = rbf(c1);
+            float sn, cs;
+            sincosf((float)P.pos * __ldg(P.invf + i), &sn, &cs);
+            const uint32_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
+            if (head < P.n_head) {
+              ll_store(P.q_ll + (size_t)head * HP + i, y0 | (y1 << 16), tg_qkv);
+            } else {
+              const int kvh = head - P.n_head;
+              ll_store(P.k_ll + (size_t)kvh * HP + i, y0 | (y1 << 16), tg_qkv);
+              uint16_t* kr = kcl + ((size_t)P.pos * P.n_kv + kvh) * HD;
+              kr[i] = (uint16_t)y0;
+              kr[i + HP] = (uint16_t)y1;
+            }
+          } else {
+            const int kvh = head - P.n_head - P.n_kv;
+            const uint32_t pv = (uint32_t)f2bf(c) | ((uint32_t)f2bf(c1) << 16);
+            ll_store(P.v_ll + (size_t)kvh * HP + (within >> 1), pv, tg_qkv);
+            *reinterpret_cast<uint32_t*>(vcl + ((size_t)P.pos * P.n_kv + kvh) * HD + within) = pv;
+          }
+        }
+      });
+      FB_STAMP(2);
+      // ================= attention =================
+      {
+        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll, kcl, vcl, P.pm, P.pd, P.pacc, P.cnt, P.ao_flags, P.n_kv, P.pos,
+                     P.nchunks, P.attn_scale, tg_qkv, tg_att};
+        named_bar_sync(kBarConsumers, kConsumerThreads);        // scratch (x_s/part) is free: every warp left the GEMV
+        attn2_phase<HD, R>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l);
+      }
+      FB_STAMP(3);
+      // ================= O projection + residual =================
+      stage_plain_ll<MAXP_D>(P.ao_ll, P.ao_flags, P.n_kv, tg_att, D, sm.x_s, tid_c, wc, l);
+      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      FB_STAMP(4);
+      consume_rows_epi<KDS, HZ>(pipe, o1 - o0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+        const int r = row0 + (lane >> 3);
+        float hn = 0.f;
+        if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+          hn = rbf(hown[r] + c * P.resid);
+          hown[r] = hn;
+        }
+        const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
+        if ((lane & 15) == 0 && (lane >> 3) < nvalid)
+          ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tg_o);
+      });
+      post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
+      FB_STAMP(5);
+      // ================= gate/up + SwiGLU =================
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c, wc, l);
+      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      FB_STAMP(6);
+      consume_rows_epi<KD, HZ>(pipe, g1 - g0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+        // rows (g_i, u_i, g_{i+1}, u_{i+1}) -> act[i], act[i+1] -> one tagged word
+        const float u = __shfl_down_sync(0xffffffffu, c, 8);
+        float av = 0.f;
+        if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
+          const float gg = rbf(c), uu = rbf(u);
+          av = rbf((gg / (1.0f + __expf(-gg))) * uu);
+        }
+        const float av1 = __shfl_down_sync(0xffffffffu, av, 16);
+        const int i = (g0 + row0) >> 1;                          // act index of lane 0's value: even, g0 % 4 == 0
+        if (lane == 0 && nvalid == 4)
+          ll_store(P.act_ll + (i >> 1), (uint32_t)f2bf(av) | ((uint32_t)f2bf(av1) << 16), tg_gu);
+      });
+      post_when_cta_done(s_done, P.act_flags + b, tg_gu, lane);
+      FB_STAMP(7);
+      // ================= down projection + residual =================
+      {
+        XRegs<KF> xf;
+        stage_plain_ll<MAXP_F>(P.act_ll, P.act_flags, G, tg_gu, FF, sm.x_s, tid_c, wc, l);
+        load_x_slice<KF>(sm.x_s, wg % KF::KS, lane, xf);
+        named_bar_sync(kBarConsumers, kConsumerThreads);
+        FB_STAMP(8);
+        consume_rows_epi<KFS, HZ>(pipe, o1 - o0, xf, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+          const int r = row0 + (lane >> 3);
+          float hn = 0.f;
+          if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+            hn = rbf(hown[r] + c * P.resid);
+            hown[r] = hn;
+          }
+          const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
+          if ((lane & 15) == 0 && (lane >> 3) < nvalid)
+            ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tg_dn);
+        });
+        post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
+      }
+      FB_STAMP(9);
+    }
+#undef FB_STAMP
+    // ================= final norm + LM head + arg-max =================
+    stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm.x_s, sm.red, tid_c, wc,
+                          L);
+    load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    consume_rows_epi<KD, HZ>(pipe, l1 - l0, xd, part_s, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
+      if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+        const int row = l0 + row0 + (lane >> 3);
+        const float y = c / P.logits_scaling;
+        if (P.d_logits) P.d_logits[row] = y;
+        if (y > bv || (y == bv && row < bi)) { bv = y; bi = row; }
+      }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sm.red[cw] = bv; sm.misc[cw] = bi; }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    const uint32_t tg_lm = mk_tag(P.tag_base, L, PH_LM);
+    if (tid_c == 0) {
+      for (int w = 1; w < kConsumerWarps; w++)
+        if (sm.red[w] > bv || (sm.red[w] == bv && sm.misc[w] < bi)) { bv = sm.red[w]; bi = sm.misc[w]; }
+      ll_store(P.cand_ll + 2 * b, __float_as_uint(bv), tg_lm);
+      ll_store(P.cand_ll + 2 * b + 1, (uint32_t)bi, tg_lm);
+    }
+    if (b == 0) {
+      uint32_t* cs = reinterpret_cast<uint32_t*>(sm.x_s);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      ll_gather<2>(P.cand_ll, 2 * G, tg_lm, cs, tid_c, kConsumerThreads, wc, L);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      if (cw == 0) {
+        float v = -INFINITY;
+        int ix = 0x7fffffff;
+        for (int c = lane; c < G; c += 32) {
+          const float ov = __uint_as_float(cs[2 * c]);
+          const int oi = (int)cs[2 * c + 1];
+          if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+          if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+        }
+        if (lane == 0 && P.d_next) *P.d_next = ix;
+      }
+    }
+    // final residual back to the caller (the reference clobbers its h argument): every CTA writes its own rows
+    if (P.d_h)
+      for (int r = tid_c; r < o1 - o0; r += kConsumerThreads) P.d_h[o0 + r] = f2bf(hown[r]);
+  }
+  __syncthreads();
+}
+
+}  // namespace fb

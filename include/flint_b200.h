@@ -116,9 +116,11 @@ int fb_gemv(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zeros,
  *   what 0: iteration limit of every device-side wait (default 4000000); a tiny value makes a launch give up
  *           with FB_ERR_TIMEOUT, which is how the time-out path is tested without hanging a GPU
  *   what 1: force the number of attention chunks per kv head (0 = choose from the cached length)
- *   what 2: value = device pointer to int64[16 * n_layer] (0 = off): SM-clock stamps of CTA 0 at the phase
- *           boundaries of every layer, the run-time replacement of the reference's -DNOSYNC/-DNOATTN diagnostic
- *           builds (reference: kernels/megakernel_decode.cu:15-24) */
+ *   what 2: value = device pointer to int64[sm_count * n_layer * 16] (0 = off): %globaltimer stamps (ns) of every CTA
+ *           at the phase boundaries of every layer, the run-time replacement of the reference's -DNOSYNC/-DNOATTN diagnostic
+ *           builds (reference: kernels/megakernel_decode.cu:15-24)
+ *   what 4: bulk weight copies one CTA keeps in flight at once (1..8, default 4)
+ *   what 3: kernel flavour: 2 = phases chained by tagged data words (default), 1 = phases separated by grid barriers */
 int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
 
 #ifdef __cplusplus
