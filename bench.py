@@ -113,13 +113,15 @@ def main():
     ap.add_argument("--config", default="granite-3b-class")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompts are for profiler captures only")
     a = ap.parse_args()
+    plen = a.prompt_len
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cfg = ModelArgs.from_name(a.config)
     metric, unit = "batch1_int4_decode_tok_per_s", "tok/s"
-    workload = (f"{a.config}: batch 1, {PROMPT_LEN}-token prompt, greedy decode, int4 g128 sym, "
+    workload = (f"{a.config}: batch 1, {plen}-token prompt, greedy decode, int4 g128 sym, "
                 f"KV max {cfg.block_size}; weights 1.70 GB >> 126 MB L2 (no L2 flush needed)")
 
     if a.impl == "reference":
@@ -132,14 +134,14 @@ def main():
         Pc = {k: v.cpu() for k, v in P.items()}
         del P
         n = max(1, min(a.steps, a.cpu_steps))
-        tps, dt = cpu_oracle_toks(cfg, Pc, n, PROMPT_LEN)
+        tps, dt = cpu_oracle_toks(cfg, Pc, n, plen)
         cores = os.cpu_count()
         line = {"impl": "reference", "metric": metric, "value": tps, "unit": unit, "n_gpus": a.gpus, "steps": n,
                 "warmup": 1, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
                 "config": {"workload": workload},
                 "cpu_baseline": {"value": tps, "unit": unit, "cores": cores, "kind": "port",
-                                 "sample": f"{n} decode steps at positions {PROMPT_LEN}.. of the full model"},
+                                 "sample": f"{n} decode steps at positions {plen}.. of the full model"},
                 "e2e": {"value": tps, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -152,9 +154,9 @@ def main():
     dev = torch.device(f"cuda:{local}")
     W = packing.synth_packed(cfg, 0, device=str(dev))
     eng = DecodeEngine(cfg, W, max_seq=cfg.block_size)
-    prompt = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=torch.Generator().manual_seed(1234)).tolist()
+    prompt = torch.randint(0, cfg.vocab_size, (plen,), generator=torch.Generator().manual_seed(1234)).tolist()
     K, Wm = a.steps, max(3, a.warmup)
-    if PROMPT_LEN + Wm + 2 * K + 4 > cfg.block_size:
+    if plen + Wm + 2 * K + 4 > cfg.block_size:
         raise SystemExit("steps do not fit the KV cache")
 
     # ---- prefill token by token (as the reference front-end does, reference: chat.py:85-86), untimed ----
@@ -162,7 +164,7 @@ def main():
         eng.decode(t, pos, want_logits=False)
     ring = torch.zeros(K + Wm + 1, dtype=torch.int32, device=dev)
     ring[0] = prompt[-1]
-    pos = PROMPT_LEN - 1
+    pos = plen - 1
     for i in range(Wm):                                   # warm-up steps (chained on the device)
         eng.decode_chained(ring[i:i + 1], pos, ring[i + 1:i + 2])
         pos += 1
@@ -240,15 +242,17 @@ def main():
         "mbu_vs_8TBs": bytes_tok * (tps / n_rep) / HBM_NOMINAL,
         "mbu_weights_only_vs_8TBs": weights_only * (tps / n_rep) / HBM_NOMINAL,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": which, "kernel": "decode_mega (one launch per token)"},
+                     "traffic": bytes_tok * 1.022, "traffic_note": "ncu: DRAM read+write / algorithmic = 1.022 on one "
+                     "launch of this kernel and model (profiles/decode_mega2_granite3b.md), scaled to this run's bytes",
+                     "peak_source": which, "kernel": "decode_mega2 (one launch per token)"},
         "e2e": {"value": tps_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": K, "clocks": clocks,
     }
     if not a.no_cpu:
         Pc = {k: v.cpu() for k, v in W.items()}
-        ctps, cdt = cpu_oracle_toks(cfg, Pc, a.cpu_steps, PROMPT_LEN)
+        ctps, cdt = cpu_oracle_toks(cfg, Pc, a.cpu_steps, plen)
         line["cpu_baseline"] = {"value": ctps, "unit": unit, "cores": os.cpu_count(), "kind": "port",
-                                "sample": f"{a.cpu_steps} decode steps at positions {PROMPT_LEN}.. of the full model "
+                                "sample": f"{a.cpu_steps} decode steps at positions {plen}.. of the full model "
                                           f"({cdt:.1f} s of CPU work)"}
     print(json.dumps(line))
     if world > 1:

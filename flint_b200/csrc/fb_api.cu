@@ -29,7 +29,7 @@ struct fb_ctx {
   int last_cuda_error;
   int force_chunks;
   long long* prof;
-  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll;   // tagged vectors of the data-flow kernel
+  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll, *part_ll;   // tagged vectors of the data-flow kernel
   unsigned* cnt;
   uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
   unsigned tag_base;
@@ -172,6 +172,10 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   c->maxchunks = c->sm_count / d.n_kv_head;
   if (c->maxchunks < 1) c->maxchunks = 1;
   if (c->maxchunks > 64) c->maxchunks = 64;
+  {  // the merging CTA gathers every other chunk's partial into shared memory next to its own
+    const int wpc_bytes = (c->rgqa * d.head_dim + 2 * c->rgqa) * 4;
+    if (c->maxchunks > kScratchBytes / wpc_bytes) c->maxchunks = kScratchBytes / wpc_bytes;
+  }
   // result buffer of a CTA must hold its rows of the widest phase
   {
     const int G = c->sm_count;
@@ -195,10 +199,12 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   A(dmalloc(&c->bar_ctr, 256));
   A(dmalloc(&c->status, sizeof(DevStatus)));
   const size_t hp = d.head_dim / 2;
-  const size_t ll_words[7] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
-                              (size_t)d.ffn / 2, 2 * (size_t)c->sm_count};
-  uint64_t** ll_ptrs[7] = {&c->h_ll, &c->q_ll, &c->k_ll, &c->v_ll, &c->ao_ll, &c->act_ll, &c->cand_ll};
-  for (int i = 0; i < 7; i++) {
+  const size_t wpc = (size_t)c->rgqa * d.head_dim + 2 * c->rgqa;
+  const size_t ll_words[8] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
+                              (size_t)d.ffn / 2, 2 * (size_t)c->sm_count, (size_t)d.n_kv_head * c->maxchunks * wpc};
+  uint64_t** ll_ptrs[8] = {&c->h_ll, &c->q_ll, &c->k_ll, &c->v_ll, &c->ao_ll, &c->act_ll, &c->cand_ll, &c->part_ll};
+  if ((size_t)(c->maxchunks - 1) * wpc * 4 + wpc * 4 > (size_t)kScratchBytes) e = cudaErrorInvalidValue;
+  for (int i = 0; i < 8; i++) {
     A(dmalloc(ll_ptrs[i], 8 * ll_words[i] + 16));
     if (e == cudaSuccess) A(cudaMemset(*ll_ptrs[i], 0, 8 * ll_words[i] + 16));
   }
@@ -230,7 +236,7 @@ int fb_ctx_destroy(fb_ctx* c) {
   DeviceGuard g(c->device);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
                   c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll,
-                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags};
+                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -384,11 +390,12 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
     Q.kc = (uint16_t*)c->kc; Q.vc = (uint16_t*)c->vc;
     Q.h_ll = c->h_ll; Q.q_ll = c->q_ll; Q.k_ll = c->k_ll; Q.v_ll = c->v_ll; Q.ao_ll = c->ao_ll; Q.act_ll = c->act_ll;
     Q.h_flags = c->flags; Q.act_flags = c->flags + 256; Q.ao_flags = c->flags + 512;
-    Q.cand_ll = c->cand_ll; Q.pm = c->pm; Q.pd = c->pd; Q.pacc = c->pacc; Q.cnt = c->cnt; Q.status = c->status;
+    Q.cand_ll = c->cand_ll; Q.part_ll = c->part_ll; Q.status = c->status;
     Q.d_token = d_token; Q.d_h = (uint16_t*)d_h; Q.d_logits = d_logits; Q.d_next = d_next;
     Q.token = token; Q.pos = pos; Q.max_seq = c->max_seq;
     Q.n_layer = d.n_layer; Q.dim = d.dim; Q.n_head = d.n_head; Q.n_kv = d.n_kv_head; Q.ffn = d.ffn; Q.vocab = d.vocab;
     Q.nchunks = chunks_for(c, pos + 1);
+    Q.maxchunks = c->maxchunks;
     const unsigned span = (unsigned)(d.n_layer + 1) * 8u;
     if (c->tag_base > 0xffffffffu - 2 * span) c->tag_base = 8;      // tags never reach 0 (the value of fresh buffers)
     Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;

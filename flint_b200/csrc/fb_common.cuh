@@ -10,8 +10,8 @@ namespace fb {
 
 // ------------------------------------------------------------------------------------------------ constants
 #ifndef FB_CW
-#define FB_CW 16
-#endif
+#define FB_CW 12      // 12 consumers + 1 producer = 13 warps -> 4 per scheduler -> 128 registers per thread, no spills that matter;
+#endif                // 16 consumers (17 warps, 96 registers) streams GEMVs slightly faster but spills in the attention phase
 #ifndef FB_DOT
 #define FB_DOT 0      // 0: bf16 pairs + fma.rn.f32.bf16 (activations packed bf16 in registers)
 #endif                // 1: prmt -> fp32 weights + fma.rn.f32 (activations fp32 in registers)

@@ -75,6 +75,7 @@ __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
 __device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
   uint32_t old;
   asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  (void)old;
 }
 // all consumer threads call; warp 0 polls flags[0..n) until each equals tag
 __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
@@ -177,7 +178,7 @@ __device__ __forceinline__ void consume_rows_epi(Pipe& p, int nrows, const XR& x
 template <int MAXP>
 __device__ __forceinline__ void stage_norm_ll(const uint64_t* hll, const uint32_t* flags, int nflags, uint32_t tag,
                                               const uint16_t* gw, int D, float eps, uint16_t* x_s, float* red, int tid_c,
-                                              const WaitCtl& wc, int layer, long long* dbg = nullptr) {
+                                              const WaitCtl& wc, int layer, bool have_h, long long* dbg = nullptr) {
   uint32_t* xs32 = reinterpret_cast<uint32_t*>(x_s);
   const int npairs = D / 4;
   uint2 wv[MAXP];                       // norm weights do not depend on the wait: fetch them first
@@ -186,10 +187,12 @@ __device__ __forceinline__ void stage_norm_ll(const uint64_t* hll, const uint32_
     const int pr = tid_c + k * kConsumerThreads;
     wv[k] = pr < npairs ? __ldg(reinterpret_cast<const uint2*>(gw) + pr) : make_uint2(0, 0);
   }
-  wait_flags(flags, nflags, tag, tid_c >> 5, tid_c & 31, wc, layer);
-  if (dbg && tid_c == 0) dbg[10] = (long long)globaltimer_ns();
-  ll_gather<MAXP>(hll, D / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
-  if (dbg && tid_c == 0) dbg[11] = (long long)globaltimer_ns();
+  if (!have_h) {      // layer 0 finds the raw residual already in x_s
+    wait_flags(flags, nflags, tag, tid_c >> 5, tid_c & 31, wc, layer);
+    if (dbg && tid_c == 0) dbg[10] = (long long)globaltimer_ns();
+    ll_gather<MAXP>(hll, D / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
+    if (dbg && tid_c == 0) dbg[11] = (long long)globaltimer_ns();
+  }
   // each thread squares the pairs it gathered itself: no barrier needed before this
   float ss = 0.f;
 #pragma unroll
@@ -241,12 +244,11 @@ struct Attn2Args {
   uint64_t* ao_ll;          // [NH * HD/2] natural order
   const uint16_t* kc;       // layer base: bf16 [max_seq, NKV, HD]
   const uint16_t* vc;
-  float *pm, *pd, *pacc;    // chunk partials
-  unsigned* cnt;            // [NKV] arrival counters of the chunk merge
+  uint64_t* part_ll;        // [NKV][maxchunks][R*HD + 2R] tagged chunk partials (acc, then m, then d per head)
   uint32_t* ao_flags;       // [NKV] arrival flags of the attention output
-  int nkv, pos, nchunks;
+  int nkv, pos, nchunks, maxchunks;
   float scale;
-  uint32_t tag_in, tag_out;
+  uint32_t tag_in, tag_part, tag_out;
 };
 
 template <int HD, int R>
@@ -391,6 +393,9 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
     // ---- merge the CTA's warps; one thread per (head, dim pair) ----
+    constexpr int WPC = R * HD + 2 * R;                       // words of one chunk partial
+    float* own = reinterpret_cast<float*>(scratch + kScratchBytes) - WPC;   // chunk 0 keeps its partial here
+    uint64_t* mine = a.part_ll + ((size_t)kvh * a.maxchunks + c) * WPC;
     for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
       const int r = o / HP, d = 2 * (o % HP);
       float gm = -1e30f;
@@ -407,45 +412,48 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
       const int qh = kvh * R + r;
       if (a.nchunks == 1) {
         ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
+      } else if (c != 0) {
+        ll_store(mine + r * HD + d, __float_as_uint(A0), a.tag_part);
+        ll_store(mine + r * HD + d + 1, __float_as_uint(A1), a.tag_part);
+        if (d == 0) {
+          ll_store(mine + R * HD + r, __float_as_uint(gm), a.tag_part);
+          ll_store(mine + R * HD + R + r, __float_as_uint(Dn), a.tag_part);
+        }
       } else {
-        float* pa = a.pacc + ((size_t)qh * a.nchunks + c) * HD + d;
-        pa[0] = A0; pa[1] = A1;
-        if (d == 0) { a.pm[qh * a.nchunks + c] = gm; a.pd[qh * a.nchunks + c] = Dn; }
+        // chunk 0 is the merger: its own partial stays in shared memory (own[] overlays nothing that is still read)
+        own[r * HD + d] = A0; own[r * HD + d + 1] = A1;
+        if (d == 0) { own[R * HD + r] = gm; own[R * HD + R + r] = Dn; }
       }
     }
-    bool published = (a.nchunks == 1);
-    if (a.nchunks > 1) {
-      // last chunk of this kv head to arrive merges the partials of its R heads
+    const bool merger = (a.nchunks > 1 && c == 0);
+    if (merger) {
+      // chunk 0 of a kv head merges: the other chunks' partials arrive as tagged words, no counter, no fence
+      named_bar_sync(kBarConsumers, kConsumerThreads);        // wacc / wm / wd are dead, own[] is written
+      uint32_t* pg = reinterpret_cast<uint32_t*>(scratch);     // [(nchunks-1)][WPC] payloads
+      const int total = (a.nchunks - 1) * WPC;
+      const uint64_t* src = a.part_ll + ((size_t)kvh * a.maxchunks + 1) * WPC;
+      for (int off = 0; off < total; off += 4096)
+        ll_gather<4>(src + off, min(4096, total - off), a.tag_part, pg + off, tid_c, kConsumerThreads, wc, layer);
       named_bar_sync(kBarConsumers, kConsumerThreads);
-      if (tid_c == 0) {
-        __threadfence();
-        const unsigned old = atomicAdd(a.cnt + kvh, 1u);
-        const int last = (old == (unsigned)(a.nchunks - 1));
-        if (last) { a.cnt[kvh] = 0; __threadfence(); }
-        misc[16] = last;
-      }
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      if (misc[16]) {
-        for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
-          const int r = o / HP, d = 2 * (o % HP);
-          const int qh = kvh * R + r;
-          float gm = -1e30f;
-          for (int cc = 0; cc < a.nchunks; cc++) gm = fmaxf(gm, ld_cg_f32(a.pm + qh * a.nchunks + cc));
-          float Dn = 0.f, A0 = 0.f, A1 = 0.f;
-          for (int cc = 0; cc < a.nchunks; cc++) {
-            const float e = __expf(ld_cg_f32(a.pm + qh * a.nchunks + cc) - gm);
-            Dn += ld_cg_f32(a.pd + qh * a.nchunks + cc) * e;
-            const float* pa = a.pacc + ((size_t)qh * a.nchunks + cc) * HD + d;
-            A0 += ld_cg_f32(pa) * e;
-            A1 += ld_cg_f32(pa + 1) * e;
-          }
-          ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
+      const float* pf = reinterpret_cast<const float*>(pg);
+      for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
+        const int r = o / HP, d = 2 * (o % HP);
+        float gm = own[R * HD + r];
+        for (int cc = 0; cc < a.nchunks - 1; cc++) gm = fmaxf(gm, pf[cc * WPC + R * HD + r]);
+        float e = __expf(own[R * HD + r] - gm);
+        float Dn = own[R * HD + R + r] * e, A0 = own[r * HD + d] * e, A1 = own[r * HD + d + 1] * e;
+        for (int cc = 0; cc < a.nchunks - 1; cc++) {
+          e = __expf(pf[cc * WPC + R * HD + r] - gm);
+          Dn += pf[cc * WPC + R * HD + R + r] * e;
+          A0 += pf[cc * WPC + r * HD + d] * e;
+          A1 += pf[cc * WPC + r * HD + d + 1] * e;
         }
-        published = true;
+        const int qh = kvh * R + r;
+        ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
-    if (published && tid_c == 0) st_relaxed_u32(a.ao_flags + kvh, a.tag_out);
+    if ((a.nchunks == 1 || merger) && tid_c == 0) st_relaxed_u32(a.ao_flags + kvh, a.tag_out);
   }
 }
 
@@ -456,8 +464,7 @@ struct Decode2Params {
   const float* invf;
   uint16_t *kc, *vc;
   uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll;   // tagged vectors
-  float *pm, *pd, *pacc;
-  unsigned* cnt;
+  uint64_t* part_ll;
   uint32_t *h_flags, *act_flags, *ao_flags;                          // arrival flags: [G], [G], [NKV]
   DevStatus* status;
   const int32_t* d_token;
@@ -465,7 +472,7 @@ struct Decode2Params {
   float* d_logits;
   int32_t* d_next;
   int32_t token, pos, max_seq;
-  int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks;
+  int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks, maxchunks;
   unsigned tag_base, spin_limit;
   float eps, attn_scale, resid, emb_mult, logits_scaling;
   long long* prof;
@@ -473,7 +480,7 @@ struct Decode2Params {
 };
 
 // tags: phase ids inside a layer
-enum { PH_QKV = 1, PH_ATT = 2, PH_O = 3, PH_GU = 4, PH_DOWN = 5, PH_LM = 6 };
+enum { PH_QKV = 1, PH_ATT = 2, PH_O = 3, PH_GU = 4, PH_DOWN = 5, PH_LM = 6, PH_PART = 7 };
 __device__ __forceinline__ uint32_t mk_tag(unsigned base, int layer, int ph) { return base + (unsigned)(layer * 8 + ph); }
 
 template <class KD, class KF, int HD, int R, bool HZ>
@@ -547,25 +554,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
                      tg_dn = mk_tag(P.tag_base, l, PH_DOWN);
       // ================= QKV: norm1 -> GEMV -> RoPE -> tagged q / new k / new v, cache append =================
       FB_STAMP(0);
-      if (l == 0) {
-        // x_s holds the raw residual: normalise in place (same arithmetic as stage_norm_ll)
-        float ss = 0.f;
-        for (int i = tid_c; i < D; i += kConsumerThreads) { const float v = bf2f(sm.x_s[i]); ss = fmaf(v, v, ss); }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) sm.red[cw] = ss;
-        named_bar_sync(kBarConsumers, kConsumerThreads);
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; w++) tot += sm.red[w];
-        const float r = 1.0f / sqrtf(tot / (float)D + P.eps);
-        for (int i = tid_c; i < D; i += kConsumerThreads)
-          sm.x_s[i] = f2bf(bf2f(sm.x_s[i]) * r * bf2f(__ldg(P.n1 + i)));
-        named_bar_sync(kBarConsumers, kConsumerThreads);
-      } else {
-        stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
-                              sm.x_s, sm.red, tid_c, wc, l, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
+      if (b < P.n_kv * P.nchunks) {
+        // the K/V rows this CTA will attend in this layer: pull them into L2 now, they do not depend on anything
+        const int kvh = b / P.nchunks, c = b % P.nchunks;
+        const int T = P.pos + 1, clen = (T + P.nchunks - 1) / P.nchunks;
+        const int t0 = c * clen, t1 = min(min(T, t0 + clen), t0 + 64);
+        constexpr int PER_ROW = (HD * 2 + 63) / 64;
+        for (int i = tid_c; i < (t1 - t0) * PER_ROW * 2; i += kConsumerThreads) {
+          const int t = t0 + (i >> 1) / PER_ROW, seg = (i >> 1) % PER_ROW;
+          const uint16_t* base = ((i & 1) ? vcl : kcl) + ((size_t)t * P.n_kv + kvh) * HD;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(base) + seg * 64));
+        }
       }
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
+                            sm.x_s, sm.red, tid_c, wc, l, l == 0, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
       named_bar_sync(kBarConsumers, kConsumerThreads);          // x_s may be rewritten only after everyone has its slice
       FB_STAMP(1);
@@ -601,8 +603,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       FB_STAMP(2);
       // ================= attention =================
       {
-        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll, kcl, vcl, P.pm, P.pd, P.pacc, P.cnt, P.ao_flags, P.n_kv, P.pos,
-                     P.nchunks, P.attn_scale, tg_qkv, tg_att};
+        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll, kcl, vcl, P.part_ll, P.ao_flags, P.n_kv, P.pos, P.nchunks,
+                     P.maxchunks, P.attn_scale, tg_qkv, mk_tag(P.tag_base, l, PH_PART), tg_att};
         named_bar_sync(kBarConsumers, kConsumerThreads);        // scratch (x_s/part) is free: every warp left the GEMV
         attn2_phase<HD, R>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l);
       }
@@ -626,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
       FB_STAMP(5);
       // ================= gate/up + SwiGLU =================
-      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c, wc, l);
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c, wc, l, false);
       load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
       named_bar_sync(kBarConsumers, kConsumerThreads);
       FB_STAMP(6);
@@ -670,7 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
 #undef FB_STAMP
     // ================= final norm + LM head + arg-max =================
     stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm.x_s, sm.red, tid_c, wc,
-                          L);
+                          L, false);
     load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
     named_bar_sync(kBarConsumers, kConsumerThreads);
     float bv = -INFINITY;
