@@ -8,6 +8,7 @@
 
 #include "../../include/flint_b200.h"
 #include "fb_decode2.cuh"
+#include "fb_verify.cuh"
 
 using namespace fb;
 
@@ -33,6 +34,7 @@ struct fb_ctx {
   unsigned* cnt;
   uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
   unsigned tag_base;
+  uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   int max_fly;
   int version;                                                      // 2: data-flow kernel (default), 1: grid-barrier kernel
 };
@@ -123,6 +125,55 @@ int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+template <int MT, int KC, int EPI, int HD>
+cudaError_t launch_vgemm_kc(const VGemmParams& p, cudaStream_t st) {
+  static bool configured = false;
+  constexpr int smem = v_gemm_smem<MT, KC>();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, KC, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  v_gemm<MT, KC, EPI, HD><<<(p.rows + VCfg<MT>::RT - 1) / VCfg<MT>::RT, 256, smem, st>>>(p);
+  return cudaGetLastError();
+}
+template <int MT, int EPI, int HD>
+cudaError_t launch_vgemm(const VGemmParams& p, cudaStream_t st) {
+  return (p.K % 256 == 0) ? launch_vgemm_kc<MT, 256, EPI, HD>(p, st) : launch_vgemm_kc<MT, 128, EPI, HD>(p, st);
+}
+template <int MT, int EPI>
+cudaError_t launch_vgemm_hd(const VGemmParams& p, int hd, cudaStream_t st) {
+  if (EPI != EPI_QKV) return launch_vgemm<MT, EPI, 64>(p, st);
+  switch (hd) {
+    case 64: return launch_vgemm<MT, EPI, 64>(p, st);
+    case 80: return launch_vgemm<MT, EPI, 80>(p, st);
+    case 128: return launch_vgemm<MT, EPI, 128>(p, st);
+  }
+  return cudaErrorInvalidValue;
+}
+template <int EPI>
+cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int hd, cudaStream_t st) {
+  switch (mt) {
+    case 16: return launch_vgemm_hd<16, EPI>(p, hd, st);
+    case 32: return launch_vgemm_hd<32, EPI>(p, hd, st);
+    case 64: return launch_vgemm_hd<64, EPI>(p, hd, st);
+  }
+  return cudaErrorInvalidValue;
+}
+cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint8_t* amask,
+                         uint16_t* ao, int pos, int M, cudaStream_t st) {
+  const fb_model_desc& d = c->d;
+  dim3 grid(M, d.n_kv_head);
+#define FB_VATTN(HD_, R_)                                                                                          \
+  if (d.head_dim == HD_ && c->rgqa == R_) {                                                                        \
+    v_attn<HD_, R_><<<grid, 512, 0, st>>>(q, kc, vc, amask, ao, d.n_head, d.n_kv_head, pos, M, d.attn_scale);      \
+    return cudaGetLastError();                                                                                     \
+  }
+  FB_VATTN(64, 4) FB_VATTN(80, 4) FB_VATTN(64, 5) FB_VATTN(128, 4)
+#undef FB_VATTN
+  return cudaErrorInvalidValue;
+}
+
 }  // namespace
 
 extern "C" {
@@ -210,6 +261,14 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   }
   A(dmalloc(&c->cnt, 256));
   if (e == cudaSuccess) A(cudaMemset(c->cnt, 0, 256));
+  {
+    const size_t rowsz[5] = {(size_t)d.dim, (size_t)d.dim, (size_t)QD, (size_t)QD, (size_t)d.ffn};
+    uint16_t** vp[5] = {&c->vh, &c->vxn, &c->vq, &c->vao, &c->vact};
+    for (int i = 0; i < 5; i++) {
+      A(dmalloc(vp[i], 64 * rowsz[i] * 2));
+      if (e == cudaSuccess) A(cudaMemset(*vp[i], 0, 64 * rowsz[i] * 2));
+    }
+  }
   A(dmalloc(&c->flags, 3 * 256 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
@@ -236,7 +295,7 @@ int fb_ctx_destroy(fb_ctx* c) {
   DeviceGuard g(c->device);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
                   c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll,
-                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll};
+                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -430,6 +489,68 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn, dim3(c->sm_count), dim3(kThreads), args,
                                          (size_t)kSmemBytes, (cudaStream_t)stream));
   c->bar_base += nbar * (unsigned)c->sm_count;
+  return FB_OK;
+}
+
+int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t* d_depth, const uint8_t* d_amask,
+              int32_t M, int32_t pos, float* d_logits, void* d_feat, void* stream) {
+  if (!c || !d_depth || !d_amask || (!d_tokens && !d_h)) return FB_ERR_ARG;
+  if (!c->weights_bound || !c->kc) return FB_ERR_STATE;
+  if (!d_h && !c->embed) return FB_ERR_STATE;
+  if (M < 1 || M > 64) return FB_ERR_RANGE;          /* never fall through to another M (reference: result.md:112-113) */
+  if (pos < 0 || pos + M > c->max_seq) return FB_ERR_RANGE;
+  const fb_model_desc& d = c->d;
+  DeviceGuard g(c->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int D = d.dim, FF = d.ffn, HD = d.head_dim, QD = d.n_head * HD, QKV = (d.n_head + 2 * d.n_kv_head) * HD;
+  const bool hz = d.has_zeros != 0;
+  const int recD = rec_bytes_of(D, hz), recQ = rec_bytes_of(QD, hz), recF = rec_bytes_of(FF, hz);
+  v_embed<<<M, 256, 0, st>>>(d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh, D, d.vocab, d.emb_mult,
+                             &c->status->code);
+  FB_CUDA(c, cudaGetLastError());
+  VGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.has_zeros = hz; p.depth = d_depth; p.invf = c->invf; p.n_head = d.n_head; p.nkv = d.n_kv_head; p.pos = pos;
+  p.resid = d.resid_mult; p.logits_scaling = d.logits_scaling;
+  for (int l = 0; l < d.n_layer; l++) {
+    uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
+    uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
+    v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
+    p.w = c->w_qkv + (size_t)l * QKV * recD; p.x_t = c->vxn; p.rows = QKV; p.K = D; p.rec = recD;
+    p.q = c->vq; p.kc = kcl; p.vc = vcl;
+    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, HD, st));
+    FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, st));
+    p.w = c->w_o + (size_t)l * D * recQ; p.x_t = c->vao; p.rows = D; p.K = QD; p.rec = recQ; p.h = c->vh; p.out_ld = D;
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
+    v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
+    p.w = c->w_gu + (size_t)l * 2 * FF * recD; p.x_t = c->vxn; p.rows = 2 * FF; p.K = D; p.rec = recD; p.act_t = c->vact;
+    p.out_ld = FF;
+    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, HD, st));
+    p.w = c->w_d + (size_t)l * D * recF; p.x_t = c->vact; p.rows = D; p.K = FF; p.rec = recF; p.out_ld = D;
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
+  }
+  v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, d.rms_eps);
+  if (d_logits) {
+    p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.K = D; p.rec = recD; p.logits = d_logits; p.out_ld = d.vocab;
+    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, HD, st));
+  }
+  FB_CUDA(c, cudaGetLastError());
+  return FB_OK;
+}
+
+int fb_kv_move(fb_ctx* c, const int32_t* src, const int32_t* dst, int32_t n, void* stream) {
+  if (!c || !c->kc || (n > 0 && (!src || !dst))) return FB_ERR_ARG;
+  const fb_model_desc& d = c->d;
+  DeviceGuard g(c->device);
+  const size_t row = (size_t)d.n_kv_head * d.head_dim * 2, layer = (size_t)c->max_seq * row;
+  for (int i = 0; i < n; i++) {     /* sequential, like the reference loop (reference: spec_tree.py:126-128) */
+    if (src[i] < 0 || dst[i] < 0 || src[i] >= c->max_seq || dst[i] >= c->max_seq) return FB_ERR_RANGE;
+    if (src[i] == dst[i]) continue;
+    for (void* base : {c->kc, c->vc})
+      FB_CUDA(c, cudaMemcpy2DAsync((char*)base + dst[i] * row, layer, (char*)base + src[i] * row, layer, row, d.n_layer,
+                                   cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  }
   return FB_OK;
 }
 

@@ -134,6 +134,50 @@ class DecodeEngine:
     def next_token(self) -> torch.Tensor:
         return self._next
 
+    # ------------------------------------------------------------------ M-token tree verification
+    def _tree_args(self, M: int, depth, amask):
+        if depth is None:
+            depth = torch.arange(M, dtype=torch.int32, device=self.device)            # chain: depth = index
+        if amask is None:
+            amask = torch.tril(torch.ones(M, M, dtype=torch.uint8, device=self.device))  # chain: causal
+        depth = torch.as_tensor(depth, device=self.device).to(torch.int32).contiguous()
+        amask = torch.as_tensor(amask, device=self.device).to(torch.uint8).contiguous()
+        if depth.numel() != M or tuple(amask.shape) != (M, M):
+            raise ValueError("depth must have M entries and amask must be [M, M]")
+        return depth, amask
+
+    def verify(self, tokens, pos: int, depth=None, amask=None, want_logits: bool = True):
+        """Score M candidate tokens in one weight pass: returns (logits f32 [M, vocab] or None, feature bf16 [M, dim]).
+        Node m lands in cache slot pos+m (reference: kernels/verify_mega.cu:153-158)."""
+        tok = torch.as_tensor(tokens, device=self.device).to(torch.int32).contiguous()
+        M = tok.numel()
+        depth, amask = self._tree_args(M, depth, amask)
+        logits = torch.empty(M, self.cfg.vocab_size, dtype=torch.float32, device=self.device) if want_logits else None
+        feat = torch.empty(M, self.cfg.dim, dtype=torch.bfloat16, device=self.device)
+        _lib.check(self.lib.fb_verify(self._ctx, _ptr(tok), None, _ptr(depth), _ptr(amask), M, int(pos), _ptr(logits),
+                                      _ptr(feat), _stream_ptr(self.device)), "fb_verify")
+        self._keepalive = (tok, depth, amask)
+        return logits, feat
+
+    def verify_h(self, h: torch.Tensor, pos: int, depth, amask):
+        """Same, from already multiplied embeddings h bf16 [M, dim] (the reference's calling convention)."""
+        M = h.shape[0]
+        depth, amask = self._tree_args(M, depth, amask)
+        logits = torch.empty(M, self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        feat = torch.empty(M, self.cfg.dim, dtype=torch.bfloat16, device=self.device)
+        hc = h.contiguous()
+        _lib.check(self.lib.fb_verify(self._ctx, None, _ptr(hc), _ptr(depth), _ptr(amask), M, int(pos), _ptr(logits),
+                                      _ptr(feat), _stream_ptr(self.device)), "fb_verify")
+        self._keepalive = (hc, depth, amask)
+        return logits, feat
+
+    def kv_move(self, src, dst):
+        """cache[:, dst[i]] = cache[:, src[i]] in order, K and V, every layer (reference: spec_tree.py:126-128)."""
+        n = len(src)
+        a = (ctypes.c_int32 * n)(*[int(x) for x in src])
+        b = (ctypes.c_int32 * n)(*[int(x) for x in dst])
+        _lib.check(self.lib.fb_kv_move(self._ctx, a, b, n, _stream_ptr(self.device)), "fb_kv_move")
+
 
 # --------------------------------------------------------------------------------------------------
 # Reference-shaped launch function. The reference infers every dimension from tensor sizes
@@ -170,6 +214,18 @@ def decode_mega_launch(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm
     eng = _engine_for(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h.shape[0], kc, vc,
                       scale, rope_base, resid, logits_scaling)
     return eng.decode_h(h, int(pos))
+
+
+def verify_mega_launch(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h, kc, vc, depth, amask, pos, M,
+                       scale, rope_base, resid, logits_scaling):
+    """Drop-in for the reference's `verify_mega_launch` (reference: kernels/verify_mega.cu:246-283): same arguments,
+    returns [logits f32 [M, vocab], feature bf16 [M, dim]]. Any M in 1..64 is accepted."""
+    eng = _engine_for(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm, s_lm, h.shape[1], kc, vc,
+                      scale, rope_base, resid, logits_scaling)
+    if int(M) != h.shape[0]:
+        raise ValueError("M must equal h.shape[0]")
+    logits, feat = eng.verify_h(h, int(pos), depth, amask)
+    return [logits, feat]
 
 
 def decode_occupancy():

@@ -96,6 +96,20 @@ int fb_bind_kv(fb_ctx* ctx, void* d_k, void* d_v, int32_t max_seq);
 int fb_decode(fb_ctx* ctx, int32_t token, const int32_t* d_token, void* d_h, int32_t pos, float* d_logits,
               int32_t* d_next, void* stream);
 
+/* M-token tree verification: every weight row is read once for all M candidate tokens. Replaces verify_mega_launch
+ * (reference: kernels/verify_mega.cu:246-283) with its tree semantics (reference: kernels/verify_mega.cu:143,153-158,169):
+ * token m is written to cache slot pos+m, rotated at position pos+depth[m], and sees every slot < pos plus the new
+ * slots j with amask[m*M + j] != 0. M is 1..64 (any value, padded internally to 16/32/64); other M is FB_ERR_RANGE.
+ *   d_tokens : device int32[M], or NULL when d_h is given
+ *   d_h      : bf16 [M, dim] already multiplied embeddings (the reference's argument), or NULL
+ *   d_logits : f32 [M, vocab] or NULL;   d_feat : bf16 [M, dim] post-final-norm feature (the draft head's input) or NULL */
+int fb_verify(fb_ctx* ctx, const int32_t* d_tokens, const void* d_h, const int32_t* d_depth, const uint8_t* d_amask,
+              int32_t M, int32_t pos, float* d_logits, void* d_feat, void* stream);
+
+/* Tree KV surgery after acceptance: cache row dst[i] <- row src[i] in every layer, in order, for K and V.
+ * src/dst are HOST arrays. Replaces `kc[:, dst] = kc[:, src]` (reference: spec_tree.py:126-128). */
+int fb_kv_move(fb_ctx* ctx, const int32_t* src, const int32_t* dst, int32_t n, void* stream);
+
 /* Stand-alone slices of the same path, on the streaming layout (unit-test granularity; they replace the
  * reference's GEMV family, reference: kernels/int4_gemv.cu:384-424).
  *   fb_stream_bytes : bytes of the streaming layout for one [rows, k] matrix

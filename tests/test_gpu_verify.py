@@ -1,0 +1,154 @@
+"""GPU parity of the M-token tree verification path against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from flint_b200 import _lib, packing
+from flint_b200.config import ModelArgs
+from flint_b200.engine import DecodeEngine, verify_mega_launch
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _tol(ref):
+    return 2e-2 * max(1.0, float(np.abs(ref).max()) / 2.56)
+
+
+def _argmax_ok(lg, ref):
+    """Equal arg-max, except where the oracle's own top-2 margin is inside the logit tolerance (a near-tie)."""
+    for m in range(ref.shape[0]):
+        a, b = int(lg[m].argmax()), int(ref[m].argmax())
+        if a != b and ref[m][b] - ref[m][a] > _tol(ref[m]):
+            return False
+    return True
+
+
+def _cuda(P):
+    return {k: v.cuda() for k, v in P.items()}
+
+
+def _prefix(orc, eng, toks):
+    for p, t in enumerate(toks):
+        orc.decode(t, p)
+        eng.decode(t, p, want_logits=False)
+
+
+@pytest.mark.parametrize("asym", [False, True])
+@pytest.mark.parametrize("M", [1, 5, 16, 26])
+def test_tiny_chain_verify_vs_oracle(M, asym):
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0, asym=asym)
+    orc, eng = O.OracleModel(cfg, P, 128), DecodeEngine(cfg, _cuda(P), max_seq=128)
+    _prefix(orc, eng, [3, 1, 4, 1, 5, 9, 2])
+    toks = torch.randint(0, cfg.vocab_size, (M,), generator=torch.Generator().manual_seed(M)).tolist()
+    ref_lg, ref_ft = orc.verify(toks, 7)
+    lg, ft = eng.verify(toks, 7)
+    eng.check()
+    lg = lg.cpu().numpy()
+    assert np.abs(lg - ref_lg).max() < _tol(ref_lg)
+    assert _argmax_ok(lg, ref_lg)
+    f = O.bf16_to_f32(ft.cpu().view(torch.int16).numpy().view(np.uint16))
+    assert np.abs(f - O.bf16_to_f32(ref_ft)).max() < 0.1
+    # the M new cache rows
+    kc = O.bf16_to_f32(eng.kc[:, 7:7 + M].cpu().view(torch.int16).numpy().view(np.uint16))
+    assert np.abs(kc - O.bf16_to_f32(orc.kc[:, 7:7 + M])).max() < 0.05
+
+
+def test_tiny_tree_verify_mask_depth_slots():
+    """A branching tree (26 nodes, depth 5, branching 4-2-2-1-1 pruned): mask, RoPE depth and slot semantics."""
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0)
+    orc, eng = O.OracleModel(cfg, P, 128), DecodeEngine(cfg, _cuda(P), max_seq=128)
+    _prefix(orc, eng, [7, 7, 7, 100, 2000])
+    from flint_b200.tree import static_tree
+    parent, depth = static_tree(26)
+    amask = O.tree_mask(parent)
+    toks = torch.randint(0, cfg.vocab_size, (26,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref_lg, _ = orc.verify(toks, 5, np.asarray(depth, np.int32), amask)
+    lg, _ = eng.verify(toks, 5, depth, torch.from_numpy(amask))
+    eng.check()
+    lg = lg.cpu().numpy()
+    assert np.abs(lg - ref_lg).max() < _tol(ref_lg)
+    assert _argmax_ok(lg, ref_lg)
+
+
+def test_verify_chain_equals_sequential_decode_on_device():
+    """The reference's own check of its verify kernel (reference: bench/verify_mega_test.py:43-59), on this library:
+    verify(M, chain) against M sequential decode launches."""
+    cfg = ModelArgs.from_name("tiny")
+    W = _cuda(packing.synth_packed(cfg, 0))
+    a, b = DecodeEngine(cfg, W, max_seq=64), DecodeEngine(cfg, W, max_seq=64)
+    pre = [11, 22, 33]
+    for p, t in enumerate(pre):
+        a.decode(t, p, want_logits=False)
+        b.decode(t, p, want_logits=False)
+    toks = [5, 17, 99, 1024, 7, 4000, 321, 12]
+    seq = torch.stack([a.decode(t, 3 + i).clone() for i, t in enumerate(toks)])
+    lg, _ = b.verify(toks, 3)
+    b.check()
+    rel = ((seq - lg).norm(dim=1) / seq.norm(dim=1)).max().item()
+    assert rel < 0.02 and _argmax_ok(lg.cpu().numpy(), seq.cpu().numpy()), rel
+
+
+def test_reference_shaped_verify_launch_and_kv_move():
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0)
+    W = _cuda(P)
+    orc = O.OracleModel(cfg, P, 64)
+    kc = torch.zeros(cfg.n_layer, 64, cfg.n_local_heads, cfg.head_dim, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    toks = [9, 8, 7, 6]
+    h = (W["embed"][torch.tensor(toks, device="cuda")].float() * cfg.embedding_multiplier).to(torch.bfloat16)
+    depth = torch.arange(4, dtype=torch.int32, device="cuda")
+    amask = torch.tril(torch.ones(4, 4, dtype=torch.uint8, device="cuda"))
+    lg, ft = verify_mega_launch(W["qkv_q"], W["qkv_s"], W["o_q"], W["o_s"], W["n1"], W["gu_q"], W["gu_s"], W["d_q"],
+                                W["d_s"], W["n2"], W["nf"], W["lm_q"], W["lm_s"], h, kc, vc, depth, amask, 0, 4,
+                                cfg.attn_scale, cfg.rope_base, cfg.residual_multiplier, cfg.logits_scaling)
+    ref, _ = orc.verify(toks, 0)
+    assert np.abs(lg.cpu().numpy() - ref).max() < _tol(ref)
+    assert tuple(ft.shape) == (4, cfg.dim) and ft.dtype == torch.bfloat16
+    # KV surgery: accepted nodes 2, 3 move to slots 1, 2 (reference: spec_tree.py:126-128)
+    from flint_b200.engine import _engines
+    eng = next(iter(_engines.values())) if len(_engines) == 1 else [e for e in _engines.values() if e.kc is kc][0]
+    before = kc.clone()
+    eng.kv_move([2, 3], [1, 2])
+    torch.cuda.synchronize()
+    assert torch.equal(kc[:, 1], before[:, 2]) and torch.equal(kc[:, 2], before[:, 3]) and torch.equal(kc[:, 3], before[:, 3])
+
+
+def test_verify_bad_m_is_an_error():
+    cfg = ModelArgs.from_name("tiny")
+    eng = DecodeEngine(cfg, _cuda(packing.synth_packed(cfg, 0)), max_seq=128)
+    with pytest.raises(_lib.FlintError) as ei:
+        eng.verify(list(range(65)), 0)
+    assert ei.value.code == _lib.FB_ERR_RANGE
+    with pytest.raises(_lib.FlintError):
+        eng.verify(list(range(20)), 120)          # pos + M > max_seq
+
+
+@pytest.mark.parametrize("M", [16, 26, 64])
+def test_granite3b_shape_verify_two_layers(M):
+    """Full-size matrices (d 2560, heads of 80, FFN 8192, vocab 49160), 2 layers, the static EAGLE trees of 16 / 26 / 64
+    nodes over a 96-token cache."""
+    from flint_b200.tree import static_tree
+    cfg = ModelArgs.from_name("granite-3b-class")
+    cfg.n_layer = 2
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    orc, eng = O.OracleModel(cfg, P, 256), DecodeEngine(cfg, W, max_seq=256)
+    gen = torch.Generator().manual_seed(3)
+    pre = torch.randint(0, cfg.vocab_size, (24,), generator=gen).tolist()
+    _prefix(orc, eng, pre)
+    parent, depth = static_tree(M)
+    amask = O.tree_mask(parent)
+    toks = torch.randint(0, cfg.vocab_size, (M,), generator=gen).tolist()
+    ref_lg, _ = orc.verify(toks, len(pre), np.asarray(depth, np.int32), amask)
+    lg, _ = eng.verify(toks, len(pre), depth, torch.from_numpy(amask))
+    eng.check()
+    lg = lg.cpu().numpy()
+    # full-size matrices: the reference's own criterion for its verify kernel, per token row
+    # (rel-L2 < 0.02 and equal arg-max, reference: bench/verify_mega_test.py:54-56); near-ties may swap
+    worst = max(float(np.linalg.norm(lg[m] - ref_lg[m]) / np.linalg.norm(ref_lg[m])) for m in range(M))
+    assert worst < 0.02, worst
+    assert _argmax_ok(lg, ref_lg)
