@@ -52,6 +52,10 @@ _PROTOS = {
     "fb_query": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Caps)]),
     "fb_ctx_create": (ctypes.c_int, [ctypes.POINTER(ModelDesc), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]),
     "fb_ctx_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "fb_ctx_create_tp": (ctypes.c_int, [ctypes.POINTER(ModelDesc), ctypes.c_int, ctypes.c_int32, ctypes.c_int32,
+                                        ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]),
+    "fb_tp_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_tp_connect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]),
     "fb_last_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Status)]),
     "fb_bind_weights": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(WeightPtrs), ctypes.c_void_p]),
     "fb_bind_kv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]),

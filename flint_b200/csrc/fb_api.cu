@@ -34,6 +34,10 @@ struct fb_ctx {
   unsigned* cnt;
   uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
   unsigned tag_base;
+  int tp_size, tp_rank, vocab_base, ko;                             // tensor parallelism (1 GPU: tp_size 1, ko = dim)
+  uint64_t* inbox;                                                  // [2][tp][dim] partial words + [tp][2] candidates
+  uint64_t* peer_inbox[8];
+  bool peers_open[8];
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   int max_fly;
   int version;                                                      // 2: data-flow kernel (default), 1: grid-barrier kernel
@@ -44,22 +48,31 @@ namespace {
 typedef void (*decode_fn_t)(const DecodeParams);
 
 struct KernelEntry {
-  int dim, ffn, head_dim, rgqa, hz;
-  const void* fn;     // grid-barrier kernel
+  int dim, ko, ffn, head_dim, rgqa, hz;
+  const void* fn;     // grid-barrier kernel (single-GPU shapes only)
   const void* fn2;    // data-flow kernel
 };
 
 #define FB_DECODE_ENTRY(KD, KF, HD, R)                                                      \
-  {KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>,                  \
-   (const void*)decode_mega2<KD, KF, HD, R, false>},                                         \
-  {KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>,                   \
-   (const void*)decode_mega2<KD, KF, HD, R, true>}
+  {KD::K, KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>,           \
+   (const void*)decode_mega2<KD, KD, KF, HD, R, false>},                                     \
+  {KD::K, KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>,            \
+   (const void*)decode_mega2<KD, KD, KF, HD, R, true>}
+// a tensor-parallel rank: O projection over this rank's heads (KO columns), FFN slice of KF columns
+#define FB_DECODE_TP_ENTRY(KD, KO, KF, HD, R)                                               \
+  {KD::K, KO::K, KF::K, HD, R, 0, nullptr, (const void*)decode_mega2<KD, KO, KF, HD, R, false>}, \
+  {KD::K, KO::K, KF::K, HD, R, 1, nullptr, (const void*)decode_mega2<KD, KO, KF, HD, R, true>}
 
 const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(K512, K1408, 64, 4),      // tiny test decoder
     FB_DECODE_ENTRY(K2560, K8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
     FB_DECODE_ENTRY(K2560, K8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
     FB_DECODE_ENTRY(K4096, K14336, 128, 4),   // 8B-class
+    FB_DECODE_TP_ENTRY(K2560, K1280, K4096, 80, 4),    // 3B-class over 2 GPUs
+    FB_DECODE_TP_ENTRY(K2560, K640, K2048, 80, 4),     // 3B-class over 4 GPUs
+    FB_DECODE_TP_ENTRY(K4096, K2048, K7168, 128, 4),   // 8B-class over 2 GPUs
+    FB_DECODE_TP_ENTRY(K4096, K1024, K3584, 128, 4),   // 8B-class over 4 GPUs
+    FB_DECODE_TP_ENTRY(K4096, K512, K1792, 128, 4),    // 8B-class over 8 GPUs
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
 
@@ -67,8 +80,8 @@ int find_kernel(const fb_model_desc& d) {
   if (d.n_kv_head <= 0 || d.n_head % d.n_kv_head) return -1;
   for (int i = 0; i < kNumDecodeKernels; i++) {
     const KernelEntry& e = kDecodeKernels[i];
-    if (e.dim == d.dim && e.ffn == d.ffn && e.head_dim == d.head_dim && e.rgqa == d.n_head / d.n_kv_head &&
-        e.hz == (d.has_zeros ? 1 : 0))
+    if (e.dim == d.dim && e.ko == d.n_head * d.head_dim && e.ffn == d.ffn && e.head_dim == d.head_dim &&
+        e.rgqa == d.n_head / d.n_kv_head && e.hz == (d.has_zeros ? 1 : 0))
       return i;
   }
   return -1;
@@ -197,10 +210,17 @@ int fb_query(int device, fb_caps* out) {
 }
 
 int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
+  return fb_ctx_create_tp(desc, device, 0, 1, 0, out);
+}
+
+int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int32_t tp_size, int32_t vocab_base,
+                     fb_ctx** out) {
   if (!desc || !out) return FB_ERR_ARG;
   *out = nullptr;
   const fb_model_desc& d = *desc;
-  if (d.n_layer <= 0 || d.vocab <= 0 || d.dim % 128 || d.ffn % 128 || d.n_head * d.head_dim != d.dim) return FB_ERR_SHAPE;
+  if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return FB_ERR_ARG;
+  if (d.n_layer <= 0 || d.vocab <= 0 || d.dim % 128 || d.ffn % 128 || (d.n_head * d.head_dim) % 128) return FB_ERR_SHAPE;
+  if (tp_size == 1 && d.n_head * d.head_dim != d.dim) return FB_ERR_SHAPE;
   const int kid = find_kernel(d);
   if (kid < 0) return FB_ERR_SHAPE;
   DeviceGuard g(device);
@@ -219,6 +239,7 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   c->spin_limit = 4000000u;
   c->version = 2;
   c->max_fly = 4;
+  c->tp_size = tp_size; c->tp_rank = tp_rank; c->vocab_base = vocab_base; c->ko = d.n_head * d.head_dim;
   c->tag_base = 8;
   c->maxchunks = c->sm_count / d.n_kv_head;
   if (c->maxchunks < 1) c->maxchunks = 1;
@@ -228,7 +249,7 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
     if (c->maxchunks > kScratchBytes / wpc_bytes) c->maxchunks = kScratchBytes / wpc_bytes;
   }
   // result buffer of a CTA must hold its rows of the widest phase
-  {
+  if (tp_size == 1) {
     const int G = c->sm_count;
     const int ksD = d.dim == 4096 ? 2 : 1;
     const long long lm_rows = ((long long)d.vocab + G - 1) / G + 1, gu_rows = (2LL * d.ffn + G - 1) / G + 2;
@@ -249,6 +270,12 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
   A(dmalloc(&c->cand_idx, 4 * (size_t)c->sm_count));
   A(dmalloc(&c->bar_ctr, 256));
   A(dmalloc(&c->status, sizeof(DevStatus)));
+  {
+    const size_t inbox_words = (size_t)2 * tp_size * d.dim + 2 * (size_t)tp_size + 16;
+    A(dmalloc(&c->inbox, inbox_words * 8));
+    if (e == cudaSuccess) A(cudaMemset(c->inbox, 0, inbox_words * 8));
+    c->peer_inbox[tp_rank] = c->inbox;
+  }
   const size_t hp = d.head_dim / 2;
   const size_t wpc = (size_t)c->rgqa * d.head_dim + 2 * c->rgqa;
   const size_t ll_words[8] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
@@ -279,7 +306,8 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
     A(cudaMemcpy(c->invf, invf, sizeof(float) * (d.head_dim / 2), cudaMemcpyHostToDevice));
     A(cudaMemset(c->bar_ctr, 0, 256));
     A(cudaMemset(c->status, 0, sizeof(DevStatus)));
-    A(cudaFuncSetAttribute(kDecodeKernels[kid].fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    if (kDecodeKernels[kid].fn)
+      A(cudaFuncSetAttribute(kDecodeKernels[kid].fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     A(cudaFuncSetAttribute(kDecodeKernels[kid].fn2, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   }
   if (e != cudaSuccess) {
@@ -293,9 +321,12 @@ int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out) {
 int fb_ctx_destroy(fb_ctx* c) {
   if (!c) return FB_ERR_ARG;
   DeviceGuard g(c->device);
+  for (int p = 0; p < 8; p++)
+    if (c->peers_open[p] && c->peer_inbox[p]) cudaIpcCloseMemHandle(c->peer_inbox[p]);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
                   c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll,
-                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact};
+                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact,
+                  c->inbox};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -307,7 +338,12 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 4) { if (value < 1 || value > kStages) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
-  if (what == 3) { if (value != 1 && value != 2) return FB_ERR_ARG; c->version = (int)value; return FB_OK; }
+  if (what == 3) {
+    if (value != 1 && value != 2) return FB_ERR_ARG;
+    if (value == 1 && (c->tp_size > 1 || !kDecodeKernels[c->kernel_id].fn)) return FB_ERR_ARG;
+    c->version = (int)value;
+    return FB_OK;
+  }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
 }
@@ -436,7 +472,7 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   if (!c->weights_bound || !c->kc) return FB_ERR_STATE;
   const fb_model_desc& d = c->d;
   if (pos < 0 || pos >= c->max_seq) return FB_ERR_RANGE;
-  if (!d_token && !d_h && (token < 0 || token >= d.vocab)) return FB_ERR_RANGE;
+  if (!d_token && !d_h && (token < 0 || (c->tp_size == 1 && token >= d.vocab))) return FB_ERR_RANGE;
   if (!d_h && !c->embed) return FB_ERR_STATE;
   if (d_h && ((uintptr_t)d_h & 1)) return FB_ERR_ARG;
   DeviceGuard g(c->device);
@@ -460,6 +496,11 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
     Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
     Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
     Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly;
+    Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox;
+    for (int p = 0; p < c->tp_size; p++) {
+      if (!c->peer_inbox[p]) return FB_ERR_STATE;       /* fb_tp_connect has not been called */
+      Q.peer_inbox[p] = c->peer_inbox[p];
+    }
     void* args2[] = {&Q};
     FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn2, dim3(c->sm_count), dim3(kThreads), args2,
                                            (size_t)kSmemBytes, (cudaStream_t)stream));
@@ -536,6 +577,31 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, HD, st));
   }
   FB_CUDA(c, cudaGetLastError());
+  return FB_OK;
+}
+
+int fb_tp_export(fb_ctx* c, void* handle_out64) {
+  if (!c || !handle_out64) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  cudaIpcMemHandle_t h;
+  FB_CUDA(c, cudaIpcGetMemHandle(&h, c->inbox));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle_out64, &h, 64);
+  return FB_OK;
+}
+
+int fb_tp_connect(fb_ctx* c, const void* handles, int32_t n) {
+  if (!c || !handles || n != c->tp_size) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  for (int p = 0; p < n; p++) {
+    if (p == c->tp_rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char*)handles + 64 * p, 64);
+    void* ptr = nullptr;
+    FB_CUDA(c, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peer_inbox[p] = (uint64_t*)ptr;
+    c->peers_open[p] = true;
+  }
   return FB_OK;
 }
 

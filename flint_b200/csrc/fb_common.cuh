@@ -208,6 +208,14 @@ using K1408S = KCfg<1408, 1, 2, 3, 2, 8>;
 using K2560S = KCfg<2560, 1, 2, 5, 2, 8>;
 using K4096S = KCfg<4096, 2, 4, 2, 2, 4>;
 using K8192S = KCfg<8192, 4, 4, 2, 2, 2>;
+// K values that only appear under tensor parallelism (a rank's slice of the attention output or of the FFN)
+using K640 = KCfg<640, 1, 2, 2, 2, 16>;
+using K1024 = KCfg<1024, 1, 4, 1, 2, 16>;
+using K1280 = KCfg<1280, 1, 2, 3, 2, 8>;
+using K1792 = KCfg<1792, 1, 4, 2, 2, 8>;
+using K2048 = KCfg<2048, 1, 4, 2, 2, 8>;
+using K3584 = KCfg<3584, 2, 4, 2, 2, 4>;
+using K7168 = KCfg<7168, 4, 4, 2, 2, 2>;
 template <class KC> struct SmallOf { using type = KC; };
 template <> struct SmallOf<K512> { using type = K512S; };
 template <> struct SmallOf<K1408> { using type = K1408S; };

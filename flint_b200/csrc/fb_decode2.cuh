@@ -28,6 +28,27 @@ __device__ __forceinline__ uint64_t ll_load1(const uint64_t* p) {
   return a;
 }
 
+// words exchanged between GPUs (peer stores over NVLink, polled in local memory): system scope
+__device__ __forceinline__ void ll_store_sys(uint64_t* p, uint32_t payload, uint32_t tag) {
+  const uint64_t v = ((uint64_t)tag << 32) | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ll_load_sys(const uint64_t* p) {
+  uint64_t a;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+// bounded poll of one word written by another GPU; returns the payload (0 after a failure)
+__device__ __forceinline__ uint32_t ll_poll_sys(const uint64_t* p, uint32_t tag, const WaitCtl& wc, int layer) {
+  for (unsigned spin = 0;; spin++) {
+    const uint64_t v = ll_load_sys(p);
+    if ((uint32_t)(v >> 32) == tag) return (uint32_t)v;
+    if (*wc.s_abort) return 0;
+    if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; return 0; }
+    if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, -3); return 0; }
+  }
+}
+
 // Poll `nwords` (even, 16-byte aligned base) tagged words into 32-bit payloads dst[0..nwords). Threads
 // tid, tid+nthreads, ... each own word pairs; all of a thread's loads are issued before any is checked.
 template <int MAXP>
@@ -477,13 +498,18 @@ struct Decode2Params {
   float eps, attn_scale, resid, emb_mult, logits_scaling;
   long long* prof;
   unsigned max_fly;
+  // tensor parallelism: this GPU holds a slice of every matrix (heads, FFN columns, vocabulary rows); the partial sums
+  // of the K-sharded O and down projections are exchanged by peer stores into every rank's inbox
+  int32_t tp_size, tp_rank, vocab_base;
+  uint64_t* inbox;            // local: [2 parities][tp_size][dim] tagged fp32 partials, then [tp_size][2] arg-max candidates
+  uint64_t* peer_inbox[8];    // the same buffer of every rank (peer-mapped); own entry = inbox
 };
 
 // tags: phase ids inside a layer
 enum { PH_QKV = 1, PH_ATT = 2, PH_O = 3, PH_GU = 4, PH_DOWN = 5, PH_LM = 6, PH_PART = 7 };
 __device__ __forceinline__ uint32_t mk_tag(unsigned base, int layer, int ph) { return base + (unsigned)(layer * 8 + ph); }
 
-template <class KD, class KF, int HD, int R, bool HZ>
+template <class KD, class KO, class KF, int HD, int R, bool HZ>
 __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params P) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem sm = carve_smem(smem_raw);
@@ -498,11 +524,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
   WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
   Pipe pipe{sm.stages, sm.full, sm.empty, 0u, P.max_fly};
   constexpr int HP = HD / 2;
-  using KDS = typename SmallOf<KD>::type;     // QKV and O: few rows per CTA
+  using KDS = typename SmallOf<KD>::type;     // QKV: few rows per CTA
+  using KOS = typename SmallOf<KO>::type;     // O projection (K = this rank's attention output width)
   using KFS = typename SmallOf<KF>::type;     // down projection
   const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
   const int QKV = (P.n_head + 2 * P.n_kv) * HD;
-  const int recD = rec_bytes_of(KD::K, HZ), recF = rec_bytes_of(KF::K, HZ);
+  const int recD = rec_bytes_of(KD::K, HZ), recO = rec_bytes_of(KO::K, HZ), recF = rec_bytes_of(KF::K, HZ);
+  const int N = P.tp_size, me = P.tp_rank;
   int q0, q1, o0, o1, g0, g1, l0, l1;
   cta_rows(QKV, 2, b, G, q0, q1);
   cta_rows(D, 2, b, G, o0, o1);          // the same rows of h belong to this CTA in the O and the down phase
@@ -514,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       bool ok = true;
       for (int l = 0; l < L && ok; l++) {
         ok = produce_rows(pipe, P.w_qkv + ((size_t)l * QKV + q0) * recD, q1 - q0, KDS::TILE_ROWS, recD, wc, l) &&
-             produce_rows(pipe, P.w_o + ((size_t)l * D + o0) * recD, o1 - o0, KDS::TILE_ROWS, recD, wc, l) &&
+             produce_rows(pipe, P.w_o + ((size_t)l * D + o0) * recO, o1 - o0, KOS::TILE_ROWS, recO, wc, l) &&
              produce_rows(pipe, P.w_gu + ((size_t)l * 2 * FF + g0) * recD, g1 - g0, KD::TILE_ROWS, recD, wc, l) &&
              produce_rows(pipe, P.w_d + ((size_t)l * D + o0) * recF, o1 - o0, KFS::TILE_ROWS, recF, wc, l);
       }
@@ -528,12 +556,56 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     float* hown = sm.hown;                                      // this CTA's rows of the residual stream (exact bf16 values)
     int* s_done = sm.misc + 20;                                 // warps of this CTA that finished the current producing phase
     if (tid_c == 0) *s_done = 0;
+    float* ypart = sm.hown + kMaxOwnRows;                       // tensor parallel: this rank's partial sums of its rows
+    constexpr int MAXP_O = (KO::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    // O / down epilogue. One GPU: h = bf16(h + y * resid) at once. Tensor parallel: y is a partial sum over this
+    // rank's K slice: keep it, push it to every peer's inbox, finish in resid_finish once all rows are done.
+    auto resid_epi = [&](int row0, float c, int nvalid, uint32_t tag, int par) {
+      const int r = row0 + (lane >> 3);
+      if (N > 1) {
+        if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+          ypart[r] = c;
+          for (int p = 0; p < N; p++)
+            if (p != me) ll_store_sys(P.peer_inbox[p] + ((size_t)(par * N + me)) * D + o0 + r, __float_as_uint(c), tag);
+        }
+        return;
+      }
+      float hn = 0.f;
+      if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+        hn = rbf(hown[r] + c * P.resid);
+        hown[r] = hn;
+      }
+      const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
+      if ((lane & 15) == 0 && (lane >> 3) < nvalid)
+        ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tag);
+    };
+    // tensor parallel only: sum the partials of all ranks in rank order (identical on every rank), update h, publish
+    auto resid_finish = [&](uint32_t tag, int par, int layer) {
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      for (int pr = tid_c; pr < (o1 - o0) / 2; pr += kConsumerThreads) {
+        float tot0 = 0.f, tot1 = 0.f;
+        for (int s2 = 0; s2 < N; s2++) {
+          if (s2 == me) {
+            tot0 += ypart[2 * pr]; tot1 += ypart[2 * pr + 1];
+          } else {
+            const uint64_t* src = P.inbox + ((size_t)(par * N + s2)) * D + o0 + 2 * pr;
+            tot0 += __uint_as_float(ll_poll_sys(src, tag, wc, layer));
+            tot1 += __uint_as_float(ll_poll_sys(src + 1, tag, wc, layer));
+          }
+        }
+        const float h0 = rbf(hown[2 * pr] + tot0 * P.resid), h1 = rbf(hown[2 * pr + 1] + tot1 * P.resid);
+        hown[2 * pr] = h0; hown[2 * pr + 1] = h1;
+        ll_store(P.h_ll + ((o0 >> 1) + pr), (uint32_t)f2bf(h0) | ((uint32_t)f2bf(h1) << 16), tag);
+      }
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      if (tid_c == 0) st_relaxed_u32(P.h_flags + b, tag);
+    };
     constexpr int MAXP_D = (KD::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
     constexpr int MAXP_F = (KF::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
     // ---- residual stream at layer 0: every CTA reads the embedding row (or the caller's h) itself ----
     {
       int tok = P.d_token ? (int)ld_cg_u32(P.d_token) : P.token;
-      if ((unsigned)tok >= (unsigned)V) {
+      if ((unsigned)tok >= (unsigned)(V * N)) {                 // V is this rank's slice of the vocabulary
         tok = 0;
         if (tid_c == 0 && b == 0) atomicCAS(&P.status->code, 0, 6 /*FB_ERR_RANGE*/);
       }
@@ -610,22 +682,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       }
       FB_STAMP(3);
       // ================= O projection + residual =================
-      stage_plain_ll<MAXP_D>(P.ao_ll, P.ao_flags, P.n_kv, tg_att, D, sm.x_s, tid_c, wc, l);
-      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      FB_STAMP(4);
-      consume_rows_epi<KDS, HZ>(pipe, o1 - o0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
-        const int r = row0 + (lane >> 3);
-        float hn = 0.f;
-        if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
-          hn = rbf(hown[r] + c * P.resid);
-          hown[r] = hn;
-        }
-        const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
-        if ((lane & 15) == 0 && (lane >> 3) < nvalid)
-          ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tg_o);
-      });
-      post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
+      {
+        XRegs<KO> xo;
+        stage_plain_ll<MAXP_O>(P.ao_ll, P.ao_flags, P.n_kv, tg_att, KO::K, sm.x_s, tid_c, wc, l);
+        load_x_slice<KO>(sm.x_s, wg % KO::KS, lane, xo);
+        named_bar_sync(kBarConsumers, kConsumerThreads);
+        FB_STAMP(4);
+        consume_rows_epi<KOS, HZ>(pipe, o1 - o0, xo, part_s, cw, lane, wc, l,
+                                  [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_o, 0); });
+        if (N > 1) resid_finish(tg_o, 0, l);
+        else post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
+      }
       FB_STAMP(5);
       // ================= gate/up + SwiGLU =================
       stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c, wc, l, false);
@@ -654,18 +721,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
         load_x_slice<KF>(sm.x_s, wg % KF::KS, lane, xf);
         named_bar_sync(kBarConsumers, kConsumerThreads);
         FB_STAMP(8);
-        consume_rows_epi<KFS, HZ>(pipe, o1 - o0, xf, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
-          const int r = row0 + (lane >> 3);
-          float hn = 0.f;
-          if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
-            hn = rbf(hown[r] + c * P.resid);
-            hown[r] = hn;
-          }
-          const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
-          if ((lane & 15) == 0 && (lane >> 3) < nvalid)
-            ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tg_dn);
-        });
-        post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
+        consume_rows_epi<KFS, HZ>(pipe, o1 - o0, xf, part_s, cw, lane, wc, l,
+                                  [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_dn, 1); });
+        if (N > 1) resid_finish(tg_dn, 1, l);
+        else post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       }
       FB_STAMP(9);
     }
@@ -679,7 +738,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     int bi = 0x7fffffff;
     consume_rows_epi<KD, HZ>(pipe, l1 - l0, xd, part_s, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
       if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
-        const int row = l0 + row0 + (lane >> 3);
+        const int row = P.vocab_base + l0 + row0 + (lane >> 3);     // index in the full vocabulary
         const float y = c / P.logits_scaling;
         if (P.d_logits) P.d_logits[row] = y;
         if (y > bv || (y == bv && row < bi)) { bv = y; bi = row; }
@@ -718,6 +777,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
           const float ov = __shfl_xor_sync(0xffffffffu, v, o);
           const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
           if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+        }
+        if (N > 1 && lane == 0) {
+          // every rank holds a slice of the vocabulary: exchange the N (value, index) candidates, reduce in rank order
+          uint64_t* mine = P.inbox + (size_t)2 * N * D;
+          for (int p = 0; p < N; p++) {
+            uint64_t* dst = (p == me ? mine : P.peer_inbox[p] + (size_t)2 * N * D) + 2 * me;
+            ll_store_sys(dst, __float_as_uint(v), tg_lm);
+            ll_store_sys(dst + 1, (uint32_t)ix, tg_lm);
+          }
+          v = -INFINITY; ix = 0x7fffffff;
+          for (int s2 = 0; s2 < N; s2++) {
+            const float ov = __uint_as_float(ll_poll_sys(mine + 2 * s2, tg_lm, wc, L));
+            const int oi = (int)ll_poll_sys(mine + 2 * s2 + 1, tg_lm, wc, L);
+            if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+          }
         }
         if (lane == 0 && P.d_next) *P.d_next = ix;
       }

@@ -35,7 +35,8 @@ class DecodeEngine:
 
     def __init__(self, cfg: ModelArgs, packed: Dict[str, torch.Tensor], max_seq: Optional[int] = None,
                  device: Optional[torch.device] = None, kc: Optional[torch.Tensor] = None,
-                 vc: Optional[torch.Tensor] = None):
+                 vc: Optional[torch.Tensor] = None, tp_rank: int = 0, tp_size: int = 1):
+        """`packed` holds this rank's slice when tp_size > 1 (flint_b200.tp.shard_packed); cfg is the full model."""
         self.lib = _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("flint_b200 needs a CUDA device (sm_100a); there is no CPU path")
@@ -46,12 +47,20 @@ class DecodeEngine:
         self.dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.has_zeros = "qkv_z" in packed
         self.max_seq = int(max_seq or cfg.block_size)
-        d = _lib.ModelDesc(cfg.n_layer, cfg.dim, cfg.n_head, cfg.n_local_heads, cfg.head_dim, cfg.ffn_padded,
-                           cfg.vocab_size, int(self.has_zeros), cfg.norm_eps, float(cfg.rope_base),
-                           float(cfg.attn_scale), float(cfg.residual_multiplier), float(cfg.embedding_multiplier),
-                           float(cfg.logits_scaling))
+        self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
+        for what, n in (("query heads", cfg.n_head), ("kv heads", cfg.n_local_heads), ("FFN width / 128", cfg.ffn_padded // 128),
+                        ("vocabulary", cfg.vocab_size)):
+            if n % self.tp_size:
+                raise ValueError(f"{what} ({n}) does not divide over {self.tp_size} ranks")
+        self.n_kv_local = cfg.n_local_heads // self.tp_size
+        self.vocab_local = cfg.vocab_size // self.tp_size
+        d = _lib.ModelDesc(cfg.n_layer, cfg.dim, cfg.n_head // self.tp_size, self.n_kv_local, cfg.head_dim,
+                           cfg.ffn_padded // self.tp_size, self.vocab_local, int(self.has_zeros), cfg.norm_eps,
+                           float(cfg.rope_base), float(cfg.attn_scale), float(cfg.residual_multiplier),
+                           float(cfg.embedding_multiplier), float(cfg.logits_scaling))
         self._ctx = ctypes.c_void_p()
-        _lib.check(self.lib.fb_ctx_create(ctypes.byref(d), self.dev_index, ctypes.byref(self._ctx)), "fb_ctx_create")
+        _lib.check(self.lib.fb_ctx_create_tp(ctypes.byref(d), self.dev_index, self.tp_rank, self.tp_size,
+                                             self.tp_rank * self.vocab_local, ctypes.byref(self._ctx)), "fb_ctx_create")
         # keep-alive: the norms and the embedding table stay caller-side tensors
         self._keep = {k: packed[k].contiguous() for k in ("n1", "n2", "nf") if k in packed}
         if "embed" in packed and packed["embed"] is not None:
@@ -65,7 +74,7 @@ class DecodeEngine:
                 setattr(w, name, t.data_ptr())
         _lib.check(self.lib.fb_bind_weights(self._ctx, ctypes.byref(w), _stream_ptr(self.device)), "fb_bind_weights")
         torch.cuda.synchronize(self.device)
-        shape = (cfg.n_layer, self.max_seq, cfg.n_local_heads, cfg.head_dim)
+        shape = (cfg.n_layer, self.max_seq, self.n_kv_local, cfg.head_dim)
         self.kc = kc if kc is not None else torch.zeros(shape, dtype=torch.bfloat16, device=self.device)
         self.vc = vc if vc is not None else torch.zeros(shape, dtype=torch.bfloat16, device=self.device)
         self.bind_kv(self.kc, self.vc)
@@ -74,12 +83,24 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ plumbing
     def bind_kv(self, kc: torch.Tensor, vc: torch.Tensor):
-        want = (self.cfg.n_layer, kc.shape[1], self.cfg.n_local_heads, self.cfg.head_dim)
+        want = (self.cfg.n_layer, kc.shape[1], self.n_kv_local, self.cfg.head_dim)
         for t in (kc, vc):
             if tuple(t.shape) != want or t.dtype != torch.bfloat16 or not t.is_contiguous() or t.device != self.device:
                 raise ValueError(f"KV cache must be contiguous bf16 {want} on {self.device}")
         self.kc, self.vc, self.max_seq = kc, vc, kc.shape[1]
         _lib.check(self.lib.fb_bind_kv(self._ctx, _ptr(kc), _ptr(vc), self.max_seq), "fb_bind_kv")
+
+    # ------------------------------------------------------------------ tensor parallel wiring
+    def tp_export(self) -> bytes:
+        """64-byte IPC handle of this rank's inbox; exchange it with every other rank (any transport)."""
+        buf = ctypes.create_string_buffer(64)
+        _lib.check(self.lib.fb_tp_export(self._ctx, buf), "fb_tp_export")
+        return buf.raw
+
+    def tp_connect(self, handles):
+        """handles[p] = rank p's exported handle."""
+        blob = b"".join(handles)
+        _lib.check(self.lib.fb_tp_connect(self._ctx, ctypes.c_char_p(blob), len(handles)), "fb_tp_connect")
 
     def set_option(self, what: int, value: int):
         _lib.check(self.lib.fb_set_option(self._ctx, what, value), "fb_set_option")

@@ -73,6 +73,20 @@ typedef struct fb_status {
  * allocations and occupancy queries of the reference launcher (reference: kernels/megakernel_decode.cu:213-223). */
 int fb_ctx_create(const fb_model_desc* desc, int device, fb_ctx** out);
 int fb_ctx_destroy(fb_ctx* ctx);
+
+/* Tensor parallelism over 2/4/8 GPUs of one box, one process per GPU (no counterpart in the reference: its
+ * generate.py imports a `tp` module that the repository does not contain, reference: engine/generate.py:238-241).
+ * `desc` describes THIS RANK'S slice: n_head / n_kv_head = local heads, ffn = local FFN columns, vocab = local
+ * vocabulary rows, dim = the full model width. vocab_base = first vocabulary row of this rank. Every rank exports the
+ * IPC handle of its inbox, the host side exchanges the handles (any transport), and every rank connects to all of
+ * them before the first fb_decode. The partial sums of the K-sharded O and down projections and the arg-max
+ * candidates then travel by peer stores over NVLink inside the kernel; no NCCL launch is involved.
+ *   fb_tp_export : 64-byte cudaIpcMemHandle_t of this rank's inbox
+ *   fb_tp_connect: handles = n * 64 bytes, entry p = rank p's handle (the own entry is ignored) */
+int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int32_t tp_size, int32_t vocab_base,
+                     fb_ctx** out);
+int fb_tp_export(fb_ctx* ctx, void* handle_out64);
+int fb_tp_connect(fb_ctx* ctx, const void* handles, int32_t n);
 int fb_last_status(fb_ctx* ctx, fb_status* out);
 
 /* Re-lays the caller's int4 tensors out into the context's streaming layout (one pass on the GPU, once).
