@@ -423,6 +423,38 @@ int fb_gemv(const void* d_in, int32_t rows, int32_t k, int32_t has_zeros, int32_
   return e == 0 ? FB_OK : FB_ERR_CUDA;
 }
 
+// ---- GEMV for callers that must not allocate ----------------------------------------------------------------------
+// The streaming-layout copy of the matrix is the scratch of this path. Here it lives in one fixed array inside the
+// library image instead of a buffer from cudaMalloc: every GPU that loads the library carries these 9 MiB until the
+// process exits. `g_static_scratch` in HOST code is only a stand-in for the symbol, not a device address: the address
+// a kernel can use comes from cudaGetSymbolAddress, once per device, with that device current.
+constexpr size_t kStaticScratchBytes = (size_t)9 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static void* g_static_scratch_addr[64];      // per device ordinal, filled by the first call on that device
+
+int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t rows, int32_t k, const void* d_x, float* d_y,
+                   void* d_status, void* stream) {
+  if (!d_q || !d_s || !d_x || !d_y || !d_status || rows <= 0 || k <= 0 || k % 128) return FB_ERR_ARG;
+  const int hz = d_z != nullptr;
+  const size_t need = (size_t)rows * rec_bytes_of(k, hz);
+  if (need > kStaticScratchBytes) return FB_ERR_RANGE;       /* matrix larger than the built-in scratch: use fb_gemv */
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FB_ERR_CUDA;
+  if (!g_static_scratch_addr[dev]) {                          /* set-up, once per device, with that device current */
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return FB_ERR_CUDA;
+    g_static_scratch_addr[dev] = p;
+  }
+  void* scratch = g_static_scratch_addr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  /* the caller's status words must start at zero; the scratch itself needs no clearing: every byte of the rows*record
+     range that the GEMV reads is rewritten by the re-layout below (padding included) */
+  if (cudaMemsetAsync(d_status, 0, 32, st) != cudaSuccess) return FB_ERR_CUDA;
+  int rc = fb_repack(d_q, d_s, d_z, rows, k, 0, 0, 0, scratch, stream);
+  if (rc != FB_OK) return rc;
+  return fb_gemv(scratch, rows, k, hz, 0, 0, 0, d_x, d_y, d_status, stream);
+}
+
 int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   if (!c || !w) return FB_ERR_ARG;
   const fb_model_desc& d = c->d;

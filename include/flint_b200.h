@@ -140,6 +140,24 @@ int fb_dequant(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zer
 int fb_gemv(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
             int32_t order_rows, const void* d_x, float* d_y, void* d_status, void* stream);
 
+/* The same GEMV for callers that are not allowed to allocate device memory. This entry point has no counterpart in the
+ * reference. Who needs it: a host that hands this library a fixed device arena and forbids any further cudaMalloc
+ * (inference servers that pre-reserve all of HBM), and code that runs where an allocation would be an error or a stall,
+ * e.g. while a stream is being captured or inside a latency-critical loop. fb_gemv needs a caller-allocated copy of the
+ * matrix in the streaming layout; here that copy goes into ONE array built into the library (9 MiB, 256-byte aligned,
+ * held by every GPU that loads the library until the process exits), so nothing is allocated or freed, here or in any
+ * library this calls.
+ *   inputs   : d_q int32 [rows, k/8], d_s bf16 [rows, k/128], d_z bf16 [rows, k/128] or NULL (caller layout), d_x bf16 [k]
+ *   outputs  : d_y f32 [rows]; d_status int32[8] (cleared by this call; word 0 becomes FB_ERR_TIMEOUT if a wait ran out)
+ *   limit    : rows * (k/2 + 16-byte-padded k/64 [x2 with zeros]) <= 9 MiB, else FB_ERR_RANGE (nothing is launched);
+ *              k must be one of the widths fb_gemv supports, else FB_ERR_SHAPE
+ *   set-up   : the first call on a device resolves the array's device address; make that first call before any stream
+ *              capture begins on that device
+ *   sharing  : every call uses the same array and leaves its contents behind; two calls that overlap on the GPU
+ *              (different streams, or another thread) race on it — order them on one stream */
+int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t rows, int32_t k, const void* d_x, float* d_y,
+                   void* d_status, void* stream);
+
 /* Tuning / test knobs (no reference counterpart: the reference has no bounded waits and a fixed split).
  *   what 0: iteration limit of every device-side wait (default 4000000); a tiny value makes a launch give up
  *           with FB_ERR_TIMEOUT, which is how the time-out path is tested without hanging a GPU
