@@ -141,9 +141,11 @@ int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
 template <int MT, int KC, int EPI, int HD>
 cudaError_t launch_vgemm_kc(const VGemmParams& p, cudaStream_t st) {
   static bool configured = false;
-  constexpr int smem = v_gemm_smem<MT, KC>();
+  constexpr int smem_max = v_gemm_smem<MT, KC>(2 * 14336 / 128);   // widest supported K, scales and zeros
+  const int smem = v_gemm_smem<MT, KC>((p.K / 128) * (p.has_zeros ? 2 : 1));
+  if (smem > smem_max) return cudaErrorInvalidValue;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, KC, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, KC, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
     if (e != cudaSuccess) return e;
     configured = true;
   }
@@ -152,6 +154,7 @@ cudaError_t launch_vgemm_kc(const VGemmParams& p, cudaStream_t st) {
 }
 template <int MT, int EPI, int HD>
 cudaError_t launch_vgemm(const VGemmParams& p, cudaStream_t st) {
+  if (VCfg<MT>::KCMAX >= 512 && p.K % 512 == 0) return launch_vgemm_kc<MT, (VCfg<MT>::KCMAX >= 512 ? 512 : 256), EPI, HD>(p, st);
   return (p.K % 256 == 0) ? launch_vgemm_kc<MT, 256, EPI, HD>(p, st) : launch_vgemm_kc<MT, 128, EPI, HD>(p, st);
 }
 template <int MT, int EPI>

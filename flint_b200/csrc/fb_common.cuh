@@ -10,15 +10,14 @@ namespace fb {
 
 // ------------------------------------------------------------------------------------------------ constants
 #ifndef FB_CW
-#define FB_CW 12      // 12 consumers + 1 producer = 13 warps -> 4 per scheduler -> 128 registers per thread, no spills that matter;
-#endif                // 16 consumers (17 warps, 96 registers) streams GEMVs slightly faster but spills in the attention phase
+#define FB_CW 14      // 14 consumers + 1 producer = 15 warps -> at most 4 per scheduler -> 128 registers per thread; 14 also
+#endif                // divides the 28 four-row blocks a CTA gets of the gate/up matrix (3B-class) into exactly 2 rounds
 #ifndef FB_DOT
 #define FB_DOT 0      // 0: bf16 pairs + fma.rn.f32.bf16 (activations packed bf16 in registers)
 #endif                // 1: prmt -> fp32 weights + fma.rn.f32 (activations fp32 in registers)
 constexpr int kConsumerWarps = FB_CW;              // groups of 4 warps; group g consumes weight tiles t with t % kGroups == g
 constexpr int kWarpsPerGroup = 4;
 constexpr int kGroups = kConsumerWarps / kWarpsPerGroup;
-static_assert(kConsumerWarps % kWarpsPerGroup == 0, "consumer warps come in groups of 4");
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;    // + one producer warp (lane 0 issues the bulk copies)
 constexpr int kStages = 8;                         // ring depth: 8 x 22 KB = 176 KB of weights in flight per SM
@@ -26,7 +25,7 @@ constexpr int kStageBytes = 23040;              // largest tile: 3 rows of K=143
 constexpr int kScratchBytes = 40960;               // x staging (<= 14336 bf16) + per-phase results; attention merge area
 constexpr int kXBytes = 28672;
 constexpr int kResFloats = (kScratchBytes - kXBytes) / 4;   // 3072 row results per CTA per phase
-constexpr int kTailBytes = 2048;                   // mbarriers, flags, reduction scratch, slice partials, owned residual rows
+constexpr int kTailBytes = 4096;                   // mbarriers, flags, reduction scratch, slice partials, owned residual rows
 constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + kTailBytes;
 constexpr int kMaxOwnRows = 64;                    // rows of the residual stream one CTA may own
 

@@ -28,6 +28,9 @@ struct Smem {
   int* misc;           // 32 ints
   float* part;         // [groups][2][4 warps][4] slice partials of sliced-K phases
   float* hown;         // [kMaxOwnRows] this CTA's rows of the residual stream
+  float* qpart;        // [kStages][2 blocks][4 slices][4 rows] slice partials of the block-queue GEMV
+  int* tdone;          // [kStages] units finished per tile in flight
+  int* bcnt;           // [kStages][2] slices finished per block
 };
 
 __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
@@ -44,6 +47,9 @@ __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
   s.misc = reinterpret_cast<int*>(tail + 384);
   s.part = reinterpret_cast<float*>(tail + 512);
   s.hown = reinterpret_cast<float*>(tail + 1024);
+  s.qpart = reinterpret_cast<float*>(tail + 2048);
+  s.tdone = reinterpret_cast<int*>(tail + 3072);
+  s.bcnt = reinterpret_cast<int*>(tail + 3104);
   return s;
 }
 

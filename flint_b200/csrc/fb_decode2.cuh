@@ -194,6 +194,82 @@ __device__ __forceinline__ void consume_rows_epi(Pipe& p, int nrows, const XR& x
   p.it += ntiles;
 }
 
+// ------------------------------------------------------------------------------------------------ block-queue GEMV
+// The phase's rows are cut into blocks of RB rows (times KS column slices); warp w takes blocks w/KS, w/KS + NL, ...
+// of its fixed slice, in order, straight off the weight ring. There are no warp groups and no barriers: a tile's
+// slot goes back to the producer when its last unit finishes (shared-memory counter), and for sliced K the warp that
+// finishes the last slice of a block adds the partials and runs the epilogue. Every warp is busy until the phase ends,
+// which is what the latency of these small phases is made of.
+struct QueueState {
+  float* qpart;
+  int* tdone;
+  int* bcnt;
+};
+template <class KC, bool HZ, class XR, class Epi>
+__device__ __forceinline__ void consume_rows_q(Pipe& p, int nrows, const XR& x, const QueueState& q, int cw, int lane,
+                                               const WaitCtl& wc, int layer, Epi epi) {
+  constexpr int RB = KC::RB, TR = KC::TILE_ROWS, KS = KC::KS, BT = TR / RB;
+  static_assert(TR % RB == 0 && (KS == 1 || BT <= 2) && KS <= 4, "queue geometry");
+  constexpr int NL = kConsumerWarps / KS;            // block lanes; warps beyond NL*KS sit this phase out
+  const int rec = rec_bytes_of(KC::K, HZ);
+  const int ntiles = (nrows + TR - 1) / TR;
+  if (cw < NL * KS) {
+    const int slice = cw % KS;
+    const int nb = (nrows + RB - 1) / RB;
+    for (int gb = cw / KS; gb < nb; gb += NL) {
+      const int t = gb / BT, blk = gb % BT;
+      const uint32_t it = p.it + t;
+      const int s = it % kStages;
+      const bool ok = mbar_wait(&p.full[s], (it / kStages) & 1, wc, W_FULL, layer);
+      const int tr = min(TR, nrows - t * TR);
+      const int nvalid = min(RB, tr - blk * RB);
+      if (ok) {
+        const uint8_t* tile = p.stages + (size_t)s * kStageBytes;
+        int rows[RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) rows[r] = min(blk * RB + r, tr - 1) * rec;
+        float acc[RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) acc[r] = 0.f;
+        rowblock_dot<KC, HZ>(tile, rows, slice, lane, x, acc);
+        float c = reduce_rows<RB>(acc, lane);
+        if (KS == 1) {
+          epi(gb * RB, c, nvalid);
+        } else {
+          float* part = q.qpart + ((s * 2 + blk) * 4) * 4;       // [slice][row]
+          if ((lane & 7) == 0) part[slice * 4 + (lane >> 3)] = c;
+          __syncwarp();
+          int last = 0;
+          if (lane == 0) {
+            __threadfence_block();
+            const int old = atomicAdd(q.bcnt + s * 2 + blk, 1);
+            last = (old == KS - 1);
+            if (last) q.bcnt[s * 2 + blk] = 0;
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {                                            // every slice of this block is in: combine, epilogue
+            __threadfence_block();
+            c = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < KS; sl++) c += part[sl * 4 + (lane >> 3)];
+            epi(gb * RB, c, nvalid);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {                                         // last unit of the tile hands the slot back
+          const int units = ((tr + RB - 1) / RB) * KS;
+          const int old = atomicAdd(q.tdone + s, 1);
+          if (old == units - 1) {
+            q.tdone[s] = 0;
+            mbar_arrive(&p.empty[s]);
+          }
+        }
+      }
+    }
+  }
+  p.it += ntiles;
+}
+
 // ------------------------------------------------------------------------------------------------ staging from tagged vectors
 // xn = bf16( (float(h) * r) * float(w) ) from the tagged residual vector (dim/2 words)
 template <int MAXP>
@@ -453,8 +529,9 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
       uint32_t* pg = reinterpret_cast<uint32_t*>(scratch);     // [(nchunks-1)][WPC] payloads
       const int total = (a.nchunks - 1) * WPC;
       const uint64_t* src = a.part_ll + ((size_t)kvh * a.maxchunks + 1) * WPC;
-      for (int off = 0; off < total; off += 4096)
-        ll_gather<4>(src + off, min(4096, total - off), a.tag_part, pg + off, tid_c, kConsumerThreads, wc, layer);
+      constexpr int SEGW = 8 * kConsumerThreads;              // words one ll_gather<4> call can own
+      for (int off = 0; off < total; off += SEGW)
+        ll_gather<4>(src + off, min(SEGW, total - off), a.tag_part, pg + off, tid_c, kConsumerThreads, wc, layer);
       named_bar_sync(kBarConsumers, kConsumerThreads);
       const float* pf = reinterpret_cast<const float*>(pg);
       for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
@@ -556,6 +633,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     float* hown = sm.hown;                                      // this CTA's rows of the residual stream (exact bf16 values)
     int* s_done = sm.misc + 20;                                 // warps of this CTA that finished the current producing phase
     if (tid_c == 0) *s_done = 0;
+    const QueueState qs_{sm.qpart, sm.tdone, sm.bcnt};
+    if (tid_c < kStages) sm.tdone[tid_c] = 0;
+    if (tid_c < 2 * kStages) sm.bcnt[tid_c] = 0;
     float* ypart = sm.hown + kMaxOwnRows;                       // tensor parallel: this rank's partial sums of its rows
     constexpr int MAXP_O = (KO::K / 4 + kConsumerThreads - 1) / kConsumerThreads;
     // O / down epilogue. One GPU: h = bf16(h + y * resid) at once. Tensor parallel: y is a partial sum over this
@@ -643,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
       named_bar_sync(kBarConsumers, kConsumerThreads);          // x_s may be rewritten only after everyone has its slice
       FB_STAMP(1);
-      consume_rows_epi<KDS, HZ>(pipe, q1 - q0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+      consume_rows_q<KDS, HZ>(pipe, q1 - q0, xd, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
         // lanes 0/8/16/24 hold rows row0..row0+3: two RoPE pairs (or four v dims)
         const float c1 = __shfl_down_sync(0xffffffffu, c, 8);
         if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
@@ -688,7 +768,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
         load_x_slice<KO>(sm.x_s, wg % KO::KS, lane, xo);
         named_bar_sync(kBarConsumers, kConsumerThreads);
         FB_STAMP(4);
-        consume_rows_epi<KOS, HZ>(pipe, o1 - o0, xo, part_s, cw, lane, wc, l,
+        consume_rows_q<KOS, HZ>(pipe, o1 - o0, xo, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_o, 0); });
         if (N > 1) resid_finish(tg_o, 0, l);
         else post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
@@ -699,7 +779,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
       named_bar_sync(kBarConsumers, kConsumerThreads);
       FB_STAMP(6);
-      consume_rows_epi<KD, HZ>(pipe, g1 - g0, xd, part_s, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+      consume_rows_q<KD, HZ>(pipe, g1 - g0, xd, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
         // rows (g_i, u_i, g_{i+1}, u_{i+1}) -> act[i], act[i+1] -> one tagged word
         const float u = __shfl_down_sync(0xffffffffu, c, 8);
         float av = 0.f;
@@ -721,7 +801,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
         load_x_slice<KF>(sm.x_s, wg % KF::KS, lane, xf);
         named_bar_sync(kBarConsumers, kConsumerThreads);
         FB_STAMP(8);
-        consume_rows_epi<KFS, HZ>(pipe, o1 - o0, xf, part_s, cw, lane, wc, l,
+        consume_rows_q<KFS, HZ>(pipe, o1 - o0, xf, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_dn, 1); });
         if (N > 1) resid_finish(tg_dn, 1, l);
         else post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
@@ -736,7 +816,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     named_bar_sync(kBarConsumers, kConsumerThreads);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    consume_rows_epi<KD, HZ>(pipe, l1 - l0, xd, part_s, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
+    consume_rows_q<KD, HZ>(pipe, l1 - l0, xd, qs_, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
       if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
         const int row = P.vocab_base + l0 + row0 + (lane >> 3);     // index in the full vocabulary
         const float y = c / P.logits_scaling;

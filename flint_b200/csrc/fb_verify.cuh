@@ -207,17 +207,24 @@ __device__ __forceinline__ uint32_t a_pair(uint32_t w, int rot) {
   return d;
 }
 
-// CTA: 16 weight rows (one m16 tile) x all MT tokens; its 8 warps split every K chunk into eighths (a warp's part
-// never straddles a 128-column group). Deep cp.async pipeline: the kernel is latency-bound unless tens of KB of
-// weights per SM are in flight.
+// CTA: 32 weight rows (two m16 tiles) x all MT tokens; its 8 warps are 2 row tiles x 4 quarters of every K chunk (a
+// quarter never straddles a 128-column group). Every CTA re-reads the activations, so taller tiles halve that traffic;
+// wide chunks amortise the per-chunk barrier; the pipeline is as deep as shared memory allows, because the kernel is
+// latency-bound unless tens of KB of weights per SM are in flight.
 template <int MT>
 struct VCfg {
-  static constexpr int RT = 16;
-  static constexpr int STAGES = MT <= 16 ? 8 : (MT <= 32 ? 6 : 4);
+  static constexpr int RT = 32;
+  static constexpr int KCMAX = MT <= 32 ? 512 : 256;            // widest K chunk whose activations still fit a stage
+  template <int KC>
+  static constexpr int stages() {
+    constexpr int stage = RT * (KC / 2 + 16) + MT * (KC * 2 + 32);
+    constexpr int budget = MT <= 16 ? 104 * 1024 : 200 * 1024;    // 2 CTAs per SM for the common 16-token case
+    return budget / stage < 2 ? 2 : (budget / stage > 8 ? 8 : budget / stage);
+  }
 };
 template <int MT, int KC, int EPI, int HD>
 __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
-  constexpr int RT = VCfg<MT>::RT, NT = MT / 8, STAGES = VCfg<MT>::STAGES;
+  constexpr int RT = VCfg<MT>::RT, NT = MT / 8, STAGES = VCfg<MT>::template stages<KC>();
   constexpr int MTILES = RT / 16, KPARTS = 8 / MTILES;
   constexpr int WSTRIDE = KC / 2 + 16;          // bytes per weight row in a stage (padding de-conflicts the A loads)
   constexpr int XSTRIDE = KC * 2 + 32;          // bytes per token row in a stage
@@ -394,13 +401,13 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
   }
 }
 
+// dynamic shared memory of a launch: the stages (reused by the reduction) + `meta` bf16 scales/zeros per row
 template <int MT, int KC>
-constexpr int v_gemm_smem() {
-  // stages + scales/zeros of the rows for K up to 14336 (112 groups x 2 x 2 bytes); the reduction reuses the stages
+constexpr int v_gemm_smem(int meta) {
   constexpr int RT = VCfg<MT>::RT;
-  constexpr int stages = VCfg<MT>::STAGES * (RT * (KC / 2 + 16) + MT * (KC * 2 + 32));
+  constexpr int stages = VCfg<MT>::template stages<KC>() * (RT * (KC / 2 + 16) + MT * (KC * 2 + 32));
   constexpr int red = (8 / (RT / 16)) * RT * MT * 4;
-  return (stages > red ? stages : red) + RT * 112 * 2 * 2;
+  return (stages > red ? stages : red) + ((RT * meta * 2 + 127) & ~127);
 }
 
 }  // namespace fb
