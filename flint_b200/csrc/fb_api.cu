@@ -7,7 +7,7 @@
 #include <new>
 
 #include "../../include/flint_b200.h"
-#include "fb_decode2.cuh"
+#include "fb_decode.cuh"
 #include "fb_verify.cuh"
 
 using namespace fb;
@@ -18,14 +18,11 @@ struct fb_ctx {
   uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
   const void *n1, *n2, *nf, *embed;
   float* invf;
-  uint16_t *h, *qbuf, *ao, *act;
-  float *pm, *pd, *pacc, *cand_val;
-  int* cand_idx;
-  unsigned* bar_ctr;
+  uint8_t *vw_qkv, *vw_o, *vw_gu, *vw_d, *vw_lm;                    // row-record copies read by the verify kernels
   DevStatus* status;
   void *kc, *vc;
   int max_seq, maxchunks;
-  unsigned bar_base, spin_limit;
+  unsigned spin_limit;
   bool weights_bound;
   int last_cuda_error;
   int force_chunks;
@@ -40,39 +37,30 @@ struct fb_ctx {
   bool peers_open[8];
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   int max_fly;
-  int version;                                                      // 2: data-flow kernel (default), 1: grid-barrier kernel
 };
 
 namespace {
 
-typedef void (*decode_fn_t)(const DecodeParams);
-
 struct KernelEntry {
   int dim, ko, ffn, head_dim, rgqa, hz;
-  const void* fn;     // grid-barrier kernel (single-GPU shapes only)
-  const void* fn2;    // data-flow kernel
+  const void* fn2;
 };
 
-#define FB_DECODE_ENTRY(KD, KF, HD, R)                                                      \
-  {KD::K, KD::K, KF::K, HD, R, 0, (const void*)decode_mega<KD, KF, HD, R, false>,           \
-   (const void*)decode_mega2<KD, KD, KF, HD, R, false>},                                     \
-  {KD::K, KD::K, KF::K, HD, R, 1, (const void*)decode_mega<KD, KF, HD, R, true>,            \
-   (const void*)decode_mega2<KD, KD, KF, HD, R, true>}
-// a tensor-parallel rank: O projection over this rank's heads (KO columns), FFN slice of KF columns
-#define FB_DECODE_TP_ENTRY(KD, KO, KF, HD, R)                                               \
-  {KD::K, KO::K, KF::K, HD, R, 0, nullptr, (const void*)decode_mega2<KD, KO, KF, HD, R, false>}, \
-  {KD::K, KO::K, KF::K, HD, R, 1, nullptr, (const void*)decode_mega2<KD, KO, KF, HD, R, true>}
+// KD: model width, KO: attention output width of this rank, KF: FFN width of this rank
+#define FB_DECODE_ENTRY(KD, KO, KF, HD, R)                                     \
+  {KD, KO, KF, HD, R, 0, (const void*)decode_mega2<KD, KO, KF, HD, R, false>},  \
+  {KD, KO, KF, HD, R, 1, (const void*)decode_mega2<KD, KO, KF, HD, R, true>}
 
 const KernelEntry kDecodeKernels[] = {
-    FB_DECODE_ENTRY(K512, K1408, 64, 4),      // tiny test decoder
-    FB_DECODE_ENTRY(K2560, K8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
-    FB_DECODE_ENTRY(K2560, K8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
-    FB_DECODE_ENTRY(K4096, K14336, 128, 4),   // 8B-class
-    FB_DECODE_TP_ENTRY(K2560, K1280, K4096, 80, 4),    // 3B-class over 2 GPUs
-    FB_DECODE_TP_ENTRY(K2560, K640, K2048, 80, 4),     // 3B-class over 4 GPUs
-    FB_DECODE_TP_ENTRY(K4096, K2048, K7168, 128, 4),   // 8B-class over 2 GPUs
-    FB_DECODE_TP_ENTRY(K4096, K1024, K3584, 128, 4),   // 8B-class over 4 GPUs
-    FB_DECODE_TP_ENTRY(K4096, K512, K1792, 128, 4),    // 8B-class over 8 GPUs
+    FB_DECODE_ENTRY(512, 512, 1408, 64, 4),       // tiny test decoder
+    FB_DECODE_ENTRY(2560, 2560, 8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
+    FB_DECODE_ENTRY(2560, 2560, 8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
+    FB_DECODE_ENTRY(4096, 4096, 14336, 128, 4),   // 8B-class
+    FB_DECODE_ENTRY(2560, 1280, 4096, 80, 4),     // 3B-class over 2 GPUs
+    FB_DECODE_ENTRY(2560, 640, 2048, 80, 4),      // 3B-class over 4 GPUs
+    FB_DECODE_ENTRY(4096, 2048, 7168, 128, 4),    // 8B-class over 2 GPUs
+    FB_DECODE_ENTRY(4096, 1024, 3584, 128, 4),    // 8B-class over 4 GPUs
+    FB_DECODE_ENTRY(4096, 512, 1792, 128, 4),     // 8B-class over 8 GPUs
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
 
@@ -112,30 +100,55 @@ struct DeviceGuard {
 
 int chunks_for(const fb_ctx* c, int T) {
   if (c->force_chunks > 0) return c->force_chunks < c->maxchunks ? c->force_chunks : c->maxchunks;
-  if (c->version == 1) {
-    if (T <= 512) return 1;
-    const int n1 = (T + 255) / 256;
-    return n1 < c->maxchunks ? n1 : c->maxchunks;
-  }
-  // data-flow kernel: spread every kv head over as many CTAs as there are (one sweep of 16 warps covers 32 positions)
+  // spread every kv head over as many CTAs as there are (one sweep of the consumer warps covers ~32 positions)
   int n = (T + 15) / 16;
   if (n < 1) n = 1;
   return n < c->maxchunks ? n : c->maxchunks;
 }
 
-template <class KC>
+// every K the stand-alone entry points (re-layout, dequantise, GEMV) are built for
+#define FB_FOR_EACH_K(X) X(512) X(640) X(1024) X(1280) X(1408) X(1792) X(2048) X(2560) X(3584) X(4096) X(7168) X(8192) X(14336)
+
+template <int K>
 int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
   cudaError_t e;
   if (hz) {
-    e = cudaFuncSetAttribute(gemv_stream<KC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(gemv_stream<TCfg<K>, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    gemv_stream<KC, true><<<grid, kThreads, kSmemBytes, st>>>(p);
+    gemv_stream<TCfg<K>, true><<<grid, kThreads, kSmemBytes, st>>>(p);
   } else {
-    e = cudaFuncSetAttribute(gemv_stream<KC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    e = cudaFuncSetAttribute(gemv_stream<TCfg<K>, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    gemv_stream<KC, false><<<grid, kThreads, kSmemBytes, st>>>(p);
+    gemv_stream<TCfg<K>, false><<<grid, kThreads, kSmemBytes, st>>>(p);
   }
   return (int)cudaGetLastError();
+}
+
+bool supported_k(int k) {
+  switch (k) {
+#define X(K_) case K_:
+    FB_FOR_EACH_K(X)
+#undef X
+    return true;
+  }
+  return false;
+}
+
+// caller layout -> tiles, for `layers` stacked matrices of `rows` rows each
+cudaError_t launch_repack(const void* q, const void* s, const void* z, int layers, int rows, int k, int order, int arg,
+                          int orows, uint8_t* out, cudaStream_t st) {
+  const int tiles = (rows + tile_rt(k) - 1) / tile_rt(k);
+  switch (k) {
+#define X(K_)                                                                                                          \
+  case K_:                                                                                                             \
+    repack_tiles<K_><<<dim3(tiles, layers), 128, 0, st>>>((const uint32_t*)q, (const uint16_t*)s, (const uint16_t*)z, rows, \
+                                                          order, arg, orows, out);                                     \
+    break;
+    FB_FOR_EACH_K(X)
+#undef X
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 template <int MT, int KC, int EPI, int HD>
@@ -208,7 +221,7 @@ int fb_query(int device, fb_caps* out) {
   out->cooperative_launch = p.cooperativeLaunch;
   out->total_mem_bytes = (int64_t)p.totalGlobalMem;
   cudaFuncAttributes fa;
-  if (cudaFuncGetAttributes(&fa, kDecodeKernels[2].fn) == cudaSuccess) out->regs_decode_kernel = fa.numRegs;
+  if (cudaFuncGetAttributes(&fa, kDecodeKernels[2].fn2) == cudaSuccess) out->regs_decode_kernel = fa.numRegs;
   return FB_OK;
 }
 
@@ -240,7 +253,6 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   c->kernel_id = kid;
   c->rgqa = d.n_head / d.n_kv_head;
   c->spin_limit = 4000000u;
-  c->version = 2;
   c->max_fly = 4;
   c->tp_size = tp_size; c->tp_rank = tp_rank; c->vocab_base = vocab_base; c->ko = d.n_head * d.head_dim;
   c->tag_base = 8;
@@ -251,27 +263,10 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
     const int wpc_bytes = (c->rgqa * d.head_dim + 2 * c->rgqa) * 4;
     if (c->maxchunks > kScratchBytes / wpc_bytes) c->maxchunks = kScratchBytes / wpc_bytes;
   }
-  // result buffer of a CTA must hold its rows of the widest phase
-  if (tp_size == 1) {
-    const int G = c->sm_count;
-    const int ksD = d.dim == 4096 ? 2 : 1;
-    const long long lm_rows = ((long long)d.vocab + G - 1) / G + 1, gu_rows = (2LL * d.ffn + G - 1) / G + 2;
-    if (lm_rows * ksD > kResFloats || gu_rows * ksD > kResFloats) { delete c; return FB_ERR_SHAPE; }
-  }
   const int QD = d.n_head * d.head_dim;
   cudaError_t e = cudaSuccess;
   auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
   A(dmalloc(&c->invf, sizeof(float) * (d.head_dim / 2)));
-  A(dmalloc(&c->h, 2 * (size_t)d.dim));
-  A(dmalloc(&c->qbuf, 2 * (size_t)QD));
-  A(dmalloc(&c->ao, 2 * (size_t)QD));
-  A(dmalloc(&c->act, 2 * (size_t)d.ffn));
-  A(dmalloc(&c->pm, 4 * (size_t)d.n_head * c->maxchunks));
-  A(dmalloc(&c->pd, 4 * (size_t)d.n_head * c->maxchunks));
-  A(dmalloc(&c->pacc, 4 * (size_t)d.n_head * c->maxchunks * d.head_dim));
-  A(dmalloc(&c->cand_val, 4 * (size_t)c->sm_count));
-  A(dmalloc(&c->cand_idx, 4 * (size_t)c->sm_count));
-  A(dmalloc(&c->bar_ctr, 256));
   A(dmalloc(&c->status, sizeof(DevStatus)));
   {
     const size_t inbox_words = (size_t)2 * tp_size * d.dim + 2 * (size_t)tp_size + 16;
@@ -302,15 +297,16 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   A(dmalloc(&c->flags, 3 * 256 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
-  if ((d.dim / 2 + c->sm_count - 1) / c->sm_count * 2 + 2 > kMaxOwnRows || (2 * d.ffn) % 4) e = cudaErrorInvalidValue;
+  {  // rows of the residual stream one CTA owns (whole tiles of the O and the down matrix)
+    const int uo = tile_rt(QD) > tile_rt(d.ffn) ? tile_rt(QD) : tile_rt(d.ffn);
+    const int units = (d.dim + uo - 1) / uo;
+    if (((units + c->sm_count - 1) / c->sm_count + 1) * uo > kMaxOwnRows || (2 * d.ffn) % 4) e = cudaErrorInvalidValue;
+  }
   if (e == cudaSuccess) {
     float invf[128];
     for (int i = 0; i < d.head_dim / 2; i++) invf[i] = (float)pow((double)d.rope_base, -2.0 * i / d.head_dim);
     A(cudaMemcpy(c->invf, invf, sizeof(float) * (d.head_dim / 2), cudaMemcpyHostToDevice));
-    A(cudaMemset(c->bar_ctr, 0, 256));
     A(cudaMemset(c->status, 0, sizeof(DevStatus)));
-    if (kDecodeKernels[kid].fn)
-      A(cudaFuncSetAttribute(kDecodeKernels[kid].fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     A(cudaFuncSetAttribute(kDecodeKernels[kid].fn2, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   }
   if (e != cudaSuccess) {
@@ -326,10 +322,9 @@ int fb_ctx_destroy(fb_ctx* c) {
   DeviceGuard g(c->device);
   for (int p = 0; p < 8; p++)
     if (c->peers_open[p] && c->peer_inbox[p]) cudaIpcCloseMemHandle(c->peer_inbox[p]);
-  void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf, c->h, c->qbuf, c->ao, c->act, c->pm, c->pd,
-                  c->pacc, c->cand_val, c->cand_idx, c->bar_ctr, c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll,
-                  c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags, c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact,
-                  c->inbox};
+  void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->vw_qkv, c->vw_o, c->vw_gu, c->vw_d, c->vw_lm, c->invf,
+                  c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags,
+                  c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->inbox};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -340,13 +335,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (!c) return FB_ERR_ARG;
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
-  if (what == 4) { if (value < 1 || value > kStages) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
-  if (what == 3) {
-    if (value != 1 && value != 2) return FB_ERR_ARG;
-    if (value == 1 && (c->tp_size > 1 || !kDecodeKernels[c->kernel_id].fn)) return FB_ERR_ARG;
-    c->version = (int)value;
-    return FB_OK;
-  }
+  if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
 }
@@ -369,18 +358,16 @@ int fb_last_status(fb_ctx* c, fb_status* out) {
   out->block = s.block;
   out->expected = s.expected;
   out->seen = s.seen;
-  if (s.code != 0) {   // a launch gave up: the barrier counter is at an arbitrary value, start over
-    cudaMemset(c->bar_ctr, 0, 256);
+  if (s.code != 0) {   // a launch gave up: clear the report so that the next launch starts clean
     cudaMemset(c->status, 0, sizeof(DevStatus));
     cudaMemset(c->cnt, 0, 256);
-    c->bar_base = 0;
   }
   return FB_OK;
 }
 
 size_t fb_stream_bytes(int32_t rows, int32_t k, int32_t has_zeros) {
-  if (rows < 0 || k <= 0 || k % 128) return 0;
-  return (size_t)rows * rec_bytes_of(k, has_zeros);
+  if (rows < 0 || !supported_k(k)) return 0;
+  return (size_t)pad_rows(rows, k) * rec_bytes_of(k, has_zeros);
 }
 
 int fb_repack(const void* d_q, const void* d_s, const void* d_z, int32_t rows, int32_t k, int32_t order, int32_t order_arg,
@@ -388,17 +375,26 @@ int fb_repack(const void* d_q, const void* d_s, const void* d_z, int32_t rows, i
   if (!d_q || !d_s || !d_out || rows <= 0 || k <= 0 || k % 128 || order < 0 || order > 2) return FB_ERR_ARG;
   if (order == 1 && (order_arg <= 0 || order_arg % 2 || order_rows % order_arg || order_rows > rows)) return FB_ERR_ARG;
   if (order == 2 && (order_arg * 2 != rows)) return FB_ERR_ARG;
-  repack_rows<<<dim3(rows, 1), 128, 0, (cudaStream_t)stream>>>((const uint32_t*)d_q, (const uint16_t*)d_s,
-                                                             (const uint16_t*)d_z, rows, k, order, order_arg, order_rows,
-                                                             (uint8_t*)d_out);
-  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+  if (!supported_k(k)) return FB_ERR_SHAPE;
+  return launch_repack(d_q, d_s, d_z, 1, rows, k, order, order_arg, order_rows, (uint8_t*)d_out, (cudaStream_t)stream) ==
+                 cudaSuccess
+             ? FB_OK
+             : FB_ERR_CUDA;
 }
 
 int fb_dequant(const void* d_in, int32_t rows, int32_t k, int32_t has_zeros, int32_t order, int32_t order_arg,
                int32_t order_rows, float* d_out, void* stream) {
   if (!d_in || !d_out || rows <= 0 || k <= 0 || k % 128 || order < 0 || order > 2) return FB_ERR_ARG;
-  dequant_rows<<<rows, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)d_in, rows, k, has_zeros, order, order_arg,
-                                                      order_rows, d_out);
+  switch (k) {
+#define X(K_)                                                                                                         \
+  case K_:                                                                                                            \
+    dequant_tiles<K_><<<rows, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)d_in, rows, has_zeros, order, order_arg, \
+                                                              order_rows, d_out);                                     \
+    break;
+    FB_FOR_EACH_K(X)
+#undef X
+    default: return FB_ERR_SHAPE;
+  }
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_CUDA;
 }
 
@@ -415,12 +411,9 @@ int fb_gemv(const void* d_in, int32_t rows, int32_t k, int32_t has_zeros, int32_
   cudaStream_t st = (cudaStream_t)stream;
   int e;
   switch (k) {
-    case 512: e = launch_gemv_k<K512>(hz, p, sms, st); break;
-    case 1408: e = launch_gemv_k<K1408>(hz, p, sms, st); break;
-    case 2560: e = launch_gemv_k<K2560>(hz, p, sms, st); break;
-    case 4096: e = launch_gemv_k<K4096>(hz, p, sms, st); break;
-    case 8192: e = launch_gemv_k<K8192>(hz, p, sms, st); break;
-    case 14336: e = launch_gemv_k<K14336>(hz, p, sms, st); break;
+#define X(K_) case K_: e = launch_gemv_k<K_>(hz, p, sms, st); break;
+    FB_FOR_EACH_K(X)
+#undef X
     default: return FB_ERR_SHAPE;
   }
   return e == 0 ? FB_OK : FB_ERR_CUDA;
@@ -439,7 +432,8 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
                    void* d_status, void* stream) {
   if (!d_q || !d_s || !d_x || !d_y || !d_status || rows <= 0 || k <= 0 || k % 128) return FB_ERR_ARG;
   const int hz = d_z != nullptr;
-  const size_t need = (size_t)rows * rec_bytes_of(k, hz);
+  if (!supported_k(k)) return FB_ERR_SHAPE;
+  const size_t need = fb_stream_bytes(rows, k, hz);
   if (need > kStaticScratchBytes) return FB_ERR_RANGE;       /* matrix larger than the built-in scratch: use fb_gemv */
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FB_ERR_CUDA;
@@ -472,21 +466,28 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int L = d.n_layer, D = d.dim, FF = d.ffn, HD = d.head_dim;
   const int QKV = (d.n_head + 2 * d.n_kv_head) * HD, QD = d.n_head * HD;
-  struct M { uint8_t** dst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
+  struct M { uint8_t **dst, **vdst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
   M ms[] = {
-      {&c->w_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
-      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
-      {&c->w_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
-      {&c->w_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
-      {&c->w_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
+      {&c->w_qkv, &c->vw_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
+      {&c->w_o, &c->vw_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
+      {&c->w_gu, &c->vw_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
+      {&c->w_d, &c->vw_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
+      {&c->w_lm, &c->vw_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
   };
   for (M& m : ms) {
-    const size_t bytes = (size_t)m.layers * m.rows * rec_bytes_of(m.k, hz);
+    // tiles for the decode kernel
+    const size_t bytes = (size_t)m.layers * pad_rows(m.rows, m.k) * rec_bytes_of(m.k, hz);
     if (*m.dst) { cudaFree(*m.dst); *m.dst = nullptr; }
     FB_CUDA(c, dmalloc(m.dst, bytes + 16));
+    FB_CUDA(c, launch_repack(m.q, m.s, hz ? m.z : nullptr, m.layers, m.rows, m.k, m.order, m.arg, m.orows, *m.dst, st));
+    // row records for the verify kernels (tensor-parallel contexts have no verify path)
+    if (c->tp_size > 1) continue;
+    const size_t vbytes = (size_t)m.layers * m.rows * vrec_bytes_of(m.k, hz);
+    if (*m.vdst) { cudaFree(*m.vdst); *m.vdst = nullptr; }
+    FB_CUDA(c, dmalloc(m.vdst, vbytes + 16));
     repack_rows<<<dim3(m.rows, m.layers), 128, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s,
                                                         hz ? (const uint16_t*)m.z : nullptr, m.rows, m.k, m.order, m.arg,
-                                                        m.orows, *m.dst);
+                                                        m.orows, *m.vdst);
     FB_CUDA(c, cudaGetLastError());
   }
   c->n1 = w->n1; c->n2 = w->n2; c->nf = w->nf; c->embed = w->embed;
@@ -511,67 +512,41 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   if (!d_h && !c->embed) return FB_ERR_STATE;
   if (d_h && ((uintptr_t)d_h & 1)) return FB_ERR_ARG;
   DeviceGuard g(c->device);
-  if (c->version == 2) {
-    Decode2Params Q;
-    memset(&Q, 0, sizeof(Q));
-    Q.w_qkv = c->w_qkv; Q.w_o = c->w_o; Q.w_gu = c->w_gu; Q.w_d = c->w_d; Q.w_lm = c->w_lm;
-    Q.n1 = (const uint16_t*)c->n1; Q.n2 = (const uint16_t*)c->n2; Q.nf = (const uint16_t*)c->nf;
-    Q.embed = (const uint16_t*)c->embed; Q.invf = c->invf;
-    Q.kc = (uint16_t*)c->kc; Q.vc = (uint16_t*)c->vc;
-    Q.h_ll = c->h_ll; Q.q_ll = c->q_ll; Q.k_ll = c->k_ll; Q.v_ll = c->v_ll; Q.ao_ll = c->ao_ll; Q.act_ll = c->act_ll;
-    Q.h_flags = c->flags; Q.act_flags = c->flags + 256; Q.ao_flags = c->flags + 512;
-    Q.cand_ll = c->cand_ll; Q.part_ll = c->part_ll; Q.status = c->status;
-    Q.d_token = d_token; Q.d_h = (uint16_t*)d_h; Q.d_logits = d_logits; Q.d_next = d_next;
-    Q.token = token; Q.pos = pos; Q.max_seq = c->max_seq;
-    Q.n_layer = d.n_layer; Q.dim = d.dim; Q.n_head = d.n_head; Q.n_kv = d.n_kv_head; Q.ffn = d.ffn; Q.vocab = d.vocab;
-    Q.nchunks = chunks_for(c, pos + 1);
-    Q.maxchunks = c->maxchunks;
-    const unsigned span = (unsigned)(d.n_layer + 1) * 8u;
-    if (c->tag_base > 0xffffffffu - 2 * span) c->tag_base = 8;      // tags never reach 0 (the value of fresh buffers)
-    Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
-    Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
-    Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly;
-    Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox;
-    for (int p = 0; p < c->tp_size; p++) {
-      if (!c->peer_inbox[p]) return FB_ERR_STATE;       /* fb_tp_connect has not been called */
-      Q.peer_inbox[p] = c->peer_inbox[p];
-    }
-    void* args2[] = {&Q};
-    FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn2, dim3(c->sm_count), dim3(kThreads), args2,
-                                           (size_t)kSmemBytes, (cudaStream_t)stream));
-    c->tag_base += span;
-    return FB_OK;
+  Decode2Params Q;
+  memset(&Q, 0, sizeof(Q));
+  Q.w_qkv = c->w_qkv; Q.w_o = c->w_o; Q.w_gu = c->w_gu; Q.w_d = c->w_d; Q.w_lm = c->w_lm;
+  Q.n1 = (const uint16_t*)c->n1; Q.n2 = (const uint16_t*)c->n2; Q.nf = (const uint16_t*)c->nf;
+  Q.embed = (const uint16_t*)c->embed; Q.invf = c->invf;
+  Q.kc = (uint16_t*)c->kc; Q.vc = (uint16_t*)c->vc;
+  Q.h_ll = c->h_ll; Q.q_ll = c->q_ll; Q.k_ll = c->k_ll; Q.v_ll = c->v_ll; Q.ao_ll = c->ao_ll; Q.act_ll = c->act_ll;
+  Q.h_flags = c->flags; Q.act_flags = c->flags + 256; Q.ao_flags = c->flags + 512;
+  Q.cand_ll = c->cand_ll; Q.part_ll = c->part_ll; Q.status = c->status;
+  Q.d_token = d_token; Q.d_h = (uint16_t*)d_h; Q.d_logits = d_logits; Q.d_next = d_next;
+  Q.token = token; Q.pos = pos; Q.max_seq = c->max_seq;
+  Q.n_layer = d.n_layer; Q.dim = d.dim; Q.n_head = d.n_head; Q.n_kv = d.n_kv_head; Q.ffn = d.ffn; Q.vocab = d.vocab;
+  Q.nchunks = chunks_for(c, pos + 1);
+  Q.maxchunks = c->maxchunks;
+  const unsigned span = (unsigned)(d.n_layer + 1) * 8u;
+  if (c->tag_base > 0xffffffffu - 2 * span) c->tag_base = 8;      // tags never reach 0 (the value of fresh buffers)
+  Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
+  Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
+  Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly;
+  Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox;
+  for (int p = 0; p < c->tp_size; p++) {
+    if (!c->peer_inbox[p]) return FB_ERR_STATE;       /* fb_tp_connect has not been called */
+    Q.peer_inbox[p] = c->peer_inbox[p];
   }
-  DecodeParams P;
-  memset(&P, 0, sizeof(P));
-  P.w_qkv = c->w_qkv; P.w_o = c->w_o; P.w_gu = c->w_gu; P.w_d = c->w_d; P.w_lm = c->w_lm;
-  P.n1 = (const uint16_t*)c->n1; P.n2 = (const uint16_t*)c->n2; P.nf = (const uint16_t*)c->nf;
-  P.embed = (const uint16_t*)c->embed; P.invf = c->invf;
-  P.kc = (uint16_t*)c->kc; P.vc = (uint16_t*)c->vc;
-  P.h = c->h; P.qbuf = c->qbuf; P.ao = c->ao; P.act = c->act;
-  P.pm = c->pm; P.pd = c->pd; P.pacc = c->pacc; P.cand_val = c->cand_val; P.cand_idx = c->cand_idx;
-  P.bar_ctr = c->bar_ctr; P.status = c->status;
-  P.d_token = d_token; P.d_h = (uint16_t*)d_h; P.d_logits = d_logits; P.d_next = d_next;
-  P.token = token; P.pos = pos; P.max_seq = c->max_seq;
-  P.n_layer = d.n_layer; P.dim = d.dim; P.n_head = d.n_head; P.n_kv = d.n_kv_head; P.ffn = d.ffn; P.vocab = d.vocab;
-  P.nchunks = chunks_for(c, pos + 1);
-  P.bar_base = c->bar_base; P.spin_limit = c->spin_limit;
-  P.eps = d.rms_eps; P.attn_scale = d.attn_scale; P.resid = d.resid_mult; P.emb_mult = d.emb_mult;
-  P.logits_scaling = d.logits_scaling;
-  P.prof = c->prof;
-  P.max_fly = (unsigned)c->max_fly;
-  const unsigned nbar = 1u + (unsigned)d.n_layer * (5u + (P.nchunks > 1 ? 1u : 0u)) + 1u;
-  void* args[] = {&P};
-  FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn, dim3(c->sm_count), dim3(kThreads), args,
+  void* args2[] = {&Q};
+  FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn2, dim3(c->sm_count), dim3(kThreads), args2,
                                          (size_t)kSmemBytes, (cudaStream_t)stream));
-  c->bar_base += nbar * (unsigned)c->sm_count;
+  c->tag_base += span;
   return FB_OK;
 }
 
 int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t* d_depth, const uint8_t* d_amask,
               int32_t M, int32_t pos, float* d_logits, void* d_feat, void* stream) {
   if (!c || !d_depth || !d_amask || (!d_tokens && !d_h)) return FB_ERR_ARG;
-  if (!c->weights_bound || !c->kc) return FB_ERR_STATE;
+  if (!c->weights_bound || !c->kc || !c->vw_qkv) return FB_ERR_STATE;
   if (!d_h && !c->embed) return FB_ERR_STATE;
   if (M < 1 || M > 64) return FB_ERR_RANGE;          /* never fall through to another M (reference: result.md:112-113) */
   if (pos < 0 || pos + M > c->max_seq) return FB_ERR_RANGE;
@@ -581,7 +556,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int D = d.dim, FF = d.ffn, HD = d.head_dim, QD = d.n_head * HD, QKV = (d.n_head + 2 * d.n_kv_head) * HD;
   const bool hz = d.has_zeros != 0;
-  const int recD = rec_bytes_of(D, hz), recQ = rec_bytes_of(QD, hz), recF = rec_bytes_of(FF, hz);
+  const int recD = vrec_bytes_of(D, hz), recQ = vrec_bytes_of(QD, hz), recF = vrec_bytes_of(FF, hz);
   v_embed<<<M, 256, 0, st>>>(d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh, D, d.vocab, d.emb_mult,
                              &c->status->code);
   FB_CUDA(c, cudaGetLastError());
@@ -593,22 +568,22 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
     uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
     v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
-    p.w = c->w_qkv + (size_t)l * QKV * recD; p.x_t = c->vxn; p.rows = QKV; p.K = D; p.rec = recD;
+    p.w = c->vw_qkv + (size_t)l * QKV * recD; p.x_t = c->vxn; p.rows = QKV; p.K = D; p.rec = recD;
     p.q = c->vq; p.kc = kcl; p.vc = vcl;
     FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, HD, st));
     FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, st));
-    p.w = c->w_o + (size_t)l * D * recQ; p.x_t = c->vao; p.rows = D; p.K = QD; p.rec = recQ; p.h = c->vh; p.out_ld = D;
+    p.w = c->vw_o + (size_t)l * D * recQ; p.x_t = c->vao; p.rows = D; p.K = QD; p.rec = recQ; p.h = c->vh; p.out_ld = D;
     FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
     v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
-    p.w = c->w_gu + (size_t)l * 2 * FF * recD; p.x_t = c->vxn; p.rows = 2 * FF; p.K = D; p.rec = recD; p.act_t = c->vact;
+    p.w = c->vw_gu + (size_t)l * 2 * FF * recD; p.x_t = c->vxn; p.rows = 2 * FF; p.K = D; p.rec = recD; p.act_t = c->vact;
     p.out_ld = FF;
     FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, HD, st));
-    p.w = c->w_d + (size_t)l * D * recF; p.x_t = c->vact; p.rows = D; p.K = FF; p.rec = recF; p.out_ld = D;
+    p.w = c->vw_d + (size_t)l * D * recF; p.x_t = c->vact; p.rows = D; p.K = FF; p.rec = recF; p.out_ld = D;
     FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
   }
   v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, d.rms_eps);
   if (d_logits) {
-    p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.K = D; p.rec = recD; p.logits = d_logits; p.out_ld = d.vocab;
+    p.w = c->vw_lm; p.x_t = c->vxn; p.rows = d.vocab; p.K = D; p.rec = recD; p.logits = d_logits; p.out_ld = d.vocab;
     FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, HD, st));
   }
   FB_CUDA(c, cudaGetLastError());

@@ -1,8 +1,9 @@
 // Shared device-side building blocks of the sm_100a decode path: PTX wrappers (mbarrier, 1-D bulk copies,
-// coherent loads), bounded waits that report instead of hanging, the streaming weight layout and the int4 row
-// dot product that every GEMV phase uses.
+// coherent loads), bounded waits that report instead of hanging, the tiled streaming weight layout and the int4 tile x
+// vector product (fp16 mma.sync) that every GEMV phase uses.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -10,28 +11,22 @@ namespace fb {
 
 // ------------------------------------------------------------------------------------------------ constants
 #ifndef FB_CW
-#define FB_CW 14      // 14 consumers + 1 producer = 15 warps -> at most 4 per scheduler -> 128 registers per thread; 14 also
-#endif                // divides the 28 four-row blocks a CTA gets of the gate/up matrix (3B-class) into exactly 2 rounds
-#ifndef FB_DOT
-#define FB_DOT 0      // 0: bf16 pairs + fma.rn.f32.bf16 (activations packed bf16 in registers)
-#endif                // 1: prmt -> fp32 weights + fma.rn.f32 (activations fp32 in registers)
-constexpr int kConsumerWarps = FB_CW;              // groups of 4 warps; group g consumes weight tiles t with t % kGroups == g
-constexpr int kWarpsPerGroup = 4;
-constexpr int kGroups = kConsumerWarps / kWarpsPerGroup;
+#define FB_CW 14      // 14 consumers + 1 producer = 15 warps -> at most 4 per scheduler -> 128 registers per thread
+#endif
+constexpr int kConsumerWarps = FB_CW;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;    // + one producer warp (lane 0 issues the bulk copies)
-constexpr int kStages = 8;                         // ring depth: 8 x 22 KB = 176 KB of weights in flight per SM
-constexpr int kStageBytes = 23040;              // largest tile: 3 rows of K=14336 with zeros = 22848 B
-constexpr int kScratchBytes = 40960;               // x staging (<= 14336 bf16) + per-phase results; attention merge area
+constexpr int kStages = 8;                         // ring depth: 8 x 22.5 KB = 180 KB of weights in flight per SM
+constexpr int kStageBytes = 23040;                 // a stage holds whole tiles (4 tiles of K = 2560, 1 of K = 8192 ...)
+constexpr int kScratchBytes = 40960;               // activations of the phase (<= 14336 fp16), then attention scratch
 constexpr int kXBytes = 28672;
-constexpr int kResFloats = (kScratchBytes - kXBytes) / 4;   // 3072 row results per CTA per phase
-constexpr int kTailBytes = 4096;                   // mbarriers, flags, reduction scratch, slice partials, owned residual rows
+constexpr int kTailBytes = 6144;                   // mbarriers, flags, reductions, slice partials, owned rows, group factors
 constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + kTailBytes;
 constexpr int kMaxOwnRows = 64;                    // rows of the residual stream one CTA may own
+constexpr int kMaxGroups = 112;                    // K <= 14336
 
 // named barriers (0 is __syncthreads)
-constexpr int kBarConsumers = 1;                   // all 512 consumer threads
-constexpr int kBarGroup0 = 2;                      // 2..5: one per consumer group (128 threads)
+constexpr int kBarConsumers = 1;                   // all consumer threads
 
 // device status words (global memory, owned by the context)
 struct DevStatus {
@@ -42,7 +37,7 @@ struct DevStatus {
   int pad;
 };
 
-enum Where { W_GRIDBAR = 1, W_FULL = 2, W_EMPTY = 3, W_DRAIN = 4, W_FLAG = 5 };
+enum Where { W_FULL = 2, W_EMPTY = 3, W_DRAIN = 4, W_FLAG = 5, W_LANDED = 6 };
 
 // ------------------------------------------------------------------------------------------------ small helpers
 __device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
@@ -156,13 +151,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, const Wa
 }
 
 // ------------------------------------------------------------------------------------------------ streaming layout
-// One record per weight row: K/2 bytes of nibble words in the caller's word order, then K/128 bf16 scales,
-// then (asymmetric layout only) K/128 bf16 zeros, padded to 16 bytes. Records are contiguous, so any run of rows is
-// one aligned byte range that a single 1-D bulk copy can bring in together with its scales.
-__host__ __device__ __forceinline__ int rec_bytes_of(int k, int has_zeros) {
-  const int meta = (k / 128) * 2 * (has_zeros ? 2 : 1);
-  return k / 2 + ((meta + 15) & ~15);
+// Weights are stored as TILES of RT consecutive stream rows x all K columns, laid out for the tensor pipe: a tile is
+// a sequence of "steps", 128 bytes each = one 32-bit word per lane of a warp, and a step is exactly the A operand of one
+// mma.m16n8k16. Batch-1 decode has no second matrix dimension to fill the 16 MMA rows with, so the 16 rows of a step
+// are RT weight rows x NJ = 16/RT column ranges of K/NJ columns each: MMA row i = (tile row i % RT, range i / RT), and
+// column n of the B operand carries the activations of range n. Output C[i][i / RT] is then the partial dot product
+// of tile row i % RT over range i / RT; the other columns are ignored.
+//
+// Inside a word the eight nibbles are placed so that no arithmetic is needed to turn them into fp16 operands:
+//   w & 0x000F000F        -> (nib0, nib4) as fp16 SUBNORMALS nib * 2^-24   = A[g  ][2t], A[g  ][2t+1]
+//   w & 0x00F000F0        -> (nib1, nib5) as 16 * nib * 2^-24              = A[g+8][2t], A[g+8][2t+1]
+//   (w >> 8) & the same   -> (nib2, nib6), (nib3, nib7)                    = A[g][2t+8..], A[g+8][2t+8..]
+// for lane (g = lane / 4, t = lane % 4). The tensor pipe multiplies subnormals exactly, so C = 2^-24 * sum nib * x for
+// the first eight MMA rows and 16 times that for the last eight; the per-group flush folds 2^24 (or 2^20), the group's
+// bf16 scale and the activations' power-of-two factor into one fp32 multiply, and removes the nibble offset with
+// -8 * scale * sum(x) (and adds zero * sum(x) for the asymmetric layout). Products and the subtraction are exact in
+// fp32 terms: the arithmetic is the reference's sum (nib - 8) * s * x with a different summation order.
+//
+// Steps are stored four to a block: block bq holds, for every lane, the words of steps 4bq..4bq+3 as one 16-byte
+// vector. Range j walks its columns with its steps rotated inside each block (local step (s & ~3) | ((s + j) & 3)),
+// which spreads the ranges' activation loads over different shared-memory banks. After the nibble area come the
+// tile's scales as bf16 [K/128][RT], then (asymmetric layout) the zeros in the same shape.
+__host__ __device__ constexpr int tile_rt(int k) {
+  const int g = k / 128;
+  if (g % 4 == 0 && 4 * (k / 2 + g * 4) <= 23040) return 4;
+  if (g % 8 == 0) return 2;
+  if (g % 2 == 0) return 8;
+  return 16;
 }
+__host__ __device__ constexpr int tile_bytes(int k, int has_zeros) {
+  return tile_rt(k) * (k / 2 + (k / 128) * 2 * (has_zeros ? 2 : 1));
+}
+// bytes per stream row (a tile is RT of these; only whole tiles are addressable)
+__host__ __device__ constexpr int rec_bytes_of(int k, int has_zeros) { return tile_bytes(k, has_zeros) / tile_rt(k); }
+__host__ __device__ constexpr int pad_rows(int rows, int k) { return (rows + tile_rt(k) - 1) / tile_rt(k) * tile_rt(k); }
+__host__ __device__ __forceinline__ int local_step(int s, int j) { return (s & ~3) | ((s + j) & 3); }
+
 // stream row j of a matrix holds source row perm(j)
 //   order 0: identity
 //   order 1: rows [0, order_rows) are heads of `arg` rows; inside a head stream rows (2p, 2p+1) hold dims (p, p+arg/2),
@@ -178,191 +202,168 @@ __host__ __device__ __forceinline__ int perm_row(int j, int order, int arg, int 
   return j;
 }
 
-// Per-K compile-time schedule. A consumer group (4 warps) owns one tile at a time; inside it warp wg takes the
-// K-slice wg % KS of the row blocks wg / KS, wg / KS + 4/KS, ... (RB rows per block). A lane owns units
-// u = lane + 32*i (i < NI) of U consecutive words inside its slice and keeps the matching activations in registers
-// for the whole phase.
-template <int K_, int KS_, int U_, int NI_, int RB_, int TILE_ROWS_>
-struct KCfg {
-  static constexpr int K = K_, KS = KS_, U = U_, NI = NI_, RB = RB_, TILE_ROWS = TILE_ROWS_;
-  static constexpr int SLICE_WORDS = K / 8 / KS;
-  static constexpr int UNITS = SLICE_WORDS / U;           // units per slice
-  static constexpr bool PRED = (UNITS != 32 * NI);         // last i is partially filled
-  static constexpr int NSUB = kWarpsPerGroup / KS;         // row sub-groups per consumer group
-  static_assert(K % 128 == 0 && SLICE_WORDS % U == 0 && UNITS <= 32 * NI && UNITS > 32 * (NI - 1), "bad KCfg");
-  static_assert(kWarpsPerGroup % KS == 0, "KS must divide the group");
-  static_assert((SLICE_WORDS * 8) % 128 == 0 || KS == 1, "slices must hold whole groups");
-  static_assert((U * 8) <= 128 && 128 % (U * 8) == 0, "a unit stays inside one group");
-};
-using K512 = KCfg<512, 1, 2, 1, 4, 64>;
-using K1408 = KCfg<1408, 1, 2, 3, 4, 28>;
-using K2560 = KCfg<2560, 1, 2, 5, 4, 16>;
-using K4096 = KCfg<4096, 2, 4, 2, 4, 8>;
-using K8192 = KCfg<8192, 4, 4, 2, 4, 4>;
-using K14336 = KCfg<14336, 4, 4, 4, 2, 2>;   // even blocks: epilogues pair rows (2i, 2i+1)
-// Same K, finer work units for phases that give a CTA only ~20 rows (QKV, O, down): blocks of 2 rows and small
-// tiles keep all consumer warps busy and shorten the tail that the next phase has to wait for.
-using K512S = KCfg<512, 1, 2, 1, 2, 16>;
-using K1408S = KCfg<1408, 1, 2, 3, 2, 8>;
-using K2560S = KCfg<2560, 1, 2, 5, 2, 8>;
-using K4096S = KCfg<4096, 2, 4, 2, 2, 4>;
-using K8192S = KCfg<8192, 4, 4, 2, 2, 2>;
-// K values that only appear under tensor parallelism (a rank's slice of the attention output or of the FFN)
-using K640 = KCfg<640, 1, 2, 2, 2, 16>;
-using K1024 = KCfg<1024, 1, 4, 1, 2, 16>;
-using K1280 = KCfg<1280, 1, 2, 3, 2, 8>;
-using K1792 = KCfg<1792, 1, 4, 2, 2, 8>;
-using K2048 = KCfg<2048, 1, 4, 2, 2, 8>;
-using K3584 = KCfg<3584, 2, 4, 2, 2, 4>;
-using K7168 = KCfg<7168, 4, 4, 2, 2, 2>;
-template <class KC> struct SmallOf { using type = KC; };
-template <> struct SmallOf<K512> { using type = K512S; };
-template <> struct SmallOf<K1408> { using type = K1408S; };
-template <> struct SmallOf<K2560> { using type = K2560S; };
-template <> struct SmallOf<K4096> { using type = K4096S; };
-template <> struct SmallOf<K8192> { using type = K8192S; };
-
-// activations of one lane for its units + the fp32 sum of every unit (for the offset trick below)
-template <class KC>
-struct XRegs {
-#if FB_DOT == 0
-  uint32_t p[KC::NI][KC::U * 4];     // packed bf16 pairs
-#else
-  float p[KC::NI][KC::U * 8];        // fp32
-#endif
-  float sum[KC::NI];
+// Compile-time schedule of one matrix shape. KS > 1 cuts a tile's blocks into KS slices that different warps take
+// (phases that give a CTA only a handful of tiles); TPS tiles travel in one bulk copy / ring stage.
+template <int K_, int KS_ = 1, int TPS_ = 0>
+struct TCfg {
+  static constexpr int K = K_, KS = KS_, RT = tile_rt(K_);
+  static constexpr int NJ = 16 / RT, G = K / 128, RG = G / NJ, BQ = RG * 2;     // rounds (8 steps) per range; 4-step blocks
+  static constexpr int NB = BQ / KS;                                             // blocks per slice
+  static constexpr int NIB = RT * K / 2;
+  static constexpr int tile(bool hz) { return tile_bytes(K_, hz); }
+  static constexpr int TPS_FIT = kStageBytes / tile_bytes(K_, 1);
+  static constexpr int TPS = TPS_ > 0 ? TPS_ : (KS_ > 1 ? (TPS_FIT > 2 ? 2 : TPS_FIT) : (TPS_FIT > 8 ? 8 : TPS_FIT));
+  static constexpr int TILE_ROWS = TPS * RT;                                      // rows per ring stage
+  static_assert(K % 128 == 0 && G % NJ == 0 && BQ % KS == 0, "columns must split into whole groups per range and slice");
+  static_assert(TPS >= 1 && TPS * tile_bytes(K_, 1) <= kStageBytes, "a stage holds whole tiles");
+  static_assert(KS == 1 || (RT <= 4 && TPS <= 2 && KS <= 4), "slice partials: 4 rows x 4 slices x 2 tiles per stage");
+  static_assert(tile_bytes(K_, 0) % 16 == 0 && tile_bytes(K_, 1) % 16 == 0, "bulk copies move multiples of 16 bytes");
 };
 
-// Load a lane's slice from the staged activations x_s (bf16[K] in shared memory).
-template <class KC>
-__device__ __forceinline__ void load_x_slice(const uint16_t* x_s, int slice, int lane, XRegs<KC>& x) {
+// activations of the current phase in shared memory: fp16 in B-operand order (inside every 16 columns the halves are
+// [2t, 2t+1, 2t+8, 2t+9] for t = 0..3) and, per group of 128 columns, {2^24 / m, 2^20 / m, -8 * sum x, sum x} where m is
+// the power of two the group was multiplied by before the conversion to fp16
+struct XStage {
+  const __half* xh;
+  const float4* xf;
+};
+
+// Convert 4 consecutive bf16 activations (elements 4*lane .. 4*lane+3 of one group of 128, one group per warp) and
+// store them; lane 0 also writes the group's factors. The whole warp must call this together.
+__device__ __forceinline__ void stage_group_fp16(uint32_t p01, uint32_t p23, __half* xh_group, float4* xf_group, int lane) {
+  const uint32_t e0 = (p01 >> 7) & 255, e1 = (p01 >> 23) & 255, e2 = (p23 >> 7) & 255, e3 = (p23 >> 23) & 255;
+  const uint32_t em = __reduce_max_sync(0xffffffffu, max(max(e0, e1), max(e2, e3)));
+  uint32_t mf = 268u - em;                    // exponent field of m: the group's largest magnitude lands in [2^14, 2^15)
+  mf = mf > 253u ? 253u : (mf < 24u ? 24u : mf);
+  const float mult = __uint_as_float(mf << 23), inv = __uint_as_float((254u - mf) << 23);
+  const float f0 = bflo(p01), f1 = bfhi(p01), f2 = bflo(p23), f3 = bfhi(p23);
+  const __half2 h01 = __floats2half2_rn(f0 * mult, f1 * mult), h23 = __floats2half2_rn(f2 * mult, f3 * mult);
+  float sx = (f0 + f1) + (f2 + f3);
 #pragma unroll
-  for (int i = 0; i < KC::NI; i++) {
-    const int unit = lane + 32 * i;
-    const bool ok = !KC::PRED || unit < KC::UNITS;
-    const uint4* src = reinterpret_cast<const uint4*>(x_s + (size_t)(slice * KC::SLICE_WORDS + unit * KC::U) * 8);
-    float s = 0.f;
+  for (int o = 16; o > 0; o >>= 1) sx += __shfl_xor_sync(0xffffffffu, sx, o);
+  // element c = 4 * (lane % 4) + e of its 16-block: the pair (c, c+1) goes to half2 slot 2 * ((c % 8) / 2) + c / 8
+  const int c = (lane & 3) * 4;
+  __half2* dst = reinterpret_cast<__half2*>(xh_group + (lane >> 2) * 16);
+  __syncwarp();                               // in-place use: every lane has read its source words
+  dst[((c % 8) / 2) * 2 + (c / 8)] = h01;
+  dst[(((c + 2) % 8) / 2) * 2 + ((c + 2) / 8)] = h23;
+  if (lane == 0) *xf_group = make_float4(inv * 16777216.f, inv * 1048576.f, -8.f * sx, sx);
+}
+
+// ------------------------------------------------------------------------------------------------ tile x vector
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_bf16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return __uint_as_float(((uint32_t)v) << 16);
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16_first(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// One slice (NB blocks) of one tile against the staged activations. RT <= 8: on return every lane with lane / 4 % RT == r
+// holds the slice's total of tile row r in out_lo. RT == 16: lane 4g holds row g in out_lo and row g + 8 in out_hi.
+template <class C, bool HZ>
+__device__ __forceinline__ void tile_dot(const uint8_t* tile, int slice, const XStage& x, int lane, float& out_lo,
+                                         float& out_hi) {
+  constexpr int RT = C::RT, NB = C::NB;
+  const int g = lane >> 2, t = lane & 3;
+  const int jl = g / RT, jh = (g + 8) / RT, jb = g % C::NJ;
+  const int rl = g % RT, rh = (g + 8) % RT;
+  const int b0 = C::KS == 1 ? 0 : slice * NB;
+  const uint32_t tb = smem_u32(tile);
+  const uint32_t wa = tb + (uint32_t)(b0 * 32 + lane) * 16;
+  const uint32_t xbase = smem_u32(x.xh) + (uint32_t)(jb * (C::K / C::NJ) + 4 * t) * 2 + (uint32_t)b0 * 128;
+  uint32_t xa[4];
 #pragma unroll
-    for (int w = 0; w < KC::U; w++) {
-      uint4 v = ok ? src[w] : make_uint4(0, 0, 0, 0);
-#if FB_DOT == 0
-      x.p[i][4 * w + 0] = v.x; x.p[i][4 * w + 1] = v.y; x.p[i][4 * w + 2] = v.z; x.p[i][4 * w + 3] = v.w;
-#else
-      x.p[i][8 * w + 0] = bflo(v.x); x.p[i][8 * w + 1] = bfhi(v.x); x.p[i][8 * w + 2] = bflo(v.y); x.p[i][8 * w + 3] = bfhi(v.y);
-      x.p[i][8 * w + 4] = bflo(v.z); x.p[i][8 * w + 5] = bfhi(v.z); x.p[i][8 * w + 6] = bflo(v.w); x.p[i][8 * w + 7] = bfhi(v.w);
-#endif
-      s += bflo(v.x); s += bfhi(v.x); s += bflo(v.y); s += bfhi(v.y);
-      s += bflo(v.z); s += bfhi(v.z); s += bflo(v.w); s += bfhi(v.w);
+  for (int i = 0; i < 4; i++) xa[i] = xbase + 32 * ((i + jb) & 3);
+  const uint32_t ml = tb + C::NIB + (uint32_t)(jl * C::RG * RT + rl) * 2;
+  const uint32_t mh = tb + C::NIB + (uint32_t)(jh * C::RG * RT + rh) * 2;
+  const uint32_t fl = smem_u32(x.xf) + (uint32_t)(jl * C::RG) * 16, fh = smem_u32(x.xf) + (uint32_t)(jh * C::RG) * 16;
+  float ct[4] = {0.f, 0.f, 0.f, 0.f}, cg[4];
+  float zl = 0.f, zh = 0.f;
+  uint4 w4 = lds128(wa);
+  uint2 xb[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) xb[i] = lds64(xa[i]);
+  const bool odd0 = (NB % 2 == 0) ? false : (b0 & 1);           // the slice starts in the middle of a round
+#pragma unroll
+  for (int bi = 0; bi < NB; bi++) {
+    uint4 wn;
+    uint2 xn[4];
+    if (bi + 1 < NB) {                                           // next block's operands are in flight during this one
+      wn = lds128(wa + (bi + 1) * 512);
+#pragma unroll
+      for (int i = 0; i < 4; i++) xn[i] = lds64(xa[i] + (bi + 1) * 128);
     }
-    x.sum[i] = s;
-  }
-}
-
-#if FB_DOT == 0
-// One packed word (8 nibbles) against 8 activations: acc += sum_k (1 + nib_k/16) * x_k, exact products, fp32 adds.
-// ((w >> (4j-3)) & 0x00780078) | 0x3F803F80 is the bf16 pair (1 + nib_j/16, 1 + nib_{j+4}/16): the nibble sits in the
-// top four mantissa bits. fma.rn.f32.bf16 multiplies two bf16 scalars into an fp32 accumulator in one instruction.
-// The caller removes the offset: sum_k (nib_k - 8) x_k = 16 * (acc - 1.5 * sum_k x_k). (Putting the nibble in the LOW
-// mantissa bits saves one shift but makes the offset 136 instead of 1.5, and the cancellation then costs ~7 bits of
-// the fp32 sum: enough to flip bf16 roundings downstream.)
-constexpr float kDotOffset = 1.5f;
-constexpr float kDotScale = 16.f;
-__device__ __forceinline__ void dot_word(uint32_t w, const uint32_t* x, float& a0, float& a1) {
-  const uint32_t M = 0x00780078u, C = 0x3F803F80u;
-  const uint32_t t0 = ((w << 3) & M) | C, t1 = ((w >> 1) & M) | C, t2 = ((w >> 5) & M) | C, t3 = ((w >> 9) & M) | C;
-  asm("{ .reg .b16 tl, th, xl, xh, yl, yh;\n"
-      "mov.b32 {tl,th}, %2; mov.b32 {xl,xh}, %6; mov.b32 {yl,yh}, %8;\n"
-      "fma.rn.f32.bf16 %0, tl, xl, %0; fma.rn.f32.bf16 %1, th, yl, %1;\n"
-      "mov.b32 {tl,th}, %3;\n"
-      "fma.rn.f32.bf16 %0, tl, xh, %0; fma.rn.f32.bf16 %1, th, yh, %1;\n"
-      "mov.b32 {tl,th}, %4; mov.b32 {xl,xh}, %7; mov.b32 {yl,yh}, %9;\n"
-      "fma.rn.f32.bf16 %0, tl, xl, %0; fma.rn.f32.bf16 %1, th, yl, %1;\n"
-      "mov.b32 {tl,th}, %5;\n"
-      "fma.rn.f32.bf16 %0, tl, xh, %0; fma.rn.f32.bf16 %1, th, yh, %1; }\n"
-      : "+f"(a0), "+f"(a1)
-      : "r"(t0), "r"(t1), "r"(t2), "r"(t3), "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]));
-}
-constexpr int kXPerWord = 4;
-#else
-// One packed word against 8 fp32 activations. Byte b of ((w << 3) & 0x78787878) | 0x80808080 is 0x80 | nib_{2b} << 3;
-// one PRMT drops it under 0x3F into bits 16..23 of a float: 0x3F800000 | nib << 19 = 1 + nib/16 exactly. So
-// acc += sum_k (1 + nib_k/16) x_k and the caller uses sum_k (nib_k - 8) x_k = 16 * (acc - 1.5 * sum_k x_k).
-constexpr float kDotOffset = 1.5f;
-constexpr float kDotScale = 16.f;
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ void dot_word(uint32_t w, const float* x, float& a0, float& a1) {
-  const uint32_t e = ((w << 3) & 0x78787878u) | 0x80808080u, o = ((w >> 1) & 0x78787878u) | 0x80808080u;
+    const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+    const bool first = (bi == 0) || (((bi & 1) != 0) == odd0);   // block b0 + bi opens a round
 #pragma unroll
-  for (int b = 0; b < 4; b++) {
-    const float fe = __uint_as_float(prmt(e, 0x3F000000u, 0x7044u | (b << 8)));
-    const float fo = __uint_as_float(prmt(o, 0x3F000000u, 0x7044u | (b << 8)));
-    a0 = fmaf(fe, x[2 * b], a0);
-    a1 = fmaf(fo, x[2 * b + 1], a1);
-  }
-}
-constexpr int kXPerWord = 8;
-#endif
-
-// RB rows of one tile against the lane's activations: acc[r] += sum over the lane's units of s*(dot) [+ z*sum x].
-// `rows` are byte offsets of the RB records inside the tile (clamped by the caller for ragged tails).
-template <class KC, bool HZ, class XR>
-__device__ __forceinline__ void rowblock_dot(const uint8_t* tile, const int (&rows)[KC::RB], int slice, int lane,
-                                             const XR& x, float (&acc)[KC::RB]) {
-  constexpr int K = KC::K;
-#pragma unroll
-  for (int i = 0; i < KC::NI; i++) {
-    const int unit = lane + 32 * i;
-    const bool ok = !KC::PRED || unit < KC::UNITS;
-    const int word = slice * KC::SLICE_WORDS + (ok ? unit : 0) * KC::U;
-    const int g = word >> 4;
-    const float off = kDotOffset * x.sum[i];
-#pragma unroll
-    for (int r = 0; r < KC::RB; r++) {
-      const uint8_t* rec = tile + rows[r];
-      float p0 = 0.f, p1 = 0.f;
-      if (KC::U == 2) {
-        const uint2 w = *reinterpret_cast<const uint2*>(rec + 4 * word);
-        dot_word(w.x, &x.p[i][0], p0, p1);
-        dot_word(w.y, &x.p[i][kXPerWord], p0, p1);
-      } else {
-        const uint4 w = *reinterpret_cast<const uint4*>(rec + 4 * word);
-        dot_word(w.x, &x.p[i][0], p0, p1);
-        dot_word(w.y, &x.p[i][kXPerWord], p0, p1);
-        dot_word(w.z, &x.p[i][2 * kXPerWord], p0, p1);
-        dot_word(w.w, &x.p[i][3 * kXPerWord], p0, p1);
-      }
-      const float s = bf2f(*reinterpret_cast<const uint16_t*>(rec + K / 2 + 2 * g)) * kDotScale;
-      const float t = (p0 + p1) - off;
-      acc[r] = fmaf(s, t, acc[r]);
-      if (HZ) {
-        const float z = bf2f(*reinterpret_cast<const uint16_t*>(rec + K / 2 + K / 64 + 2 * g));
-        acc[r] = fmaf(z, x.sum[i], acc[r]);
+    for (int i = 0; i < 4; i++) {
+      const uint32_t w2 = ws[i] >> 8;
+      const uint32_t a[4] = {ws[i] & 0x000F000Fu, ws[i] & 0x00F000F0u, w2 & 0x000F000Fu, w2 & 0x00F000F0u};
+      if (first && i == 0) mma_f16_first(cg, a, xb[i].x, xb[i].y);
+      else mma_f16(cg, a, xb[i].x, xb[i].y);
+    }
+    const bool closes = (((bi & 1) != 0) != odd0);               // block b0 + bi closes a round
+    if (closes || bi == NB - 1) {
+      const uint32_t ro = (NB % 2 == 0) ? (uint32_t)(b0 >> 1) + (bi >> 1) : (uint32_t)((b0 + bi) >> 1);
+      const float4 Fl = lds128f(fl + ro * 16), Fh = lds128f(fh + ro * 16);
+      const float sl = lds_bf16(ml + ro * RT * 2), sh = lds_bf16(mh + ro * RT * 2);
+      const float sl2 = sl * Fl.x, sh2 = sh * Fh.y;
+      ct[0] = fmaf(sl2, cg[0], ct[0]); ct[1] = fmaf(sl2, cg[1], ct[1]);
+      ct[2] = fmaf(sh2, cg[2], ct[2]); ct[3] = fmaf(sh2, cg[3], ct[3]);
+      if (closes) {                                              // once per (row, group): offset and zero point
+        zl = fmaf(sl, Fl.z, zl);
+        zh = fmaf(sh, Fh.z, zh);
+        if (HZ) {
+          zl = fmaf(lds_bf16(ml + C::G * RT * 2 + ro * RT * 2), Fl.w, zl);
+          zh = fmaf(lds_bf16(mh + C::G * RT * 2 + ro * RT * 2), Fh.w, zh);
+        }
       }
     }
-  }
-}
-
-// Sum acc[r] over the 32 lanes for RB <= 4 rows with a transposed butterfly (6 shuffles for 4 rows instead of 20).
-// On return lane (r << 3) holds the total of row r in `out`.
-template <int RB>
-__device__ __forceinline__ float reduce_rows(float (&acc)[RB], int lane) {
-  float a[4];
+    if (bi + 1 < NB) {
+      w4 = wn;
 #pragma unroll
-  for (int r = 0; r < 4; r++) a[r] = r < RB ? acc[r] : 0.f;
-  const bool hi16 = lane & 16, hi8 = lane & 8;
-  const float s0 = hi16 ? a[0] : a[2], s1 = hi16 ? a[1] : a[3];
-  const float k0 = hi16 ? a[2] : a[0], k1 = hi16 ? a[3] : a[1];
-  const float b0 = k0 + __shfl_xor_sync(0xffffffffu, s0, 16);
-  const float b1 = k1 + __shfl_xor_sync(0xffffffffu, s1, 16);
-  float c = (hi8 ? b1 : b0) + __shfl_xor_sync(0xffffffffu, hi8 ? b0 : b1, 8);
-  c += __shfl_xor_sync(0xffffffffu, c, 4);
-  c += __shfl_xor_sync(0xffffffffu, c, 2);
-  c += __shfl_xor_sync(0xffffffffu, c, 1);
-  return c;   // row index = (lane >> 3): bit4 -> +2, bit3 -> +1
+      for (int i = 0; i < 4; i++) xb[i] = xn[i];
+    }
+  }
+  // valid outputs: MMA row g -> column jl, MMA row g + 8 -> column jh
+  const float vl = (jl == 2 * t) ? ct[0] + zl : ((jl == 2 * t + 1) ? ct[1] + zl : 0.f);
+  const float vh = (jh == 2 * t) ? ct[2] + zh : ((jh == 2 * t + 1) ? ct[3] + zh : 0.f);
+  if (RT <= 8) {
+    float v = vl + vh;
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+#pragma unroll
+    for (int o = 4 * RT; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    out_lo = v;
+    out_hi = 0.f;
+  } else {
+    out_lo = vl;
+    out_hi = vh;
+  }
 }
 
 }  // namespace fb

@@ -1,241 +1,21 @@
-// The persistent cooperative decode megakernel and the stand-alone GEMV that shares its weight pipeline.
+// Decode megakernel, data-flow synchronisation.
 //
-// One CTA per SM: warp 16 (lane 0) is the producer, it walks the CTA's static list of weight tiles for the whole
-// step and issues 1-D bulk copies into an 8-stage shared-memory ring; it never waits for activations, so weights
-// for the next phase stream in while the consumers sit in a grid barrier. Warps 0..15 are consumers in 4 groups.
+// Phases of one token are chained by DATA, not by grid barriers: every vector that crosses CTAs (residual h, q / new
+// k / new v, attention output, SwiGLU activations, arg-max candidates) lives in global memory as 8-byte words that
+// carry their payload (two bf16 values or one fp32/int32) together with a 32-bit tag unique to (launch, layer,
+// phase). A producer stores the word once; a consumer polls the word itself until the tag matches, so the value
+// arrives with the same L2 round trip that a barrier would only have announced. Each hop costs about one L2 round
+// trip instead of three (barrier arrive, barrier poll, data fetch).
+//
+// Why single buffers are enough: every phase consumes a vector that ALL CTAs contributed to, so a CTA can only be
+// one full phase ahead of the slowest one; a buffer is rewritten two phases after its last reader at the earliest.
 #pragma once
-#include "fb_common.cuh"
+#include "fb_pipe.cuh"
 
 namespace fb {
 
-struct Pipe {
-  uint8_t* stages;
-  uint64_t* full;
-  uint64_t* empty;
-  uint32_t it;       // running tile counter; producer and consumers walk the same sequence
-  uint32_t max_fly;  // producer only: bulk copies allowed in flight at once (<= kStages)
-};
-
-struct Smem {
-  uint8_t* stages;
-  uint8_t* scratch;
-  uint16_t* x_s;       // bf16 activations of the current phase
-  float* res_s;        // per-row results of the current phase
-  uint64_t* full;
-  uint64_t* empty;
-  volatile int* s_abort;
-  float* red;          // 32 floats for block reductions
-  int* misc;           // 32 ints
-  float* part;         // [groups][2][4 warps][4] slice partials of sliced-K phases
-  float* hown;         // [kMaxOwnRows] this CTA's rows of the residual stream
-  float* qpart;        // [kStages][2 blocks][4 slices][4 rows] slice partials of the block-queue GEMV
-  int* tdone;          // [kStages] units finished per tile in flight
-  int* bcnt;           // [kStages][2] slices finished per block
-};
-
-__device__ __forceinline__ Smem carve_smem(uint8_t* base) {
-  Smem s;
-  s.stages = base;
-  s.scratch = base + kStages * kStageBytes;
-  s.x_s = reinterpret_cast<uint16_t*>(s.scratch);
-  s.res_s = reinterpret_cast<float*>(s.scratch + kXBytes);
-  uint8_t* tail = s.scratch + kScratchBytes;
-  s.full = reinterpret_cast<uint64_t*>(tail);
-  s.empty = s.full + kStages;
-  s.s_abort = reinterpret_cast<volatile int*>(tail + 128);
-  s.red = reinterpret_cast<float*>(tail + 256);
-  s.misc = reinterpret_cast<int*>(tail + 384);
-  s.part = reinterpret_cast<float*>(tail + 512);
-  s.hown = reinterpret_cast<float*>(tail + 1024);
-  s.qpart = reinterpret_cast<float*>(tail + 2048);
-  s.tdone = reinterpret_cast<int*>(tail + 3072);
-  s.bcnt = reinterpret_cast<int*>(tail + 3104);
-  return s;
-}
-
-// rows [r0, r1) of a phase that CTA b of G owns; `unit` rows stay together (2 for RoPE / gate-up pairs)
-__device__ __forceinline__ void cta_rows(int rows, int unit, int b, int G, int& r0, int& r1) {
-  const long long nu = rows / unit;
-  r0 = (int)((nu * b) / G) * unit;
-  r1 = (int)((nu * (b + 1)) / G) * unit;
-}
-
-// ------------------------------------------------------------------------------------------------ producer side
-__device__ __forceinline__ bool produce_rows(Pipe& p, const uint8_t* src, int nrows, int tile_rows, int rec,
-                                             const WaitCtl& wc, int layer) {
-  for (int r = 0; r < nrows; r += tile_rows) {
-    const int n = min(tile_rows, nrows - r);
-    const uint32_t bytes = (uint32_t)n * rec;
-    const int s = p.it % kStages;
-    const uint32_t ph = (p.it / kStages) & 1;
-    if (!mbar_wait(&p.empty[s], ph ^ 1, wc, W_EMPTY, layer)) return false;   // p.it counts issued tiles only
-    // Keep the memory system's queues short: with the whole ring in flight (27 MB over 148 SMs) every small
-    // latency-critical access of the consumers (flags, tagged words) waits microseconds behind bulk weight traffic.
-    if (p.it >= p.max_fly) {
-      const uint32_t j = p.it - p.max_fly;
-      if (!mbar_wait(&p.full[j % kStages], (j / kStages) & 1, wc, W_FULL, layer)) return false;
-    }
-    mbar_expect_tx(&p.full[s], bytes);
-    bulk_g2s(p.stages + (size_t)s * kStageBytes, src + (size_t)r * rec, bytes, &p.full[s]);
-    p.it++;
-  }
-  return true;
-}
-
-// Before the CTA may exit, every bulk copy it issued must have landed. In a clean run the consumers have already
-// waited for all of them; after a failed wait the last (up to) kStages issued tiles may still be in flight.
-__device__ __forceinline__ void producer_drain(Pipe& p, const WaitCtl& wc) {
-  if (*wc.s_abort == 0) return;
-  const uint32_t n = p.it < (uint32_t)kStages ? p.it : (uint32_t)kStages;
-  for (uint32_t k = 0; k < n; k++) {
-    const uint32_t it = p.it - 1 - k;
-    const int s = it % kStages;
-    const uint32_t ph = (it / kStages) & 1;
-    for (unsigned i = 0; i < wc.limit; i++) {
-      if (mbar_try(&p.full[s], ph)) break;
-      if ((i & 1023) == 1023) __nanosleep(64);
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------------ consumer side
-// GEMV over this CTA's `nrows` rows of one phase. Results land in res_s[row * KS + slice].
-template <class KC, bool HZ>
-__device__ __forceinline__ void consume_rows(Pipe& p, int nrows, const XRegs<KC>& x, float* res_s, int cw, int lane,
-                                             const WaitCtl& wc, int layer) {
-  constexpr int RB = KC::RB, TR = KC::TILE_ROWS;
-  const int grp = cw >> 2, wg = cw & 3;
-  const int slice = wg % KC::KS, sub = wg / KC::KS;
-  const int rec = rec_bytes_of(KC::K, HZ);
-  const int ntiles = (nrows + TR - 1) / TR;
-  for (int t = 0; t < ntiles; t++) {
-    const uint32_t it = p.it + t;
-    if ((int)(it % kGroups) != grp) continue;
-    const int s = it % kStages;
-    const uint32_t ph = (it / kStages) & 1;
-    const bool ok = mbar_wait(&p.full[s], ph, wc, W_FULL, layer);
-    const int row0 = t * TR;
-    const int tr = min(TR, nrows - row0);
-    const uint8_t* tile = p.stages + (size_t)s * kStageBytes;
-    if (ok) {
-      for (int b = sub; b * RB < tr; b += KC::NSUB) {
-        int rows[RB];
-#pragma unroll
-        for (int r = 0; r < RB; r++) rows[r] = min(b * RB + r, tr - 1) * rec;
-        float acc[RB];
-#pragma unroll
-        for (int r = 0; r < RB; r++) acc[r] = 0.f;
-        rowblock_dot<KC, HZ>(tile, rows, slice, lane, x, acc);
-        const float c = reduce_rows<RB>(acc, lane);
-        const int r = lane >> 3;
-        if ((lane & 7) == 0 && r < RB && b * RB + r < tr) res_s[(row0 + b * RB + r) * KC::KS + slice] = c;
-      }
-    }
-    named_bar_sync(kBarGroup0 + grp, kWarpsPerGroup * 32);   // the group's 4 warps are done with this tile
-    if (ok && wg == 0 && lane == 0) mbar_arrive(&p.empty[s]);
-  }
-  p.it += ntiles;
-}
-
-// sum of slice partials of local row r
-template <class KC>
-__device__ __forceinline__ float row_result(const float* res_s, int r) {
-  float v = res_s[r * KC::KS];
-#pragma unroll
-  for (int s = 1; s < KC::KS; s++) v += res_s[r * KC::KS + s];
-  return v;
-}
-
-// ---- activation staging: every consumer thread calls; ends with a consumer-wide barrier ----
-__device__ __forceinline__ void stage_x_plain(const uint16_t* gx, int K, uint16_t* x_s, int tid_c) {
-  const int n16 = K / 8;
-  for (int j = tid_c; j < n16; j += kConsumerThreads)
-    reinterpret_cast<uint4*>(x_s)[j] = ld_cg_v4(reinterpret_cast<const uint4*>(gx) + j);
-  named_bar_sync(kBarConsumers, kConsumerThreads);
-}
-
-// xn = bf16( (float(h) * r) * float(w) ), r = 1/sqrt(mean(h^2) + eps); up to 2 eight-value chunks per thread
-__device__ __forceinline__ void stage_x_norm(const uint16_t* gh, const uint16_t* gw, int D, float eps, uint16_t* x_s,
-                                             float* red, int tid_c) {
-  const int n16 = D / 8;
-  uint4 hv[2], wv[2];
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < 2; c++) {
-    const int j = tid_c + c * kConsumerThreads;
-    hv[c] = make_uint4(0, 0, 0, 0); wv[c] = make_uint4(0, 0, 0, 0);
-    if (j < n16) {
-      hv[c] = ld_cg_v4(reinterpret_cast<const uint4*>(gh) + j);
-      wv[c] = __ldg(reinterpret_cast<const uint4*>(gw) + j);
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < 2; c++) {
-    const float hf[8] = {bflo(hv[c].x), bfhi(hv[c].x), bflo(hv[c].y), bfhi(hv[c].y), bflo(hv[c].z), bfhi(hv[c].z), bflo(hv[c].w), bfhi(hv[c].w)};
-#pragma unroll
-    for (int e = 0; e < 8; e++) ss = fmaf(hf[e], hf[e], ss);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if ((tid_c & 31) == 0) red[tid_c >> 5] = ss;
-  named_bar_sync(kBarConsumers, kConsumerThreads);
-  float tot = 0.f;
-#pragma unroll
-  for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
-  const float r = 1.0f / sqrtf(tot / (float)D + eps);
-#pragma unroll
-  for (int c = 0; c < 2; c++) {
-    const int j = tid_c + c * kConsumerThreads;
-    if (j < n16) {
-      const float hf[8] = {bflo(hv[c].x), bfhi(hv[c].x), bflo(hv[c].y), bfhi(hv[c].y), bflo(hv[c].z), bfhi(hv[c].z), bflo(hv[c].w), bfhi(hv[c].w)};
-      const float wf[8] = {bflo(wv[c].x), bfhi(wv[c].x), bflo(wv[c].y), bfhi(wv[c].y), bflo(wv[c].z), bfhi(wv[c].z), bflo(wv[c].w), bfhi(wv[c].w)};
-      uint32_t o[4];
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const uint32_t lo = f2bf(hf[2 * e] * r * wf[2 * e]), hi = f2bf(hf[2 * e + 1] * r * wf[2 * e + 1]);
-        o[e] = lo | (hi << 16);
-      }
-      reinterpret_cast<uint4*>(x_s)[j] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-  }
-  named_bar_sync(kBarConsumers, kConsumerThreads);
-}
-
-// ------------------------------------------------------------------------------------------------ grid barrier
-struct GridBar {
-  unsigned* ctr;
-  unsigned target;   // meaningful in consumer thread 0 only
-};
-
-// All 512 consumer threads call. Release/acquire at gpu scope through one counter; the wait is bounded.
-__device__ __forceinline__ void grid_barrier(GridBar& gb, const WaitCtl& wc, int tid_c, int layer) {
-  named_bar_sync(kBarConsumers, kConsumerThreads);
-  if (tid_c == 0) {
-    gb.target += gridDim.x;
-    if (*wc.s_abort == 0) {
-      __threadfence();
-      red_release_add(gb.ctr, 1u);
-      bool done = false;
-      unsigned seen = 0;
-      for (unsigned i = 0; i < wc.limit; i++) {
-        seen = ld_acquire_u32(gb.ctr);
-        if ((int)(seen - gb.target) >= 0) { done = true; break; }
-        if ((i & 255) == 255) {
-          if (ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
-          __nanosleep(32);
-        }
-      }
-      if (!done && *wc.s_abort == 0) report_fail(wc, W_GRIDBAR, layer, (int)gb.target, (int)seen);
-      __threadfence();
-    }
-  }
-  named_bar_sync(kBarConsumers, kConsumerThreads);
-}
-
-// ------------------------------------------------------------------------------------------------ attention
-// GQA flash-decode for one (kv head, chunk of positions) item per CTA. A row of K or V (HD bf16) is spread over
-// HD/8 lanes (16 bytes each); a warp handles 32/SEG positions per step, its 16 warps stride through the chunk.
-// The R query heads of the group share every K/V load.
+// GQA flash-decode geometry: a row of K or V (HD bf16) is spread over HD/8 lanes (16 bytes each); a warp handles
+// 32/SEG positions per step. The R query heads of a group share every K/V load.
 template <int HD, int R>
 struct AttnCfg {
   static constexpr int LPR = HD / 8;
@@ -244,38 +24,278 @@ struct AttnCfg {
   static_assert(HD % 8 == 0 && LPR <= 16, "head_dim must be a multiple of 8 and <= 128");
 };
 
-struct AttnArgs {
-  const uint16_t* qbuf;   // bf16 [NH*HD], post-RoPE queries of this step
-  const uint16_t* kc;     // layer base: bf16 [max_seq, NKV, HD]
+// ------------------------------------------------------------------------------------------------ tagged words
+__device__ __forceinline__ void ll_store(uint64_t* p, uint32_t payload, uint32_t tag) {
+  const uint64_t v = ((uint64_t)tag << 32) | payload;
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void ll_load2(const uint64_t* p, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ uint64_t ll_load1(const uint64_t* p) {
+  uint64_t a;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+
+// words exchanged between GPUs (peer stores over NVLink, polled in local memory): system scope
+__device__ __forceinline__ void ll_store_sys(uint64_t* p, uint32_t payload, uint32_t tag) {
+  const uint64_t v = ((uint64_t)tag << 32) | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ll_load_sys(const uint64_t* p) {
+  uint64_t a;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+// bounded poll of one word written by another GPU; returns the payload (0 after a failure)
+__device__ __forceinline__ uint32_t ll_poll_sys(const uint64_t* p, uint32_t tag, const WaitCtl& wc, int layer) {
+  for (unsigned spin = 0;; spin++) {
+    const uint64_t v = ll_load_sys(p);
+    if ((uint32_t)(v >> 32) == tag) return (uint32_t)v;
+    if (*wc.s_abort) return 0;
+    if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; return 0; }
+    if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, -3); return 0; }
+  }
+}
+
+// Poll `nwords` (even, 16-byte aligned base) tagged words into 32-bit payloads dst[0..nwords). Threads
+// tid, tid+nthreads, ... each own word pairs; all of a thread's loads are issued before any is checked.
+template <int MAXP>
+__device__ __forceinline__ void ll_gather(const uint64_t* src, int nwords, uint32_t tag, uint32_t* dst, int tid,
+                                          int nthreads, const WaitCtl& wc, int layer) {
+  const int npairs = nwords >> 1;
+  uint32_t pending = 0;
+#pragma unroll
+  for (int k = 0; k < MAXP; k++)
+    if (tid + k * nthreads < npairs) pending |= 1u << k;
+  for (unsigned spin = 0; pending; spin++) {
+    uint64_t a[MAXP], b[MAXP];
+#pragma unroll
+    for (int k = 0; k < MAXP; k++)
+      if (pending & (1u << k)) ll_load2(src + 2 * (size_t)(tid + k * nthreads), a[k], b[k]);
+#pragma unroll
+    for (int k = 0; k < MAXP; k++)
+      if (pending & (1u << k)) {
+        if ((uint32_t)(a[k] >> 32) == tag && (uint32_t)(b[k] >> 32) == tag) {
+          const int j = 2 * (tid + k * nthreads);
+          dst[j] = (uint32_t)a[k];
+          dst[j + 1] = (uint32_t)b[k];
+          pending &= ~(1u << k);
+        }
+      }
+    if (pending) {
+      if (*wc.s_abort) break;
+      if (spin > 16) __nanosleep(40);
+      if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+      if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, -1); break; }
+    }
+  }
+}
+
+// Arrival flags: polling the tagged data words directly from 75 000 threads floods the few L2 lines that hold a
+// vector, so a CTA first waits (one warp, a handful of coalesced loads per round) until every producer CTA has posted
+// its arrival flag, and only then gathers the words. The flag is posted without a fence, so the tags in the words
+// stay the correctness check: a word that lags behind its flag is simply polled again.
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// flags are posted with an atomic exchange: it is performed at L2 at once instead of waiting in the SM's store path
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.relaxed.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  (void)old;
+}
+// all consumer threads call; warp 0 polls flags[0..n) until each equals tag
+__device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
+                                           int layer) {
+  if (cw == 0) {
+    for (unsigned spin = 0;; spin++) {
+      // all loads of a round are issued before any is compared (n <= 256: at most 8 per lane)
+      uint32_t v[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
+      bool ok = true;
+#pragma unroll
+      for (int j = 0; j < 8; j++) ok = ok && (v[j] == tag);
+      if (__all_sync(0xffffffffu, ok)) break;
+      int stop = 0;
+      if (lane == 0) {
+        if (*wc.s_abort) stop = 1;
+        else if ((spin & 63) == 63 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; stop = 1; }
+        else if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, n); stop = 1; }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) break;
+    }
+  }
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+// a warp that has finished its part of a phase calls this; the CTA's last warp posts the flag
+__device__ __forceinline__ void post_when_cta_done(int* s_done, uint32_t* flag, uint32_t tag, int lane,
+                                                   long long* dbg = nullptr) {
+  __syncwarp();
+  if (lane == 0) {
+    const int old = atomicAdd(s_done, 1);
+    if (old == kConsumerWarps - 1) {
+      *s_done = 0;
+      st_relaxed_u32(flag, tag);
+      if (dbg) dbg[12] = (long long)globaltimer_ns();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ staging from tagged vectors
+// Both functions leave the phase's activations in sm.xh / sm.xf (fp16 in B-operand order + per-group factors) and end
+// with a consumer-wide barrier. A thread owns the 4 elements 4*pr .. 4*pr+3 for pr = tid_c, tid_c + kConsumerThreads, ...
+// so a warp owns whole groups of 128 and converts them in place.
+// xn = bf16( (float(h) * r) * float(w) ) from the tagged residual vector (dim/2 words)
+template <int MAXP>
+__device__ __forceinline__ void stage_norm_ll(const uint64_t* hll, const uint32_t* flags, int nflags, uint32_t tag,
+                                              const uint16_t* gw, int D, float eps, const Smem& sm, int tid_c,
+                                              const WaitCtl& wc, int layer, bool have_h, long long* dbg = nullptr) {
+  uint32_t* xs32 = reinterpret_cast<uint32_t*>(sm.xh);
+  float* red = sm.red;
+  const int npairs = D / 4, lane = tid_c & 31;
+  uint2 wv[MAXP];                       // norm weights do not depend on the wait: fetch them first
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    wv[k] = pr < npairs ? __ldg(reinterpret_cast<const uint2*>(gw) + pr) : make_uint2(0, 0);
+  }
+  if (!have_h) {      // layer 0 finds the raw residual (bf16, natural order) already in place
+    wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+    if (dbg && tid_c == 0) dbg[10] = (long long)globaltimer_ns();
+    ll_gather<MAXP>(hll, D / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
+    if (dbg && tid_c == 0) dbg[11] = (long long)globaltimer_ns();
+  }
+  // each thread squares the pairs it gathered itself: no barrier needed before this
+  uint2 raw[MAXP];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    raw[k] = make_uint2(0, 0);
+    if (pr < npairs) {
+      const uint32_t a = xs32[2 * pr], b = xs32[2 * pr + 1];
+      raw[k] = make_uint2(a, b);
+      ss = fmaf(bflo(a), bflo(a), ss); ss = fmaf(bfhi(a), bfhi(a), ss);
+      ss = fmaf(bflo(b), bflo(b), ss); ss = fmaf(bfhi(b), bfhi(b), ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (lane == 0) red[tid_c >> 5] = ss;
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
+  const float r = 1.0f / sqrtf(tot / (float)D + eps);
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;      // warp-uniform bound: npairs is a multiple of 32
+    if (pr < npairs) {
+      const uint32_t a = raw[k].x, b = raw[k].y;
+      const uint32_t o0 = (uint32_t)f2bf(bflo(a) * r * bflo(wv[k].x)) | ((uint32_t)f2bf(bfhi(a) * r * bfhi(wv[k].x)) << 16);
+      const uint32_t o1 = (uint32_t)f2bf(bflo(b) * r * bflo(wv[k].y)) | ((uint32_t)f2bf(bfhi(b) * r * bfhi(wv[k].y)) << 16);
+      const int grp = pr >> 5;
+      stage_group_fp16(o0, o1, sm.xh + grp * 128, sm.xf + grp, lane);
+    }
+  }
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
+template <int MAXP>
+__device__ __forceinline__ void stage_plain_ll(const uint64_t* src, const uint32_t* flags, int nflags, uint32_t tag, int K,
+                                               const Smem& sm, int tid_c, const WaitCtl& wc, int layer) {
+  uint32_t* xs32 = reinterpret_cast<uint32_t*>(sm.xh);
+  const int npairs = K / 4, lane = tid_c & 31;
+  wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+  ll_gather<MAXP>(src, K / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
+  // a thread converts exactly the words it gathered itself
+#pragma unroll
+  for (int k = 0; k < MAXP; k++) {
+    const int pr = tid_c + k * kConsumerThreads;
+    if (pr < npairs) {
+      const uint32_t a = xs32[2 * pr], b = xs32[2 * pr + 1];
+      const int grp = pr >> 5;
+      stage_group_fp16(a, b, sm.xh + grp * 128, sm.xf + grp, lane);
+    }
+  }
+  named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
+// ------------------------------------------------------------------------------------------------ attention (tagged in/out)
+// q and the new k live in "pair-major" tagged words: word (head*HD/2 + p) = (x[p], x[p + HD/2]), which is what one
+// RoPE thread produces. A lane owns pairs 4*sl .. 4*sl+3, i.e. dims {4sl..4sl+3} and {HD/2+4sl..+3}.
+struct Attn2Args {
+  const uint64_t* q_ll;     // [NH * HD/2]
+  const uint64_t* k_ll;     // [NKV * HD/2] new key of this step, pair-major
+  const uint64_t* v_ll;     // [NKV * HD/2] new value, natural order: word w = (v[2w], v[2w+1])
+  uint64_t* ao_ll;          // [NH * HD/2] natural order
+  const uint16_t* kc;       // layer base: bf16 [max_seq, NKV, HD]
   const uint16_t* vc;
-  uint16_t* ao;           // bf16 [NH*HD]
-  float *pm, *pd, *pacc;  // chunk partials [NH, nchunks], [NH, nchunks, HD]
-  int nkv, T, nchunks;
+  uint64_t* part_ll;        // [NKV][maxchunks][R*HD + 2R] tagged chunk partials (acc, then m, then d per head)
+  uint32_t* ao_flags;       // [NKV] arrival flags of the attention output
+  int nkv, pos, nchunks, maxchunks;
   float scale;
+  uint32_t tag_in, tag_part, tag_out;
 };
 
 template <int HD, int R>
-__device__ __forceinline__ void attn_phase(const AttnArgs& a, uint8_t* scratch, int cw, int lane, int tid_c) {
+__device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch, int* misc, int cw, int lane, int tid_c,
+                                            const WaitCtl& wc, int layer) {
   using C = AttnCfg<HD, R>;
-  float* wacc = reinterpret_cast<float*>(scratch);                 // [16][R][HD]
-  float* wm = wacc + kConsumerWarps * R * HD;                      // [16][R]
-  float* wd = wm + kConsumerWarps * R;                             // [16][R]
+  constexpr int HP = HD / 2;
+  float* wacc = reinterpret_cast<float*>(scratch);                 // [CW][R][HD]  (dims in lane order, see below)
+  float* wm = wacc + kConsumerWarps * R * HD;                      // [CW][R]
+  float* wd = wm + kConsumerWarps * R;                             // [CW][R]
+  uint32_t* qs = reinterpret_cast<uint32_t*>(wd + kConsumerWarps * R);   // [R*HP] q pairs, then [HP] k pairs, [HP] v words
+  const int T = a.pos + 1;
   const int items = a.nkv * a.nchunks;
-  const int chunk_len = (a.T + a.nchunks - 1) / a.nchunks;
+  const int chunk_len = (T + a.nchunks - 1) / a.nchunks;
   const int seg = lane / C::SEG, sl = lane % C::SEG;
   const bool active = sl < C::LPR;
-  const int d0 = sl * 8;
   for (int item = blockIdx.x; item < items; item += gridDim.x) {
     const int kvh = item / a.nchunks, c = item % a.nchunks;
-    const int t0 = c * chunk_len, t1 = min(a.T, t0 + chunk_len);
+    const int t0 = c * chunk_len, t1 = min(T, t0 + chunk_len);
+    const bool has_new = (a.pos >= t0 && a.pos < t1);     // the chunk that contains this step's own position
+    // ---- gather q (R heads) and, for the last chunk, the new k / v ----
+    {
+      const int nq = R * HP;
+      const int total = nq + (has_new ? 2 * HP : 0);
+      // one pass: every thread owns at most one word pair of each source
+      uint32_t pending = 0;
+      const int pr = tid_c;
+      if (2 * pr < total) pending = 1;
+      for (unsigned spin = 0; pending; spin++) {
+        const int w = 2 * pr;
+        const uint64_t* src = w < nq ? a.q_ll + (size_t)kvh * R * HP + w
+                            : (w < nq + HP ? a.k_ll + (size_t)kvh * HP + (w - nq) : a.v_ll + (size_t)kvh * HP + (w - nq - HP));
+        uint64_t u, v;
+        ll_load2(src, u, v);
+        if ((uint32_t)(u >> 32) == a.tag_in && (uint32_t)(v >> 32) == a.tag_in) {
+          qs[w] = (uint32_t)u; qs[w + 1] = (uint32_t)v;
+          pending = 0;
+        } else {
+          if (*wc.s_abort) break;
+          if (spin > 16) __nanosleep(40);
+          if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+          if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)a.tag_in, -2); break; }
+        }
+      }
+    }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
     float q[R][8];
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (active) v = ld_cg_v4(a.qbuf + (size_t)(kvh * R + r) * HD + d0);
-      q[r][0] = bflo(v.x); q[r][1] = bfhi(v.x); q[r][2] = bflo(v.y); q[r][3] = bfhi(v.y);
-      q[r][4] = bflo(v.z); q[r][5] = bfhi(v.z); q[r][6] = bflo(v.w); q[r][7] = bfhi(v.w);
-    }
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const uint32_t u = active ? qs[r * HP + 4 * sl + e] : 0u;
+        q[r][e] = bflo(u);        // dim 4sl+e
+        q[r][4 + e] = bfhi(u);    // dim HP+4sl+e
+      }
     float m[R], den[R], acc[R][8];
 #pragma unroll
     for (int r = 0; r < R; r++) {
@@ -283,36 +303,60 @@ __device__ __forceinline__ void attn_phase(const AttnArgs& a, uint8_t* scratch, 
 #pragma unroll
       for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
     }
-    for (int tb = t0 + cw * C::PPW; tb < t1; tb += kConsumerWarps * C::PPW) {
-      const int t = tb + seg;
-      const bool valid = t < t1;
-      uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (valid && active) {
-        const size_t off = ((size_t)t * a.nkv + kvh) * HD + d0;
-        kk = ld_cg_v4(a.kc + off);
-        vv = ld_cg_v4(a.vc + off);
+    constexpr int BATCH = 2;
+    const int stride = kConsumerWarps * C::PPW;
+    for (int tb = t0 + cw * C::PPW; tb < t1; tb += BATCH * stride) {
+      uint2 klo[BATCH], khi[BATCH], vlo[BATCH], vhi[BATCH];
+      bool valid[BATCH];
+#pragma unroll
+      for (int j = 0; j < BATCH; j++) {
+        const int t = tb + j * stride + seg;
+        valid[j] = t < t1;
+        klo[j] = khi[j] = vlo[j] = vhi[j] = make_uint2(0, 0);
+        if (valid[j] && active) {
+          if (t == a.pos) {      // this step's own k / v: from the tagged words (the cache row is for later steps)
+            const uint32_t* kp = qs + R * HP + 4 * sl;
+            const uint32_t* vp = qs + R * HP + HP;
+            klo[j] = make_uint2((kp[0] & 0xffffu) | (kp[1] << 16), (kp[2] & 0xffffu) | (kp[3] << 16));
+            khi[j] = make_uint2((kp[0] >> 16) | (kp[1] & 0xffff0000u), (kp[2] >> 16) | (kp[3] & 0xffff0000u));
+            vlo[j] = make_uint2(vp[2 * sl], vp[2 * sl + 1]);
+            vhi[j] = make_uint2(vp[HP / 2 + 2 * sl], vp[HP / 2 + 2 * sl + 1]);
+          } else {
+            const size_t off = ((size_t)t * a.nkv + kvh) * HD + 4 * sl;
+            klo[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off));
+            khi[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off + HP));
+            vlo[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off));
+            vhi[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off + HP));
+          }
+        }
       }
-      const float kf[8] = {bflo(kk.x), bfhi(kk.x), bflo(kk.y), bfhi(kk.y), bflo(kk.z), bfhi(kk.z), bflo(kk.w), bfhi(kk.w)};
-      const float vf[8] = {bflo(vv.x), bfhi(vv.x), bflo(vv.y), bfhi(vv.y), bflo(vv.z), bfhi(vv.z), bflo(vv.w), bfhi(vv.w)};
 #pragma unroll
-      for (int r = 0; r < R; r++) {
-        float s = 0.f;
+      for (int j = 0; j < BATCH; j++) {
+        if (tb + j * stride >= t1) break;     // warp-uniform
+        const float kf[8] = {bflo(klo[j].x), bfhi(klo[j].x), bflo(klo[j].y), bfhi(klo[j].y),
+                             bflo(khi[j].x), bfhi(khi[j].x), bflo(khi[j].y), bfhi(khi[j].y)};
+        const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
+                             bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
 #pragma unroll
-        for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
+        for (int r = 0; r < R; r++) {
+          float s = 0.f;
 #pragma unroll
-        for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        s *= a.scale;
-        if (valid) {
-          const float m2 = fmaxf(m[r], s);
-          const float corr = __expf(m[r] - m2), w = __expf(s - m2);
-          den[r] = den[r] * corr + w;
+          for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
 #pragma unroll
-          for (int e = 0; e < 8; e++) acc[r][e] = acc[r][e] * corr + w * vf[e];
-          m[r] = m2;
+          for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          s *= a.scale;
+          if (valid[j]) {
+            const float m2 = fmaxf(m[r], s);
+            const float corr = __expf(m[r] - m2), w = __expf(s - m2);
+            den[r] = den[r] * corr + w;
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[r][e] = acc[r][e] * corr + w * vf[e];
+            m[r] = m2;
+          }
         }
       }
     }
-    // merge the warp's segments (positions were interleaved over segments)
+    // merge the warp's segments
 #pragma unroll
     for (int off = C::SEG; off < 32; off <<= 1) {
 #pragma unroll
@@ -333,240 +377,339 @@ __device__ __forceinline__ void attn_phase(const AttnArgs& a, uint8_t* scratch, 
     if (seg == 0 && active) {
 #pragma unroll
       for (int r = 0; r < R; r++) {
-        float* dst = wacc + ((size_t)cw * R + r) * HD + d0;
+        float* dst = wacc + ((size_t)cw * R + r) * HD;
 #pragma unroll
-        for (int e = 0; e < 8; e++) dst[e] = acc[r][e];
+        for (int e = 0; e < 4; e++) { dst[4 * sl + e] = acc[r][e]; dst[HP + 4 * sl + e] = acc[r][4 + e]; }
         if (sl == 0) { wm[cw * R + r] = m[r]; wd[cw * R + r] = den[r]; }
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
-    for (int o = tid_c; o < R * HD; o += kConsumerThreads) {
-      const int r = o / HD, d = o % HD;
+    // ---- merge the CTA's warps; one thread per (head, dim pair) ----
+    constexpr int WPC = R * HD + 2 * R;                       // words of one chunk partial
+    float* own = reinterpret_cast<float*>(scratch + kScratchBytes) - WPC;   // chunk 0 keeps its partial here
+    uint64_t* mine = a.part_ll + ((size_t)kvh * a.maxchunks + c) * WPC;
+    for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
+      const int r = o / HP, d = 2 * (o % HP);
       float gm = -1e30f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; w++) gm = fmaxf(gm, wm[w * R + r]);
-      float D = 0.f, A = 0.f;
+      float Dn = 0.f, A0 = 0.f, A1 = 0.f;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; w++) {
         const float e = __expf(wm[w * R + r] - gm);
-        D += wd[w * R + r] * e;
-        A += wacc[((size_t)w * R + r) * HD + d] * e;
+        Dn += wd[w * R + r] * e;
+        A0 += wacc[((size_t)w * R + r) * HD + d] * e;
+        A1 += wacc[((size_t)w * R + r) * HD + d + 1] * e;
       }
       const int qh = kvh * R + r;
       if (a.nchunks == 1) {
-        a.ao[(size_t)qh * HD + d] = f2bf(A / D);
+        ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
+      } else if (c != 0) {
+        ll_store(mine + r * HD + d, __float_as_uint(A0), a.tag_part);
+        ll_store(mine + r * HD + d + 1, __float_as_uint(A1), a.tag_part);
+        if (d == 0) {
+          ll_store(mine + R * HD + r, __float_as_uint(gm), a.tag_part);
+          ll_store(mine + R * HD + R + r, __float_as_uint(Dn), a.tag_part);
+        }
       } else {
-        a.pacc[((size_t)qh * a.nchunks + c) * HD + d] = A;
-        if (d == 0) { a.pm[qh * a.nchunks + c] = gm; a.pd[qh * a.nchunks + c] = D; }
+        // chunk 0 is the merger: its own partial stays in shared memory (own[] overlays nothing that is still read)
+        own[r * HD + d] = A0; own[r * HD + d + 1] = A1;
+        if (d == 0) { own[R * HD + r] = gm; own[R * HD + R + r] = Dn; }
+      }
+    }
+    const bool merger = (a.nchunks > 1 && c == 0);
+    if (merger) {
+      // chunk 0 of a kv head merges: the other chunks' partials arrive as tagged words, no counter, no fence
+      named_bar_sync(kBarConsumers, kConsumerThreads);        // wacc / wm / wd are dead, own[] is written
+      uint32_t* pg = reinterpret_cast<uint32_t*>(scratch);     // [(nchunks-1)][WPC] payloads
+      const int total = (a.nchunks - 1) * WPC;
+      const uint64_t* src = a.part_ll + ((size_t)kvh * a.maxchunks + 1) * WPC;
+      constexpr int SEGW = 8 * kConsumerThreads;              // words one ll_gather<4> call can own
+      for (int off = 0; off < total; off += SEGW)
+        ll_gather<4>(src + off, min(SEGW, total - off), a.tag_part, pg + off, tid_c, kConsumerThreads, wc, layer);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      const float* pf = reinterpret_cast<const float*>(pg);
+      for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
+        const int r = o / HP, d = 2 * (o % HP);
+        float gm = own[R * HD + r];
+        for (int cc = 0; cc < a.nchunks - 1; cc++) gm = fmaxf(gm, pf[cc * WPC + R * HD + r]);
+        float e = __expf(own[R * HD + r] - gm);
+        float Dn = own[R * HD + R + r] * e, A0 = own[r * HD + d] * e, A1 = own[r * HD + d + 1] * e;
+        for (int cc = 0; cc < a.nchunks - 1; cc++) {
+          e = __expf(pf[cc * WPC + R * HD + r] - gm);
+          Dn += pf[cc * WPC + R * HD + R + r] * e;
+          A0 += pf[cc * WPC + r * HD + d] * e;
+          A1 += pf[cc * WPC + r * HD + d + 1] * e;
+        }
+        const int qh = kvh * R + r;
+        ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
+    if ((a.nchunks == 1 || merger) && tid_c == 0) st_relaxed_u32(a.ao_flags + kvh, a.tag_out);
   }
 }
 
-// merge the chunk partials of every query head (one warp per head)
-template <int HD>
-__device__ __forceinline__ void attn_merge_phase(const AttnArgs& a, int n_head, int cw, int lane) {
-  for (int qh = blockIdx.x * kConsumerWarps + cw; qh < n_head; qh += gridDim.x * kConsumerWarps) {
-    float gm = -1e30f;
-    for (int c = 0; c < a.nchunks; c++) gm = fmaxf(gm, ld_cg_f32(a.pm + qh * a.nchunks + c));
-    float D = 0.f;
-    for (int c = 0; c < a.nchunks; c++) D += ld_cg_f32(a.pd + qh * a.nchunks + c) * __expf(ld_cg_f32(a.pm + qh * a.nchunks + c) - gm);
-    for (int d = lane; d < HD; d += 32) {
-      float A = 0.f;
-      for (int c = 0; c < a.nchunks; c++)
-        A += ld_cg_f32(a.pacc + ((size_t)qh * a.nchunks + c) * HD + d) * __expf(ld_cg_f32(a.pm + qh * a.nchunks + c) - gm);
-      a.ao[(size_t)qh * HD + d] = f2bf(A / D);
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------------ decode kernel
-struct DecodeParams {
-  const uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;      // streaming layout
+// ------------------------------------------------------------------------------------------------ kernel
+struct Decode2Params {
+  const uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
   const uint16_t *n1, *n2, *nf, *embed;
-  const float* invf;                                    // fp32 [HD/2] inverse RoPE frequencies
-  uint16_t *kc, *vc;                                    // bf16 [L, max_seq, NKV, HD]
-  uint16_t *h, *qbuf, *ao, *act;                        // global scratch (L2 resident)
-  float *pm, *pd, *pacc;
-  float* cand_val;
-  int* cand_idx;
-  unsigned* bar_ctr;
+  const float* invf;
+  uint16_t *kc, *vc;
+  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll;   // tagged vectors
+  uint64_t* part_ll;
+  uint32_t *h_flags, *act_flags, *ao_flags;                          // arrival flags: [G], [G], [NKV]
   DevStatus* status;
   const int32_t* d_token;
-  uint16_t* d_h;                                        // optional caller residual in/out
+  uint16_t* d_h;
   float* d_logits;
   int32_t* d_next;
   int32_t token, pos, max_seq;
-  int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks;
-  unsigned bar_base, spin_limit;
+  int32_t n_layer, dim, n_head, n_kv, ffn, vocab, nchunks, maxchunks;
+  unsigned tag_base, spin_limit;
   float eps, attn_scale, resid, emb_mult, logits_scaling;
-  long long* prof;                                      // optional phase stamps
+  long long* prof;
   unsigned max_fly;
+  // tensor parallelism: this GPU holds a slice of every matrix (heads, FFN columns, vocabulary rows); the partial sums
+  // of the K-sharded O and down projections are exchanged by peer stores into every rank's inbox
+  int32_t tp_size, tp_rank, vocab_base;
+  uint64_t* inbox;            // local: [2 parities][tp_size][dim] tagged fp32 partials, then [tp_size][2] arg-max candidates
+  uint64_t* peer_inbox[8];    // the same buffer of every rank (peer-mapped); own entry = inbox
 };
 
-template <class KD, class KF, int HD, int R, bool HZ>
-__global__ void __launch_bounds__(kThreads, 1) decode_mega(const DecodeParams P) {
+// tags: phase ids inside a layer
+enum { PH_QKV = 1, PH_ATT = 2, PH_O = 3, PH_GU = 4, PH_DOWN = 5, PH_LM = 6, PH_PART = 7 };
+__device__ __forceinline__ uint32_t mk_tag(unsigned base, int layer, int ph) { return base + (unsigned)(layer * 8 + ph); }
+
+// small phases (QKV, O, down give a CTA a handful of tiles): cut long tiles in two so that more warps share them
+__host__ __device__ constexpr int small_ks(int k) {
+  const int rt = tile_rt(k), bq = (k / 128) / (16 / rt) * 2;
+  return (rt <= 4 && bq >= 16 && bq % 2 == 0) ? 2 : 1;
+}
+__host__ __device__ constexpr int imax(int a, int b) { return a > b ? a : b; }
+
+template <int KDIM, int KOUT, int KFFN, int HD, int R, bool HZ>
+__global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params P) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem sm = carve_smem(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, b = blockIdx.x;
-  if (tid == 0) {
-    for (int s = 0; s < kStages; s++) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    *sm.s_abort = 0;
-    mbar_fence_init();
-  }
+  if (tid == 0) pipe_init(sm);
   __syncthreads();
   WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
-  Pipe pipe{sm.stages, sm.full, sm.empty, 0u, P.max_fly};
-
+  Pipe pipe{sm.stages, sm.full, sm.empty, sm.landed, 0u, P.max_fly};
+  constexpr int HP = HD / 2;
+  using CQ = TCfg<KDIM, small_ks(KDIM)>;      // QKV: few rows per CTA
+  using CG = TCfg<KDIM>;                      // gate/up and LM head: many rows per CTA
+  using CO = TCfg<KOUT, small_ks(KOUT)>;      // O projection (K = this rank's attention output width)
+  using CF = TCfg<KFFN, small_ks(KFFN)>;      // down projection
+  constexpr int UO = imax(CO::RT, CF::RT);    // O and down give a CTA the same rows of the residual stream
+  static_assert(CG::RT % 4 == 0, "the SwiGLU epilogue packs rows (g, u, g', u') into one tagged word");
   const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
   const int QKV = (P.n_head + 2 * P.n_kv) * HD;
-  const int recD = rec_bytes_of(KD::K, HZ), recF = rec_bytes_of(KF::K, HZ);
-  int q0, q1, o0, o1, g0, g1, d0r, d1r, l0, l1;
-  cta_rows(QKV, 2, b, G, q0, q1);
-  cta_rows(D, 1, b, G, o0, o1);
-  cta_rows(2 * FF, 2, b, G, g0, g1);
-  cta_rows(D, 1, b, G, d0r, d1r);
-  cta_rows(V, 1, b, G, l0, l1);
+  constexpr int recD = rec_bytes_of(KDIM, HZ), recO = rec_bytes_of(KOUT, HZ), recF = rec_bytes_of(KFFN, HZ);
+  const size_t strQ = (size_t)pad_rows(QKV, KDIM) * recD, strO = (size_t)pad_rows(D, KOUT) * recO,
+               strG = (size_t)pad_rows(2 * FF, KDIM) * recD, strF = (size_t)pad_rows(D, KFFN) * recF;
+  const int N = P.tp_size, me = P.tp_rank;
+  int q0, q1, o0, o1, g0, g1, l0, l1;
+  cta_rows(QKV, CQ::RT, b, G, q0, q1);
+  cta_rows(D, UO, b, G, o0, o1);         // the same rows of h belong to this CTA in the O and the down phase
+  cta_rows(2 * FF, CG::RT, b, G, g0, g1);   // (g_i, u_i, g_i+1, u_i+1) stay together: one tagged word of activations
+  cta_rows(V, CG::RT, b, G, l0, l1);
 
   if (warp == kConsumerWarps) {
-    // ================================ producer ================================
     if (lane == 0) {
       bool ok = true;
       for (int l = 0; l < L && ok; l++) {
-        ok = produce_rows(pipe, P.w_qkv + ((size_t)l * QKV + q0) * recD, q1 - q0, KD::TILE_ROWS, recD, wc, l) &&
-             produce_rows(pipe, P.w_o + ((size_t)l * D + o0) * recD, o1 - o0, KD::TILE_ROWS, recD, wc, l) &&
-             produce_rows(pipe, P.w_gu + ((size_t)l * 2 * FF + g0) * recD, g1 - g0, KD::TILE_ROWS, recD, wc, l) &&
-             produce_rows(pipe, P.w_d + ((size_t)l * D + d0r) * recF, d1r - d0r, KF::TILE_ROWS, recF, wc, l);
+        ok = produce_rows(pipe, P.w_qkv + l * strQ + (size_t)q0 * recD, q1 - q0, CQ::TILE_ROWS, CQ::RT, recD, wc, l) &&
+             produce_rows(pipe, P.w_o + l * strO + (size_t)o0 * recO, o1 - o0, CO::TILE_ROWS, CO::RT, recO, wc, l) &&
+             produce_rows(pipe, P.w_gu + l * strG + (size_t)g0 * recD, g1 - g0, CG::TILE_ROWS, CG::RT, recD, wc, l) &&
+             produce_rows(pipe, P.w_d + l * strF + (size_t)o0 * recF, o1 - o0, CF::TILE_ROWS, CF::RT, recF, wc, l);
       }
-      if (ok) produce_rows(pipe, P.w_lm + (size_t)l0 * recD, l1 - l0, KD::TILE_ROWS, recD, wc, L);
+      if (ok) produce_rows(pipe, P.w_lm + (size_t)l0 * recD, l1 - l0, CG::TILE_ROWS, CG::RT, recD, wc, L);
       producer_drain(pipe, wc);
     }
   } else {
-    // ================================ consumers ================================
     const int cw = warp, tid_c = tid;
-    const int wg = cw & 3;
-    GridBar gb{P.bar_ctr, P.bar_base};
-    // ---- embedding (or caller-supplied residual) -> h ----
+    float* hown = sm.hown;                                      // this CTA's rows of the residual stream (exact bf16 values)
+    int* s_done = sm.misc + 20;                                 // warps of this CTA that finished the current producing phase
+    if (tid_c == 0) *s_done = 0;
+    const QueueState qs_{sm.qpart, sm.tdone, sm.bcnt};
+    const XStage xs_{sm.xh, sm.xf};
+    float* ypart = sm.hown + kMaxOwnRows;                       // tensor parallel: this rank's partial sums of its rows
+    constexpr int MAXP_O = (KOUT / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    // O / down epilogue. One GPU: h = bf16(h + y * resid) at once. Tensor parallel: y is a partial sum over this
+    // rank's K slice: keep it, push it to every peer's inbox, finish in resid_finish once all rows are done.
+    auto resid_epi = [&](int row0, float c, int nvalid, uint32_t tag, int par) {
+      const int r = row0 + (lane >> 3);
+      if (N > 1) {
+        if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+          ypart[r] = c;
+          for (int p = 0; p < N; p++)
+            if (p != me) ll_store_sys(P.peer_inbox[p] + ((size_t)(par * N + me)) * D + o0 + r, __float_as_uint(c), tag);
+        }
+        return;
+      }
+      float hn = 0.f;
+      if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+        hn = rbf(hown[r] + c * P.resid);
+        hown[r] = hn;
+      }
+      const float hn1 = __shfl_down_sync(0xffffffffu, hn, 8);
+      if ((lane & 15) == 0 && (lane >> 3) < nvalid)
+        ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tag);
+    };
+    // tensor parallel only: sum the partials of all ranks in rank order (identical on every rank), update h, publish
+    auto resid_finish = [&](uint32_t tag, int par, int layer) {
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      for (int pr = tid_c; pr < (o1 - o0) / 2; pr += kConsumerThreads) {
+        float tot0 = 0.f, tot1 = 0.f;
+        for (int s2 = 0; s2 < N; s2++) {
+          if (s2 == me) {
+            tot0 += ypart[2 * pr]; tot1 += ypart[2 * pr + 1];
+          } else {
+            const uint64_t* src = P.inbox + ((size_t)(par * N + s2)) * D + o0 + 2 * pr;
+            tot0 += __uint_as_float(ll_poll_sys(src, tag, wc, layer));
+            tot1 += __uint_as_float(ll_poll_sys(src + 1, tag, wc, layer));
+          }
+        }
+        const float h0 = rbf(hown[2 * pr] + tot0 * P.resid), h1 = rbf(hown[2 * pr + 1] + tot1 * P.resid);
+        hown[2 * pr] = h0; hown[2 * pr + 1] = h1;
+        ll_store(P.h_ll + ((o0 >> 1) + pr), (uint32_t)f2bf(h0) | ((uint32_t)f2bf(h1) << 16), tag);
+      }
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      if (tid_c == 0) st_relaxed_u32(P.h_flags + b, tag);
+    };
+    constexpr int MAXP_D = (KDIM / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    constexpr int MAXP_F = (KFFN / 4 + kConsumerThreads - 1) / kConsumerThreads;
+    // ---- residual stream at layer 0: every CTA reads the embedding row (or the caller's h) itself ----
     {
       int tok = P.d_token ? (int)ld_cg_u32(P.d_token) : P.token;
-      if ((unsigned)tok >= (unsigned)V) {
+      if ((unsigned)tok >= (unsigned)(V * N)) {                 // V is this rank's slice of the vocabulary
         tok = 0;
         if (tid_c == 0 && b == 0) atomicCAS(&P.status->code, 0, 6 /*FB_ERR_RANGE*/);
       }
-      for (int i = b * kConsumerThreads + tid_c; i < D; i += G * kConsumerThreads) {
-        if (P.d_h) P.h[i] = ld_cg_u16(P.d_h + i);
-        else P.h[i] = f2bf(bf2f(__ldg(P.embed + (size_t)tok * D + i)) * P.emb_mult);
+      for (int i = tid_c; i < D; i += kConsumerThreads) {
+        const uint16_t v = P.d_h ? ld_cg_u16(P.d_h + i) : f2bf(bf2f(__ldg(P.embed + (size_t)tok * D + i)) * P.emb_mult);
+        reinterpret_cast<uint16_t*>(sm.xh)[i] = v;
+        if (i >= o0 && i < o1) hown[i - o0] = bf2f(v);
       }
+      named_bar_sync(kBarConsumers, kConsumerThreads);
     }
-    grid_barrier(gb, wc, tid_c, -1);
-
-    XRegs<KD> xd;
 #define FB_STAMP(i) do { if (P.prof && tid_c == 0) P.prof[((size_t)b * L + l) * 16 + (i)] = (long long)globaltimer_ns(); } while (0)
     for (int l = 0; l < L; l++) {
       uint16_t* kcl = P.kc + (size_t)l * P.max_seq * P.n_kv * HD;
       uint16_t* vcl = P.vc + (size_t)l * P.max_seq * P.n_kv * HD;
-      // ---- QKV: norm1 -> GEMV -> RoPE -> q scratch / KV append ----
+      const uint32_t tg_qkv = mk_tag(P.tag_base, l, PH_QKV), tg_att = mk_tag(P.tag_base, l, PH_ATT),
+                     tg_o = mk_tag(P.tag_base, l, PH_O), tg_gu = mk_tag(P.tag_base, l, PH_GU),
+                     tg_dn = mk_tag(P.tag_base, l, PH_DOWN);
+      // ================= QKV: norm1 -> GEMV -> RoPE -> tagged q / new k / new v, cache append =================
       FB_STAMP(0);
-      stage_x_norm(P.h, P.n1 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c);
-      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
-      FB_STAMP(1);
-      consume_rows<KD, HZ>(pipe, q1 - q0, xd, sm.res_s, cw, lane, wc, l);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      FB_STAMP(2);
-      for (int pr = tid_c; pr < (q1 - q0) / 2; pr += kConsumerThreads) {
-        const float a = row_result<KD>(sm.res_s, 2 * pr), c = row_result<KD>(sm.res_s, 2 * pr + 1);
-        const int rs = q0 + 2 * pr;
-        const int head = rs / HD, within = rs % HD;
-        if (head < P.n_head + P.n_kv) {
-          const int i = within >> 1;
-          const float x0 = rbf(a), x1 = rbf(c);
-          float sn, cs;
-          sincosf((float)P.pos * __ldg(P.invf + i), &sn, &cs);
-          const uint16_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
-          if (head < P.n_head) {
-            P.qbuf[head * HD + i] = y0;
-            P.qbuf[head * HD + i + HD / 2] = y1;
-          } else {
-            uint16_t* kr = kcl + ((size_t)P.pos * P.n_kv + (head - P.n_head)) * HD;
-            kr[i] = y0;
-            kr[i + HD / 2] = y1;
-          }
-        } else {
-          uint16_t* vr = vcl + ((size_t)P.pos * P.n_kv + (head - P.n_head - P.n_kv)) * HD;
-          vr[within] = f2bf(a);
-          vr[within + 1] = f2bf(c);
+      if (b < P.n_kv * P.nchunks) {
+        // the K/V rows this CTA will attend in this layer: pull them into L2 now, they do not depend on anything
+        const int kvh = b / P.nchunks, c = b % P.nchunks;
+        const int T = P.pos + 1, clen = (T + P.nchunks - 1) / P.nchunks;
+        const int t0 = c * clen, t1 = min(min(T, t0 + clen), t0 + 64);
+        constexpr int PER_ROW = (HD * 2 + 63) / 64;
+        for (int i = tid_c; i < (t1 - t0) * PER_ROW * 2; i += kConsumerThreads) {
+          const int t = t0 + (i >> 1) / PER_ROW, seg = (i >> 1) % PER_ROW;
+          const uint16_t* base = ((i & 1) ? vcl : kcl) + ((size_t)t * P.n_kv + kvh) * HD;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(base) + seg * 64));
         }
       }
-      grid_barrier(gb, wc, tid_c, l);
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
+                            sm, tid_c, wc, l, l == 0, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
+      FB_STAMP(1);
+      consume_tiles<CQ, HZ>(pipe, q1 - q0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+        // lanes 0/8/16/24 hold rows row0..row0+3: two RoPE pairs (or four v dims)
+        const float c1 = __shfl_down_sync(0xffffffffu, c, 8);
+        if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
+          const int rs = q0 + row0 + (lane >> 3);              // stream row of the pair's first element (even)
+          const int head = rs / HD, within = rs % HD;
+          if (head < P.n_head + P.n_kv) {
+            const int i = within >> 1;
+            const float x0 = rbf(c), x1 = rbf(c1);
+            float sn, cs;
+            sincosf((float)P.pos * __ldg(P.invf + i), &sn, &cs);
+            const uint32_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
+            if (head < P.n_head) {
+              ll_store(P.q_ll + (size_t)head * HP + i, y0 | (y1 << 16), tg_qkv);
+            } else {
+              const int kvh = head - P.n_head;
+              ll_store(P.k_ll + (size_t)kvh * HP + i, y0 | (y1 << 16), tg_qkv);
+              uint16_t* kr = kcl + ((size_t)P.pos * P.n_kv + kvh) * HD;
+              kr[i] = (uint16_t)y0;
+              kr[i + HP] = (uint16_t)y1;
+            }
+          } else {
+            const int kvh = head - P.n_head - P.n_kv;
+            const uint32_t pv = (uint32_t)f2bf(c) | ((uint32_t)f2bf(c1) << 16);
+            ll_store(P.v_ll + (size_t)kvh * HP + (within >> 1), pv, tg_qkv);
+            *reinterpret_cast<uint32_t*>(vcl + ((size_t)P.pos * P.n_kv + kvh) * HD + within) = pv;
+          }
+        }
+      });
+      FB_STAMP(2);
+      // ================= attention =================
+      {
+        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll, kcl, vcl, P.part_ll, P.ao_flags, P.n_kv, P.pos, P.nchunks,
+                     P.maxchunks, P.attn_scale, tg_qkv, mk_tag(P.tag_base, l, PH_PART), tg_att};
+        named_bar_sync(kBarConsumers, kConsumerThreads);        // scratch (the activations) is free: every warp left the GEMV
+        attn2_phase<HD, R>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l);
+      }
       FB_STAMP(3);
-      // ---- attention ----
-      AttnArgs aa{P.qbuf, kcl, vcl, P.ao, P.pm, P.pd, P.pacc, P.n_kv, P.pos + 1, P.nchunks, P.attn_scale};
-      attn_phase<HD, R>(aa, sm.scratch, cw, lane, tid_c);
-      FB_STAMP(4);
-      grid_barrier(gb, wc, tid_c, l);
-      if (P.nchunks > 1) {
-        attn_merge_phase<HD>(aa, P.n_head, cw, lane);
-        grid_barrier(gb, wc, tid_c, l);
+      // ================= O projection + residual =================
+      {
+        stage_plain_ll<MAXP_O>(P.ao_ll, P.ao_flags, P.n_kv, tg_att, KOUT, sm, tid_c, wc, l);
+        FB_STAMP(4);
+        consume_tiles<CO, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
+                                  [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_o, 0); });
+        if (N > 1) resid_finish(tg_o, 0, l);
+        else post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
       }
       FB_STAMP(5);
-      // ---- O projection + residual ----
-      stage_x_plain(P.ao, D, sm.x_s, tid_c);
-      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
+      // ================= gate/up + SwiGLU =================
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm, tid_c, wc, l, false);
       FB_STAMP(6);
-      consume_rows<KD, HZ>(pipe, o1 - o0, xd, sm.res_s, cw, lane, wc, l);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
+      consume_tiles<CG, HZ>(pipe, g1 - g0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+        // rows (g_i, u_i, g_{i+1}, u_{i+1}) -> act[i], act[i+1] -> one tagged word
+        const float u = __shfl_down_sync(0xffffffffu, c, 8);
+        float av = 0.f;
+        if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
+          const float gg = rbf(c), uu = rbf(u);
+          av = rbf((gg / (1.0f + __expf(-gg))) * uu);
+        }
+        const float av1 = __shfl_down_sync(0xffffffffu, av, 16);
+        const int i = (g0 + row0) >> 1;                          // act index of lane 0's value: even, g0 % 4 == 0
+        if (lane == 0 && nvalid == 4)
+          ll_store(P.act_ll + (i >> 1), (uint32_t)f2bf(av) | ((uint32_t)f2bf(av1) << 16), tg_gu);
+      });
+      post_when_cta_done(s_done, P.act_flags + b, tg_gu, lane);
       FB_STAMP(7);
-      for (int r = tid_c; r < o1 - o0; r += kConsumerThreads) {
-        const float y = row_result<KD>(sm.res_s, r);
-        P.h[o0 + r] = f2bf(bf2f(ld_cg_u16(P.h + o0 + r)) + y * P.resid);
-      }
-      grid_barrier(gb, wc, tid_c, l);
-      FB_STAMP(8);
-      // ---- gate/up + SwiGLU ----
-      stage_x_norm(P.h, P.n2 + (size_t)l * D, D, P.eps, sm.x_s, sm.red, tid_c);
-      load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
-      FB_STAMP(9);
-      consume_rows<KD, HZ>(pipe, g1 - g0, xd, sm.res_s, cw, lane, wc, l);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      FB_STAMP(10);
-      for (int pr = tid_c; pr < (g1 - g0) / 2; pr += kConsumerThreads) {
-        const float gg = rbf(row_result<KD>(sm.res_s, 2 * pr)), uu = rbf(row_result<KD>(sm.res_s, 2 * pr + 1));
-        P.act[g0 / 2 + pr] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
-      }
-      grid_barrier(gb, wc, tid_c, l);
-      FB_STAMP(11);
-      // ---- down projection + residual ----
+      // ================= down projection + residual =================
       {
-        XRegs<KF> xf;
-        stage_x_plain(P.act, FF, sm.x_s, tid_c);
-        load_x_slice<KF>(sm.x_s, wg % KF::KS, lane, xf);
-        FB_STAMP(12);
-        consume_rows<KF, HZ>(pipe, d1r - d0r, xf, sm.res_s, cw, lane, wc, l);
+        stage_plain_ll<MAXP_F>(P.act_ll, P.act_flags, G, tg_gu, FF, sm, tid_c, wc, l);
+        FB_STAMP(8);
+        consume_tiles<CF, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
+                                  [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_dn, 1); });
+        if (N > 1) resid_finish(tg_dn, 1, l);
+        else post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       }
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      FB_STAMP(13);
-      for (int r = tid_c; r < d1r - d0r; r += kConsumerThreads) {
-        const float y = row_result<KF>(sm.res_s, r);
-        P.h[d0r + r] = f2bf(bf2f(ld_cg_u16(P.h + d0r + r)) + y * P.resid);
-      }
-      grid_barrier(gb, wc, tid_c, l);
-      FB_STAMP(14);
+      FB_STAMP(9);
     }
 #undef FB_STAMP
-    // ---- final norm + LM head + argmax ----
-    stage_x_norm(P.h, P.nf, D, P.eps, sm.x_s, sm.red, tid_c);
-    load_x_slice<KD>(sm.x_s, wg % KD::KS, lane, xd);
-    consume_rows<KD, HZ>(pipe, l1 - l0, xd, sm.res_s, cw, lane, wc, L);
-    named_bar_sync(kBarConsumers, kConsumerThreads);
+    // ================= final norm + LM head + arg-max =================
+    stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm, tid_c, wc, L, false);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int r = tid_c; r < l1 - l0; r += kConsumerThreads) {
-      const float y = row_result<KD>(sm.res_s, r) / P.logits_scaling;
-      if (P.d_logits) P.d_logits[l0 + r] = y;
-      if (y > bv) { bv = y; bi = l0 + r; }
-    }
+    consume_tiles<CG, HZ>(pipe, l1 - l0, xs_, qs_, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
+      if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
+        const int row = P.vocab_base + l0 + row0 + (lane >> 3);     // index in the full vocabulary
+        const float y = c / P.logits_scaling;
+        if (P.d_logits) P.d_logits[row] = y;
+        if (y > bv || (y == bv && row < bi)) { bv = y; bi = row; }
+      }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -575,20 +718,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega(const DecodeParams P)
     }
     if (lane == 0) { sm.red[cw] = bv; sm.misc[cw] = bi; }
     named_bar_sync(kBarConsumers, kConsumerThreads);
+    const uint32_t tg_lm = mk_tag(P.tag_base, L, PH_LM);
     if (tid_c == 0) {
       for (int w = 1; w < kConsumerWarps; w++)
         if (sm.red[w] > bv || (sm.red[w] == bv && sm.misc[w] < bi)) { bv = sm.red[w]; bi = sm.misc[w]; }
-      P.cand_val[b] = bv;
-      P.cand_idx[b] = bi;
+      ll_store(P.cand_ll + 2 * b, __float_as_uint(bv), tg_lm);
+      ll_store(P.cand_ll + 2 * b + 1, (uint32_t)bi, tg_lm);
     }
-    grid_barrier(gb, wc, tid_c, L);
     if (b == 0) {
+      uint32_t* cs = reinterpret_cast<uint32_t*>(sm.xh);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
+      ll_gather<2>(P.cand_ll, 2 * G, tg_lm, cs, tid_c, kConsumerThreads, wc, L);
+      named_bar_sync(kBarConsumers, kConsumerThreads);
       if (cw == 0) {
         float v = -INFINITY;
         int ix = 0x7fffffff;
         for (int c = lane; c < G; c += 32) {
-          const float ov = ld_cg_f32(P.cand_val + c);
-          const int oi = (int)ld_cg_u32(P.cand_idx + c);
+          const float ov = __uint_as_float(cs[2 * c]);
+          const int oi = (int)cs[2 * c + 1];
           if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
         }
 #pragma unroll
@@ -597,100 +744,29 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega(const DecodeParams P)
           const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
           if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
         }
+        if (N > 1 && lane == 0) {
+          // every rank holds a slice of the vocabulary: exchange the N (value, index) candidates, reduce in rank order
+          uint64_t* mine = P.inbox + (size_t)2 * N * D;
+          for (int p = 0; p < N; p++) {
+            uint64_t* dst = (p == me ? mine : P.peer_inbox[p] + (size_t)2 * N * D) + 2 * me;
+            ll_store_sys(dst, __float_as_uint(v), tg_lm);
+            ll_store_sys(dst + 1, (uint32_t)ix, tg_lm);
+          }
+          v = -INFINITY; ix = 0x7fffffff;
+          for (int s2 = 0; s2 < N; s2++) {
+            const float ov = __uint_as_float(ll_poll_sys(mine + 2 * s2, tg_lm, wc, L));
+            const int oi = (int)ll_poll_sys(mine + 2 * s2 + 1, tg_lm, wc, L);
+            if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+          }
+        }
         if (lane == 0 && P.d_next) *P.d_next = ix;
       }
-      if (P.d_h)
-        for (int i = tid_c; i < D; i += kConsumerThreads) P.d_h[i] = ld_cg_u16(P.h + i);
     }
+    // final residual back to the caller (the reference clobbers its h argument): every CTA writes its own rows
+    if (P.d_h)
+      for (int r = tid_c; r < o1 - o0; r += kConsumerThreads) P.d_h[o0 + r] = f2bf(hown[r]);
   }
   __syncthreads();
-}
-
-// ------------------------------------------------------------------------------------------------ stand-alone GEMV
-struct GemvParams {
-  const uint8_t* w;        // streaming layout, `rows` records
-  const uint16_t* x;       // bf16 [K]
-  float* y;                // f32 [rows], original row order
-  DevStatus* status;
-  int32_t rows, order, order_arg, order_rows;
-  unsigned spin_limit;
-};
-
-template <class KC, bool HZ>
-__global__ void __launch_bounds__(kThreads, 1) gemv_stream(const GemvParams P) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  Smem sm = carve_smem(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) {
-    for (int s = 0; s < kStages; s++) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    *sm.s_abort = 0;
-    mbar_fence_init();
-  }
-  __syncthreads();
-  WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
-  Pipe pipe{sm.stages, sm.full, sm.empty, 0u, (uint32_t)kStages};
-  const int rec = rec_bytes_of(KC::K, HZ);
-  int r0, r1;
-  cta_rows(P.rows, 1, blockIdx.x, gridDim.x, r0, r1);
-  // a CTA's result buffer holds kResFloats/KS rows: walk the CTA's range in passes of that many rows
-  constexpr int PASS = (kResFloats / KC::KS) / KC::TILE_ROWS * KC::TILE_ROWS;
-  if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      bool ok = true;
-      for (int p0 = r0; p0 < r1 && ok; p0 += PASS)
-        ok = produce_rows(pipe, P.w + (size_t)p0 * rec, min(PASS, r1 - p0), KC::TILE_ROWS, rec, wc, 0);
-      producer_drain(pipe, wc);
-    }
-  } else {
-    XRegs<KC> x;
-    stage_x_plain(P.x, KC::K, sm.x_s, tid);
-    load_x_slice<KC>(sm.x_s, (warp & 3) % KC::KS, lane, x);
-    for (int p0 = r0; p0 < r1; p0 += PASS) {
-      const int n = min(PASS, r1 - p0);
-      consume_rows<KC, HZ>(pipe, n, x, sm.res_s, warp, lane, wc, 0);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      for (int r = tid; r < n; r += kConsumerThreads)
-        P.y[perm_row(p0 + r, P.order, P.order_arg, P.order_rows)] = row_result<KC>(sm.res_s, r);
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-    }
-  }
-  __syncthreads();
-}
-
-// ------------------------------------------------------------------------------------------------ layout kernels
-// one CTA per stream row; blockIdx.y = layer (matrices of all layers are stacked, the row order repeats per layer)
-__global__ void repack_rows(const uint32_t* q, const uint16_t* s, const uint16_t* z, int rows, int k, int order,
-                            int order_arg, int order_rows, uint8_t* out) {
-  const int j = blockIdx.x;
-  const int src = blockIdx.y * rows + perm_row(j, order, order_arg, order_rows);
-  const int rec = rec_bytes_of(k, z != nullptr);
-  uint8_t* dst = out + ((size_t)blockIdx.y * rows + j) * rec;
-  const int words = k / 8, groups = k / 128;
-  for (int i = threadIdx.x; i < words; i += blockDim.x) reinterpret_cast<uint32_t*>(dst)[i] = q[(size_t)src * words + i];
-  uint16_t* meta = reinterpret_cast<uint16_t*>(dst + k / 2);
-  const int meta_n = (rec - k / 2) / 2;
-  for (int i = threadIdx.x; i < meta_n; i += blockDim.x) {
-    uint16_t v = 0;
-    if (i < groups) v = s[(size_t)src * groups + i];
-    else if (z != nullptr && i < 2 * groups) v = z[(size_t)src * groups + (i - groups)];
-    meta[i] = v;
-  }
-}
-
-__global__ void dequant_rows(const uint8_t* in, int rows, int k, int has_zeros, int order, int order_arg, int order_rows,
-                             float* out) {
-  const int j = blockIdx.x;
-  const int dstrow = perm_row(j, order, order_arg, order_rows);
-  const int rec = rec_bytes_of(k, has_zeros);
-  const uint8_t* src = in + (size_t)j * rec;
-  const uint16_t* meta = reinterpret_cast<const uint16_t*>(src + k / 2);
-  for (int c = threadIdx.x; c < k; c += blockDim.x) {
-    const uint32_t w = reinterpret_cast<const uint32_t*>(src)[c >> 3];
-    const float nib = (float)((w >> (4 * (c & 7))) & 0xF) - 8.0f;
-    float v = nib * bf2f(meta[c >> 7]);
-    if (has_zeros) v = v + bf2f(meta[k / 128 + (c >> 7)]);
-    out[(size_t)dstrow * k + c] = v;
-  }
 }
 
 }  // namespace fb

@@ -1,6 +1,6 @@
 """Per-phase timeline of one decode step (the run-time replacement of the reference's -DNOSYNC / -DNOATTN builds).
 
-    python -m flint_b200.phase_profile --config granite-3b-class --cached 200 [--kernel 2]
+    python -m flint_b200.phase_profile --config granite-3b-class --cached 200
 
 Every CTA stamps %globaltimer at the phase boundaries of every layer (fb_set_option(ctx, 2, buffer)); this prints,
 per phase, the mean / min / max over CTAs of the time spent, averaged over the middle layers, and the layer period.
@@ -14,23 +14,19 @@ from . import packing
 from .config import ModelArgs
 from .engine import DecodeEngine, query
 
-NAMES = {1: ["qkv stage", "qkv gemv", "qkv epi+bar", "attn", "attn bar", "o stage", "o gemv", "o epi+bar", "gu stage",
-             "gu gemv", "gu epi+bar", "d stage", "d gemv", "d epi+bar"],
-         2: ["qkv wait+stage", "qkv gemv+epi", "attention", "o wait+stage", "o gemv+epi", "gu wait+stage", "gu gemv+epi",
-             "down wait+stage", "down gemv+epi"]}
+NAMES = ["qkv wait+stage", "qkv gemv+epi", "attention", "o wait+stage", "o gemv+epi", "gu wait+stage", "gu gemv+epi",
+         "down wait+stage", "down gemv+epi"]
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="granite-3b-class")
     ap.add_argument("--cached", type=int, default=200, help="positions already in the KV cache")
-    ap.add_argument("--kernel", type=int, default=2, choices=(1, 2), help="2: data-flow kernel, 1: grid-barrier kernel")
     ap.add_argument("--steps", type=int, default=64)
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
     W = packing.synth_packed(cfg, 0, device="cuda")
     eng = DecodeEngine(cfg, W, max_seq=max(cfg.block_size, a.cached + a.steps + 8))
-    eng.set_option(3, a.kernel)
     G = query(torch.cuda.current_device())["sm_count"]
     prof = torch.zeros(G * cfg.n_layer * 16, dtype=torch.int64, device="cuda")
     for pos in range(a.cached):
@@ -43,12 +39,12 @@ def main():
         eng.decode_chained(nxt[i:i + 1], a.cached + i, nxt[i + 1:i + 2])
     e1.record()
     torch.cuda.synchronize()
-    print(f"kernel {a.kernel}: {e0.elapsed_time(e1) / a.steps * 1e3:.1f} us/token over {a.steps} chained steps")
+    print(f"decode: {e0.elapsed_time(e1) / a.steps * 1e3:.1f} us/token over {a.steps} chained steps")
     eng.set_option(2, prof.data_ptr())
     eng.decode(77, a.cached + a.steps, want_logits=False)
     eng.check()
     p = prof.cpu().numpy().reshape(G, cfg.n_layer, 16).astype(np.float64)
-    names = NAMES[a.kernel]
+    names = NAMES
     lo, hi = (1, cfg.n_layer - 1) if cfg.n_layer > 4 else (0, cfg.n_layer)
     d = np.diff(p[:, lo:hi, :len(names) + 1], axis=2) / 1e3
     print(f"{'phase':18s} {'mean':>7s} {'min':>7s} {'max':>7s}   (us per layer; mean/min/max over {G} CTAs)")

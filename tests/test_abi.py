@@ -30,8 +30,9 @@ def test_library_exports_every_symbol():
 
 def test_stream_bytes_is_host_only_arithmetic():
     lib = _lib.load()
-    assert lib.fb_stream_bytes(16, 2560, 0) == 16 * (1280 + 48)
-    assert lib.fb_stream_bytes(3, 14336, 1) == 3 * (7168 + 448)
+    assert lib.fb_stream_bytes(16, 2560, 0) == 16 * (1280 + 40)       # 4 tiles of 4 rows: nibbles + 20 bf16 scales per row
+    assert lib.fb_stream_bytes(3, 14336, 1) == 4 * (7168 + 448)        # tiles of 2 rows: 3 rows occupy 2 tiles
+    assert lib.fb_stream_bytes(5, 640, 0) == 16 * (320 + 10)           # 5 groups: one tile of 16 rows
     assert lib.fb_stream_bytes(4, 1376, 0) == 0          # not a multiple of the group
 
 

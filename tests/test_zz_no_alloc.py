@@ -66,6 +66,6 @@ def test_static_scratch_rejects_oversized_matrix():
     q, s, z, x = _case(8, 2560, 3, False)
     y = torch.zeros(8, dtype=torch.float32, device="cuda")
     status = torch.zeros(8, dtype=torch.int32, device="cuda")
-    too_many = (9 << 20) // (1280 + 48) + 1                         # one record more than the built-in array holds
+    too_many = ((9 << 20) // (4 * 1320) + 1) * 4                    # one 4-row tile more than the built-in array holds
     rc = lib.fb_gemv_static(_p(q), _p(s), None, too_many, 2560, _p(x), _p(y), _p(status), None)
     assert rc == _lib.FB_ERR_RANGE
