@@ -648,7 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
             *reinterpret_cast<uint32_t*>(vcl + ((size_t)P.pos * P.n_kv + kvh) * HD + within) = pv;
           }
         }
-      });
+      }, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       FB_STAMP(2);
       // ================= attention =================
       {

@@ -129,7 +129,7 @@ struct QueueState {
 // that finishes the last slice adds the partials in slice order and runs the epilogue.
 template <class C, bool HZ, class Epi>
 __device__ __forceinline__ void consume_tiles(Pipe& p, int nrows, const XStage& x, const QueueState& q, int cw, int lane,
-                                              const WaitCtl& wc, int layer, Epi epi) {
+                                              const WaitCtl& wc, int layer, Epi epi, long long* dbg = nullptr) {
   constexpr int RT = C::RT, KS = C::KS, TPS = C::TPS;
   constexpr int NL = kConsumerWarps / KS;            // tile lanes; warps beyond NL * KS sit this phase out
   constexpr int TILE = C::tile(HZ);
@@ -153,10 +153,12 @@ __device__ __forceinline__ void consume_tiles(Pipe& p, int nrows, const XStage& 
         }
       }
       if (!mbar_wait(&p.full[s], (it / kStages) & 1, wc, W_FULL, layer)) break;
+      if (dbg && cw == 0 && lane == 0 && tl == 0) dbg[13] = (long long)globaltimer_ns();
       const uint8_t* tile = p.stages + (size_t)s * kStageBytes + (size_t)blk * TILE;
       const int nvalid_tile = min(RT, nrows - tl * RT);
       float lo, hi;
       tile_dot<C, HZ>(tile, slice, x, lane, lo, hi);
+      if (dbg && cw == 0 && lane == 0 && tl == 0) dbg[14] = (long long)globaltimer_ns();
       if (KS == 1) {
         if (RT <= 4) {
           epi(tl * RT, __shfl_sync(0xffffffffu, lo, (lane >> 3) * 4), nvalid_tile);

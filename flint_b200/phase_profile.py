@@ -23,10 +23,13 @@ def main():
     ap.add_argument("--config", default="granite-3b-class")
     ap.add_argument("--cached", type=int, default=200, help="positions already in the KV cache")
     ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--chunks", type=int, default=0, help="attention chunks per kv head (0: the library's choice)")
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
     W = packing.synth_packed(cfg, 0, device="cuda")
     eng = DecodeEngine(cfg, W, max_seq=max(cfg.block_size, a.cached + a.steps + 8))
+    if a.chunks:
+        eng.set_option(1, a.chunks)
     G = query(torch.cuda.current_device())["sm_count"]
     prof = torch.zeros(G * cfg.n_layer * 16, dtype=torch.int64, device="cuda")
     for pos in range(a.cached):
@@ -51,6 +54,20 @@ def main():
     for i, nm in enumerate(names):
         x = d[:, :, i].mean(1)
         print(f"{nm:18s} {x.mean():7.2f} {x.min():7.2f} {x.max():7.2f}")
+    w = (p[:, lo:hi, 13] - p[:, lo:hi, 1]).mean() / 1e3
+    t = (p[:, lo:hi, 14] - p[:, lo:hi, 13]).mean() / 1e3
+    r = (p[:, lo:hi, 2] - p[:, lo:hi, 14]).mean() / 1e3
+    print(f"qkv, warp 0: weights ready {w:.2f} us after staging, first tile product {t:.2f} us, rest of the phase {r:.2f} us")
+    f = (p[:, lo:hi, 10] - p[:, lo:hi, 0]).mean() / 1e3
+    g = (p[:, lo:hi, 11] - p[:, lo:hi, 10]).mean() / 1e3
+    n = (p[:, lo:hi, 1] - p[:, lo:hi, 11]).mean() / 1e3
+    print(f"qkv staging: flags seen after {f:.2f} us, gather {g:.2f} us, norm + convert {n:.2f} us")
+    if hi - lo > 2:
+        # the last CTA's down-phase flag post (stamp 12 of layer l) -> every CTA has seen all flags (stamp 10 of layer l+1)
+        post = p[:, lo:hi - 1, 12].max(0)
+        seen = p[:, lo + 1:hi, 10]
+        print(f"flag hop: last post -> seen by a CTA: mean {(seen - post[None]).mean() / 1e3:.2f} us, "
+              f"max {(seen - post[None]).max(0).mean() / 1e3:.2f} us")
     if hi - lo > 1:
         per = (p[:, lo + 1:hi, 0] - p[:, lo:hi - 1, 0]).mean() / 1e3
         print(f"layer period {per:.2f} us -> {per * cfg.n_layer / 1e3:.3f} ms for {cfg.n_layer} layers")
