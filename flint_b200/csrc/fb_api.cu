@@ -18,7 +18,6 @@ struct fb_ctx {
   uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
   const void *n1, *n2, *nf, *embed;
   float* invf;
-  uint8_t *vw_qkv, *vw_o, *vw_gu, *vw_d, *vw_lm;                    // row-record copies read by the verify kernels
   DevStatus* status;
   void *kc, *vc;
   int max_seq, maxchunks;
@@ -36,6 +35,7 @@ struct fb_ctx {
   uint64_t* peer_inbox[8];
   bool peers_open[8];
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
+  float* vpart;                                                     // verify attention: per-span partials
   int max_fly;
 };
 
@@ -151,52 +151,75 @@ cudaError_t launch_repack(const void* q, const void* s, const void* z, int layer
   return cudaGetLastError();
 }
 
-template <int MT, int KC, int EPI, int HD>
-cudaError_t launch_vgemm_kc(const VGemmParams& p, cudaStream_t st) {
+template <int MT, int K, int EPI, int HD>
+cudaError_t launch_vgemm_k(const VGemmParams& p, cudaStream_t st) {
   static bool configured = false;
-  constexpr int smem_max = v_gemm_smem<MT, KC>(2 * 14336 / 128);   // widest supported K, scales and zeros
-  const int smem = v_gemm_smem<MT, KC>((p.K / 128) * (p.has_zeros ? 2 : 1));
-  if (smem > smem_max) return cudaErrorInvalidValue;
+  using V = VG<MT, K>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, KC, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem(true));
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  v_gemm<MT, KC, EPI, HD><<<(p.rows + VCfg<MT>::RT - 1) / VCfg<MT>::RT, 256, smem, st>>>(p);
+  v_gemm<MT, K, EPI, HD><<<(p.rows + V::ROWS - 1) / V::ROWS, 256, V::smem(p.has_zeros != 0), st>>>(p);
   return cudaGetLastError();
 }
-template <int MT, int EPI, int HD>
-cudaError_t launch_vgemm(const VGemmParams& p, cudaStream_t st) {
-  if (VCfg<MT>::KCMAX >= 512 && p.K % 512 == 0) return launch_vgemm_kc<MT, (VCfg<MT>::KCMAX >= 512 ? 512 : 256), EPI, HD>(p, st);
-  return (p.K % 256 == 0) ? launch_vgemm_kc<MT, 256, EPI, HD>(p, st) : launch_vgemm_kc<MT, 128, EPI, HD>(p, st);
-}
+// the shapes the decode kernel table knows: K = model width for QKV / gate-up / LM head and O, FFN width for down
 template <int MT, int EPI>
-cudaError_t launch_vgemm_hd(const VGemmParams& p, int hd, cudaStream_t st) {
-  if (EPI != EPI_QKV) return launch_vgemm<MT, EPI, 64>(p, st);
-  switch (hd) {
-    case 64: return launch_vgemm<MT, EPI, 64>(p, st);
-    case 80: return launch_vgemm<MT, EPI, 80>(p, st);
-    case 128: return launch_vgemm<MT, EPI, 128>(p, st);
+cudaError_t launch_vgemm_shape(const VGemmParams& p, int k, int hd, cudaStream_t st) {
+  if constexpr (EPI == EPI_QKV) {
+    if (k == 512 && hd == 64) return launch_vgemm_k<MT, 512, EPI, 64>(p, st);
+    if (k == 2560 && hd == 80) return launch_vgemm_k<MT, 2560, EPI, 80>(p, st);
+    if (k == 2560 && hd == 64) return launch_vgemm_k<MT, 2560, EPI, 64>(p, st);
+    if (k == 4096 && hd == 128) return launch_vgemm_k<MT, 4096, EPI, 128>(p, st);
+    return cudaErrorInvalidValue;
+  } else {
+    switch (k) {
+      case 512: return launch_vgemm_k<MT, 512, EPI, 64>(p, st);
+      case 2560: return launch_vgemm_k<MT, 2560, EPI, 64>(p, st);
+      case 4096: return launch_vgemm_k<MT, 4096, EPI, 64>(p, st);
+    }
+    if constexpr (EPI == EPI_RESID) {
+      switch (k) {
+        case 1408: return launch_vgemm_k<MT, 1408, EPI_RESID, 64>(p, st);
+        case 8192: return launch_vgemm_k<MT, 8192, EPI_RESID, 64>(p, st);
+        case 14336: return launch_vgemm_k<MT, 14336, EPI_RESID, 64>(p, st);
+      }
+    }
+    return cudaErrorInvalidValue;
   }
-  return cudaErrorInvalidValue;
 }
 template <int EPI>
-cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int hd, cudaStream_t st) {
+cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int k, int hd, cudaStream_t st) {
   switch (mt) {
-    case 16: return launch_vgemm_hd<16, EPI>(p, hd, st);
-    case 32: return launch_vgemm_hd<32, EPI>(p, hd, st);
-    case 64: return launch_vgemm_hd<64, EPI>(p, hd, st);
+    case 16: return launch_vgemm_shape<16, EPI>(p, k, hd, st);
+    case 32: return launch_vgemm_shape<32, EPI>(p, k, hd, st);
+    case 64: return launch_vgemm_shape<64, EPI>(p, k, hd, st);
   }
   return cudaErrorInvalidValue;
 }
+cudaError_t launch_vnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D, int M, float eps,
+                         cudaStream_t st) {
+  if (D % 16 || D > 8 * 256 * 2) return cudaErrorInvalidValue;
+  if (D <= 8 * 256) v_rmsnorm<1><<<M, 256, 0, st>>>(h, w, xn_t, xn_nat, D, eps);
+  else v_rmsnorm<2><<<M, 256, 0, st>>>(h, w, xn_t, xn_nat, D, eps);
+  return cudaGetLastError();
+}
+constexpr int kVSpans = 32;       // most spans of positions a kv head's attention is cut into
+
 cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint8_t* amask,
                          uint16_t* ao, int pos, int M, cudaStream_t st) {
   const fb_model_desc& d = c->d;
-  dim3 grid(M, d.n_kv_head);
-#define FB_VATTN(HD_, R_)                                                                                          \
-  if (d.head_dim == HD_ && c->rgqa == R_) {                                                                        \
-    v_attn<HD_, R_><<<grid, 512, 0, st>>>(q, kc, vc, amask, ao, d.n_head, d.n_kv_head, pos, M, d.attn_scale);      \
-    return cudaGetLastError();                                                                                     \
+  const int T = pos + M;
+  int S = (T + 63) / 64;
+  if (S > kVSpans) S = kVSpans;
+  const int span = ((T + S - 1) / S + 63) / 64 * 64;
+  S = (T + span - 1) / span;
+#define FB_VATTN(HD_, R_)                                                                                               \
+  if (d.head_dim == HD_ && c->rgqa == R_) {                                                                             \
+    v_attn_mma<HD_, R_><<<dim3(d.n_kv_head, S), 128, 0, st>>>(q, kc, vc, amask, c->vpart, d.n_head, d.n_kv_head, pos, M, \
+                                                              d.attn_scale, span);                                      \
+    v_attn_merge<HD_, R_><<<dim3(M, d.n_kv_head), 256, 0, st>>>(c->vpart, ao, d.n_head, d.n_kv_head, M, S);              \
+    return cudaGetLastError();                                                                                          \
   }
   FB_VATTN(64, 4) FB_VATTN(80, 4) FB_VATTN(64, 5) FB_VATTN(128, 4)
 #undef FB_VATTN
@@ -294,6 +317,7 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
       if (e == cudaSuccess) A(cudaMemset(*vp[i], 0, 64 * rowsz[i] * 2));
     }
   }
+  A(dmalloc(&c->vpart, (size_t)d.n_kv_head * 32 * 64 * c->rgqa * (d.head_dim + 2) * 4));
   A(dmalloc(&c->flags, 3 * 256 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
@@ -322,9 +346,9 @@ int fb_ctx_destroy(fb_ctx* c) {
   DeviceGuard g(c->device);
   for (int p = 0; p < 8; p++)
     if (c->peers_open[p] && c->peer_inbox[p]) cudaIpcCloseMemHandle(c->peer_inbox[p]);
-  void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->vw_qkv, c->vw_o, c->vw_gu, c->vw_d, c->vw_lm, c->invf,
+  void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf,
                   c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags,
-                  c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->inbox};
+                  c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -466,29 +490,19 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int L = d.n_layer, D = d.dim, FF = d.ffn, HD = d.head_dim;
   const int QKV = (d.n_head + 2 * d.n_kv_head) * HD, QD = d.n_head * HD;
-  struct M { uint8_t **dst, **vdst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
+  struct M { uint8_t** dst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
   M ms[] = {
-      {&c->w_qkv, &c->vw_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
-      {&c->w_o, &c->vw_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
-      {&c->w_gu, &c->vw_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
-      {&c->w_d, &c->vw_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
-      {&c->w_lm, &c->vw_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
+      {&c->w_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
+      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
+      {&c->w_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
+      {&c->w_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
+      {&c->w_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
   };
   for (M& m : ms) {
-    // tiles for the decode kernel
     const size_t bytes = (size_t)m.layers * pad_rows(m.rows, m.k) * rec_bytes_of(m.k, hz);
     if (*m.dst) { cudaFree(*m.dst); *m.dst = nullptr; }
     FB_CUDA(c, dmalloc(m.dst, bytes + 16));
     FB_CUDA(c, launch_repack(m.q, m.s, hz ? m.z : nullptr, m.layers, m.rows, m.k, m.order, m.arg, m.orows, *m.dst, st));
-    // row records for the verify kernels (tensor-parallel contexts have no verify path)
-    if (c->tp_size > 1) continue;
-    const size_t vbytes = (size_t)m.layers * m.rows * vrec_bytes_of(m.k, hz);
-    if (*m.vdst) { cudaFree(*m.vdst); *m.vdst = nullptr; }
-    FB_CUDA(c, dmalloc(m.vdst, vbytes + 16));
-    repack_rows<<<dim3(m.rows, m.layers), 128, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s,
-                                                        hz ? (const uint16_t*)m.z : nullptr, m.rows, m.k, m.order, m.arg,
-                                                        m.orows, *m.vdst);
-    FB_CUDA(c, cudaGetLastError());
   }
   c->n1 = w->n1; c->n2 = w->n2; c->nf = w->nf; c->embed = w->embed;
   c->weights_bound = true;
@@ -546,7 +560,8 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
 int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t* d_depth, const uint8_t* d_amask,
               int32_t M, int32_t pos, float* d_logits, void* d_feat, void* stream) {
   if (!c || !d_depth || !d_amask || (!d_tokens && !d_h)) return FB_ERR_ARG;
-  if (!c->weights_bound || !c->kc || !c->vw_qkv) return FB_ERR_STATE;
+  if (!c->weights_bound || !c->kc) return FB_ERR_STATE;
+  if (c->tp_size > 1) return FB_ERR_STATE;           /* a tensor-parallel rank holds slices only */
   if (!d_h && !c->embed) return FB_ERR_STATE;
   if (M < 1 || M > 64) return FB_ERR_RANGE;          /* never fall through to another M (reference: result.md:112-113) */
   if (pos < 0 || pos + M > c->max_seq) return FB_ERR_RANGE;
@@ -556,7 +571,8 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int D = d.dim, FF = d.ffn, HD = d.head_dim, QD = d.n_head * HD, QKV = (d.n_head + 2 * d.n_kv_head) * HD;
   const bool hz = d.has_zeros != 0;
-  const int recD = vrec_bytes_of(D, hz), recQ = vrec_bytes_of(QD, hz), recF = vrec_bytes_of(FF, hz);
+  const size_t strQ = (size_t)pad_rows(QKV, D) * rec_bytes_of(D, hz), strO = (size_t)pad_rows(D, QD) * rec_bytes_of(QD, hz),
+               strG = (size_t)pad_rows(2 * FF, D) * rec_bytes_of(D, hz), strF = (size_t)pad_rows(D, FF) * rec_bytes_of(FF, hz);
   v_embed<<<M, 256, 0, st>>>(d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh, D, d.vocab, d.emb_mult,
                              &c->status->code);
   FB_CUDA(c, cudaGetLastError());
@@ -567,24 +583,24 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   for (int l = 0; l < d.n_layer; l++) {
     uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
     uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
-    v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
-    p.w = c->vw_qkv + (size_t)l * QKV * recD; p.x_t = c->vxn; p.rows = QKV; p.K = D; p.rec = recD;
+    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+    p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
     p.q = c->vq; p.kc = kcl; p.vc = vcl;
-    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, st));
     FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, st));
-    p.w = c->vw_o + (size_t)l * D * recQ; p.x_t = c->vao; p.rows = D; p.K = QD; p.rec = recQ; p.h = c->vh; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
-    v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, d.rms_eps);
-    p.w = c->vw_gu + (size_t)l * 2 * FF * recD; p.x_t = c->vxn; p.rows = 2 * FF; p.K = D; p.rec = recD; p.act_t = c->vact;
+    p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, st));
+    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+    p.w = c->w_gu + l * strG; p.x_t = c->vxn; p.rows = 2 * FF; p.act_t = c->vact;
     p.out_ld = FF;
-    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, HD, st));
-    p.w = c->vw_d + (size_t)l * D * recF; p.x_t = c->vact; p.rows = D; p.K = FF; p.rec = recF; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, st));
+    p.w = c->w_d + l * strF; p.x_t = c->vact; p.rows = D; p.out_ld = D;
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, FF, HD, st));
   }
-  v_rmsnorm<<<M, 256, 0, st>>>(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, d.rms_eps);
+  FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, M, d.rms_eps, st));
   if (d_logits) {
-    p.w = c->vw_lm; p.x_t = c->vxn; p.rows = d.vocab; p.K = D; p.rec = recD; p.logits = d_logits; p.out_ld = d.vocab;
-    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, HD, st));
+    p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.logits = d_logits; p.out_ld = d.vocab;
+    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, D, HD, st));
   }
   FB_CUDA(c, cudaGetLastError());
   return FB_OK;

@@ -320,30 +320,4 @@ __global__ void dequant_tiles(const uint8_t* in, int rows, int has_zeros, int or
   }
 }
 
-// ------------------------------------------------------------------------------------------------ row-record layout
-// The M-token verify kernels still read one record per weight row: K/2 bytes of nibble words in the caller's word
-// order, then K/128 bf16 scales, then (asymmetric layout only) K/128 bf16 zeros, padded to 16 bytes.
-__host__ __device__ __forceinline__ int vrec_bytes_of(int k, int has_zeros) {
-  const int meta = (k / 128) * 2 * (has_zeros ? 2 : 1);
-  return k / 2 + ((meta + 15) & ~15);
-}
-// one CTA per stream row; blockIdx.y = layer
-__global__ void repack_rows(const uint32_t* q, const uint16_t* s, const uint16_t* z, int rows, int k, int order,
-                            int order_arg, int order_rows, uint8_t* out) {
-  const int j = blockIdx.x;
-  const int src = blockIdx.y * rows + perm_row(j, order, order_arg, order_rows);
-  const int rec = vrec_bytes_of(k, z != nullptr);
-  uint8_t* dst = out + ((size_t)blockIdx.y * rows + j) * rec;
-  const int words = k / 8, groups = k / 128;
-  for (int i = threadIdx.x; i < words; i += blockDim.x) reinterpret_cast<uint32_t*>(dst)[i] = q[(size_t)src * words + i];
-  uint16_t* meta = reinterpret_cast<uint16_t*>(dst + k / 2);
-  const int meta_n = (rec - k / 2) / 2;
-  for (int i = threadIdx.x; i < meta_n; i += blockDim.x) {
-    uint16_t v = 0;
-    if (i < groups) v = s[(size_t)src * groups + i];
-    else if (z != nullptr && i < 2 * groups) v = z[(size_t)src * groups + (i - groups)];
-    meta[i] = v;
-  }
-}
-
 }  // namespace fb

@@ -1,23 +1,25 @@
 // M-token tree verification (EAGLE): every weight row is read once and applied to all M candidate tokens.
 //
-// First version of this path: a short sequence of kernels per layer on one stream (RMSNorm, int4 x bf16 GEMM with a
-// fused epilogue, tree-masked attention), graph-capturable, instead of one persistent kernel. The contraction runs
-// on the tensor pipe through warp-level mma (m16n8k16, bf16 x bf16 -> fp32): weight rows are the M dimension of the
-// MMA, tokens the N dimension. Weights are dequantised in registers straight into A fragments as the exact bf16
-// value (nibble - 8) / 16; the group scale (times 16) is applied in fp32 to each 128-column partial sum, so the
-// arithmetic is the reference's (nib - 8) * s * x with fp32 accumulation, only the summation order differs.
+// A short sequence of kernels per layer on one stream (RMSNorm, int4 x bf16 GEMM with a fused epilogue, tree-masked
+// attention), graph-capturable. The GEMM reads the same tiled streaming layout as the decode kernel and runs on the
+// tensor pipe through warp-level mma (m16n8k16, bf16 x bf16 -> fp32): 16 weight rows are the M dimension of the MMA,
+// 8 tokens the N dimension. A tile word holds, for one lane slot, the nibbles of one weight row in two column ranges
+// (low and high nibble of every byte); masking them leaves bf16 SUBNORMALS nib * 2^-133 (or 16 * nib * 2^-133), and one
+// bf16x2 fma with 2^127 turns those into the exact values (nib - 8) / 64 (or / 4). The group scale (times 64 or 4) is
+// applied in fp32 to each group's partial sum, so the arithmetic is the reference's (nib - 8) * s * x with fp32
+// accumulation; only the summation order differs.
 //
-// Activations that feed a GEMM are stored "k16-transposed": inside every block of 16 columns, column 4a+b sits at
-// position 4b+a. A lane's B fragment (columns t, t+4 and 8+t, 12+t of a k16 step) is then one 8-byte shared-memory
-// load, and the bf16 pair (nibble t, nibble t+4) that one shift+LOP3 extracts from a packed word is its A fragment.
+// Activations that feed a GEMM are stored in "B order": inside every block of 16 columns the sequence is
+// [0 1 8 9 | 2 3 10 11 | 4 5 12 13 | 6 7 14 15], so a lane's B fragment of a k16 step (columns 2t, 2t+1, 2t+8, 2t+9) is
+// one 8-byte shared-memory load.
 #pragma once
 #include "fb_common.cuh"
 
 namespace fb {
 
-__host__ __device__ __forceinline__ int k16_pos(int col) {       // where column `col` lives in the transposed layout
+__host__ __device__ __forceinline__ int k16_pos(int col) {       // where column `col` lives in B order
   const int c = col & 15;
-  return (col & ~15) + ((c & 3) << 2) + (c >> 2);
+  return (col & ~15) + (((c & 7) >> 1) << 2) + ((c >> 3) << 1) + (c & 1);
 }
 
 // ------------------------------------------------------------------------------------------------ small kernels
@@ -34,133 +36,222 @@ __global__ void v_embed(const int32_t* tokens, const uint16_t* embed, const uint
     h[(size_t)m * D + i] = h_in ? h_in[(size_t)m * D + i] : f2bf(bf2f(embed[(size_t)tok * D + i]) * mult);
 }
 
-// xn[m] = bf16((float(h) * r) * float(w)) in the k16-transposed layout; optionally also in natural order (feature out)
-__global__ void v_rmsnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D, float eps) {
-  const int m = blockIdx.x;
-  const uint16_t* hm = h + (size_t)m * D;
-  __shared__ float red[32];
+// xn[m] = bf16((float(h) * r) * float(w)) in B order; optionally also in natural order (feature out).
+// One CTA per token; a thread keeps its 8-element pieces in registers between the two passes (D <= 8 * 256 * NV).
+template <int NV>
+__global__ void __launch_bounds__(256) v_rmsnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D,
+                                                 float eps) {
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const uint4* hm = reinterpret_cast<const uint4*>(h + (size_t)m * D);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  const int nvec = D / 8;
+  __shared__ float red[8];
+  uint4 hv[NV], ww[NV];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = bf2f(hm[i]); ss = fmaf(v, v, ss); }
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const int i = tid + k * 256;
+    hv[k] = make_uint4(0, 0, 0, 0);
+    ww[k] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) { hv[k] = hm[i]; ww[k] = __ldg(wv + i); }
+    const uint32_t p[4] = {hv[k].x, hv[k].y, hv[k].z, hv[k].w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) { ss = fmaf(bflo(p[e]), bflo(p[e]), ss); ss = fmaf(bfhi(p[e]), bfhi(p[e]), ss); }
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
-  for (int i = 0; i < (int)(blockDim.x >> 5); i++) tot += red[i];
+#pragma unroll
+  for (int i = 0; i < 8; i++) tot += red[i];
   const float r = 1.0f / sqrtf(tot / (float)D + eps);
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    const uint16_t v = f2bf(bf2f(hm[i]) * r * bf2f(w[i]));
-    xn_t[(size_t)m * D + k16_pos(i)] = v;
-    if (xn_nat) xn_nat[(size_t)m * D + i] = v;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const int i = tid + k * 256;
+    if (i < nvec) {
+      const uint32_t p[4] = {hv[k].x, hv[k].y, hv[k].z, hv[k].w}, q[4] = {ww[k].x, ww[k].y, ww[k].z, ww[k].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        o[e] = (uint32_t)f2bf(bflo(p[e]) * r * bflo(q[e])) | ((uint32_t)f2bf(bfhi(p[e]) * r * bfhi(q[e])) << 16);
+      // elements 8i .. 8i+7 are half (i & 1) of a 16-block: pair e goes to 32-bit slot 2e + half of the block
+      uint32_t* dst = reinterpret_cast<uint32_t*>(xn_t + (size_t)m * D + (size_t)(i >> 1) * 16);
+#pragma unroll
+      for (int e = 0; e < 4; e++) dst[2 * e + (i & 1)] = o[e];
+      if (xn_nat) reinterpret_cast<uint4*>(xn_nat + (size_t)m * D)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------------ attention
-// One CTA per (token m, kv head): the R query heads of the group share each K/V load. Query m sees every cached
-// position t < pos and, among the M new slots pos..pos+M-1, those with amask[m][t - pos] != 0.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
+
+// Tree-masked attention of all M candidate tokens on the tensor pipe. One CTA per (kv head, span of cached positions):
+// the M * R query rows that share the kv head (row = token * R + head in group) are the M dimension of the MMAs, 64
+// positions at a time the N dimension of Q K^T and the K dimension of P V. Query m sees every cached position
+// t < pos and, among the M new slots pos..pos+M-1, those with amask[m][t - pos] != 0. Probabilities enter P V as a
+// sum of two bf16 values (p = hi + lo), which keeps their fp32 precision to ~2^-17. Every span writes, per query row,
+// an un-normalised partial (acc[HD], running max, denominator); v_attn_merge combines the spans.
 template <int HD, int R>
-__global__ void __launch_bounds__(512) v_attn(const uint16_t* q, const uint16_t* kc, const uint16_t* vc,
-                                              const uint8_t* amask, uint16_t* ao_t, int n_head, int nkv, int pos, int M,
-                                              float scale) {
-  constexpr int LPR = HD / 8, SEG = LPR <= 8 ? 8 : 16, PPW = 32 / SEG, NW = 16, BATCH = 4;
-  const int m = blockIdx.x, kvh = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seg = lane / SEG, sl = lane % SEG;
-  const bool active = sl < LPR;
-  const int d0 = sl * 8, QD = n_head * HD, T = pos + M;
-  __shared__ float wacc[NW][R][HD];
-  __shared__ float wm[NW][R], wd[NW][R];
-  float qf[R][8];
+__global__ void __launch_bounds__(128) v_attn_mma(const uint16_t* q, const uint16_t* kc, const uint16_t* vc,
+                                                  const uint8_t* amask, float* part, int n_head, int nkv, int pos, int M,
+                                                  float scale, int span) {
+  constexpr int CH = 64, KSTEPS = HD / 16, NTD = HD / 8, STR = HD * 2 + 16, PW = HD + 2;
+  static_assert(HD % 16 == 0 && NTD % 2 == 0, "head_dim must be a multiple of 16");
+  __shared__ __align__(16) uint8_t k_s[CH * STR];
+  __shared__ __align__(16) uint8_t v_s[CH * STR];
+  const int kvh = blockIdx.x, sp = blockIdx.y, S = gridDim.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int T = pos + M, QD = n_head * HD, rows = M * R;
+  const int t_begin = sp * span, t_end = min(T, t_begin + span);
+  const int ntile = (rows + 15) / 16;
+  for (int mt0 = 0; mt0 < ntile; mt0 += 4) {
+    const int mt = mt0 + warp;
+    const bool live = mt < ntile;
+    const int r_lo = min(mt * 16 + g, rows - 1), r_hi = min(mt * 16 + g + 8, rows - 1);
+    const int m_lo = r_lo / R, m_hi = r_hi / R;
+    const uint16_t* q_lo = q + (size_t)m_lo * QD + (size_t)(kvh * R + r_lo % R) * HD;
+    const uint16_t* q_hi = q + (size_t)m_hi * QD + (size_t)(kvh * R + r_hi % R) * HD;
+    uint32_t aq[KSTEPS][4];
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (active) v = *reinterpret_cast<const uint4*>(q + (size_t)m * QD + (size_t)(kvh * R + r) * HD + d0);
-    qf[r][0] = bflo(v.x); qf[r][1] = bfhi(v.x); qf[r][2] = bflo(v.y); qf[r][3] = bfhi(v.y);
-    qf[r][4] = bflo(v.z); qf[r][5] = bfhi(v.z); qf[r][6] = bflo(v.w); qf[r][7] = bfhi(v.w);
-  }
-  float mx[R], den[R], acc[R][8];
+    for (int ks = 0; ks < KSTEPS; ks++) {
+      aq[ks][0] = *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks + 2 * t);
+      aq[ks][1] = *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks + 2 * t);
+      aq[ks][2] = *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks + 2 * t + 8);
+      aq[ks][3] = *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks + 2 * t + 8);
+    }
+    float o[NTD][4];
 #pragma unroll
-  for (int r = 0; r < R; r++) {
-    mx[r] = -1e30f; den[r] = 0.f;
+    for (int j = 0; j < NTD; j++)
 #pragma unroll
-    for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
-  }
-  for (int tb0 = warp * PPW; tb0 < T; tb0 += BATCH * NW * PPW) {
-    uint4 kk[BATCH], vv[BATCH];
-    bool valid[BATCH];
+      for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+    float mrun[2] = {-1e30f, -1e30f}, lrun[2] = {0.f, 0.f};
+    for (int c0 = t_begin; c0 < t_end; c0 += CH) {
+      __syncthreads();                                  // the previous chunk's readers are done
+      for (int i = tid; i < CH * (HD / 8); i += 128) {
+        const int row = i / (HD / 8), pc = i % (HD / 8), tp = c0 + row;
+        uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);   // rows past the end: zeros (0 * garbage could be NaN)
+        if (tp < T) {
+          const size_t off = ((size_t)tp * nkv + kvh) * HD + pc * 8;
+          kv = *reinterpret_cast<const uint4*>(kc + off);
+          vv = *reinterpret_cast<const uint4*>(vc + off);
+        }
+        *reinterpret_cast<uint4*>(k_s + row * STR + pc * 16) = kv;
+        *reinterpret_cast<uint4*>(v_s + row * STR + pc * 16) = vv;
+      }
+      __syncthreads();
+      if (!live) continue;
+      float s[8][4];
 #pragma unroll
-    for (int j = 0; j < BATCH; j++) {                 // all loads of a batch are issued before any is used
-      const int t = tb0 + j * NW * PPW + seg;
-      valid[j] = t < T;
-      if (valid[j] && t >= pos) valid[j] = amask[m * M + (t - pos)] != 0;
-      kk[j] = vv[j] = make_uint4(0, 0, 0, 0);
-      if (valid[j] && active) {
-        const size_t off = ((size_t)t * nkv + kvh) * HD + d0;
-        kk[j] = *reinterpret_cast<const uint4*>(kc + off);
-        vv[j] = *reinterpret_cast<const uint4*>(vc + off);
+      for (int nt = 0; nt < 8; nt++) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ks++) {
+          const uint8_t* kr = k_s + (nt * 8 + g) * STR + (16 * ks + 2 * t) * 2;
+          mma_bf16(s[nt], aq[ks], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 16));
+        }
+      }
+      // scale, mask, row maxima (rows g and g + 8; a row's 64 scores live in the 4 lanes of a quad)
+      float mx[2] = {-INFINITY, -INFINITY};
+      const bool tree = c0 + CH > pos;                   // the chunk reaches into the M new slots
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int tp = c0 + nt * 8 + 2 * t + (e & 1);
+          bool ok = tp < T;
+          if (tree && ok && tp >= pos) ok = amask[(e < 2 ? m_lo : m_hi) * M + (tp - pos)] != 0;
+          const float v = ok ? s[nt][e] * scale : -INFINITY;
+          s[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float mn = fmaxf(mrun[h], mx[h]);           // finite: the running maximum starts at -1e30
+        corr[h] = __expf(mrun[h] - mn);
+        mrun[h] = mn;
+        lrun[h] *= corr[h];
+      }
+#pragma unroll
+      for (int j = 0; j < NTD; j++) { o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1]; }
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float pv = __expf(s[nt][e] - mrun[e >> 1]);
+          s[nt][e] = pv;
+          lrun[e >> 1] += pv;                             // this lane's columns; the quad is summed at the end
+        }
+      // O += P V, 16 positions per step
+#pragma unroll
+      for (int kk = 0; kk < 4; kk++) {
+        uint32_t ah[4], al[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float p0 = s[2 * kk + (e >> 1)][(e & 1) * 2], p1 = s[2 * kk + (e >> 1)][(e & 1) * 2 + 1];
+          const float h0 = rbf(p0), h1 = rbf(p1);
+          ah[e] = pack_bf16(h0, h1);
+          al[e] = pack_bf16(p0 - h0, p1 - h1);
+        }
+#pragma unroll
+        for (int j = 0; j < NTD; j += 2) {
+          uint32_t b[4];
+          const int mat = lane >> 3;
+          ldmatrix_x4_trans(b, v_s + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * STR + (j + (mat >> 1)) * 16);
+          mma_bf16(o[j], ah, b[0], b[1]);
+          mma_bf16(o[j], al, b[0], b[1]);
+          mma_bf16(o[j + 1], ah, b[2], b[3]);
+          mma_bf16(o[j + 1], al, b[2], b[3]);
+        }
       }
     }
+    if (live) {
 #pragma unroll
-    for (int j = 0; j < BATCH; j++) {
-      if (tb0 + j * NW * PPW >= T) break;             // warp-uniform
-      const float kf[8] = {bflo(kk[j].x), bfhi(kk[j].x), bflo(kk[j].y), bfhi(kk[j].y), bflo(kk[j].z), bfhi(kk[j].z), bflo(kk[j].w), bfhi(kk[j].w)};
-      const float vf[8] = {bflo(vv[j].x), bfhi(vv[j].x), bflo(vv[j].y), bfhi(vv[j].y), bflo(vv[j].z), bfhi(vv[j].z), bflo(vv[j].w), bfhi(vv[j].w)};
+      for (int h = 0; h < 2; h++) {
+        lrun[h] += __shfl_xor_sync(0xffffffffu, lrun[h], 1);
+        lrun[h] += __shfl_xor_sync(0xffffffffu, lrun[h], 2);
+        const int row = mt * 16 + g + 8 * h;
+        if (row < rows) {
+          float* pr = part + ((size_t)(kvh * S + sp) * rows + row) * PW;
 #pragma unroll
-      for (int r = 0; r < R; r++) {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; e++) s = fmaf(qf[r][e], kf[e], s);
-#pragma unroll
-        for (int o = SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        s *= scale;
-        if (valid[j]) {
-          const float m2 = fmaxf(mx[r], s);
-          const float corr = __expf(mx[r] - m2), w = __expf(s - m2);
-          den[r] = den[r] * corr + w;
-#pragma unroll
-          for (int e = 0; e < 8; e++) acc[r][e] = acc[r][e] * corr + w * vf[e];
-          mx[r] = m2;
+          for (int j = 0; j < NTD; j++)
+            *reinterpret_cast<float2*>(pr + j * 8 + 2 * t) = make_float2(o[j][2 * h], o[j][2 * h + 1]);
+          if (t == 0) { pr[HD] = mrun[h]; pr[HD + 1] = lrun[h]; }
         }
       }
     }
   }
-#pragma unroll
-  for (int off = SEG; off < 32; off <<= 1) {
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-      const float mo = __shfl_xor_sync(0xffffffffu, mx[r], off);
-      const float dn = __shfl_xor_sync(0xffffffffu, den[r], off);
-      const float gm = fmaxf(mx[r], mo);
-      const float wa = __expf(mx[r] - gm), wb = __expf(mo - gm);
-      den[r] = den[r] * wa + dn * wb;
-#pragma unroll
-      for (int e = 0; e < 8; e++) {
-        const float ao_ = __shfl_xor_sync(0xffffffffu, acc[r][e], off);
-        acc[r][e] = acc[r][e] * wa + ao_ * wb;
-      }
-      mx[r] = gm;
-    }
-  }
-  if (seg == 0 && active) {
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-#pragma unroll
-      for (int e = 0; e < 8; e++) wacc[warp][r][d0 + e] = acc[r][e];
-      if (sl == 0) { wm[warp][r] = mx[r]; wd[warp][r] = den[r]; }
-    }
-  }
-  __syncthreads();
+}
+
+// one CTA per (token, kv head): combine the spans' partials, write bf16 in B order
+template <int HD, int R>
+__global__ void __launch_bounds__(256) v_attn_merge(const float* part, uint16_t* ao_t, int n_head, int nkv, int M, int S) {
+  constexpr int PW = HD + 2;
+  const int m = blockIdx.x, kvh = blockIdx.y, rows = M * R, QD = n_head * HD;
   for (int o = threadIdx.x; o < R * HD; o += blockDim.x) {
-    const int r = o / HD, d = o % HD;
+    const int r = o / HD, d = o % HD, row = m * R + r;
+    const float* p0 = part + ((size_t)kvh * S * rows + row) * PW;
     float gm = -1e30f;
-#pragma unroll
-    for (int w = 0; w < NW; w++) gm = fmaxf(gm, wm[w][r]);
-    float Dn = 0.f, A = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; w++) {
-      const float e = __expf(wm[w][r] - gm);
-      Dn += wd[w][r] * e;
-      A += wacc[w][r][d] * e;
+    for (int s2 = 0; s2 < S; s2++) gm = fmaxf(gm, p0[(size_t)s2 * rows * PW + HD]);
+    float A = 0.f, Dn = 0.f;
+    for (int s2 = 0; s2 < S; s2++) {
+      const float* ps = p0 + (size_t)s2 * rows * PW;
+      const float e = __expf(ps[HD] - gm);
+      Dn = fmaf(ps[HD + 1], e, Dn);
+      A = fmaf(ps[d], e, A);
     }
     ao_t[(size_t)m * QD + k16_pos((kvh * R + r) * HD + d)] = f2bf(A / Dn);
   }
@@ -170,14 +261,14 @@ __global__ void __launch_bounds__(512) v_attn(const uint16_t* q, const uint16_t*
 enum { EPI_QKV = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
 
 struct VGemmParams {
-  const uint8_t* w;        // streaming records of this matrix (layer offset applied)
-  const uint16_t* x_t;     // bf16 [MT][K], k16-transposed, rows >= M are padding
-  int rows, K, rec, M, has_zeros;
+  const uint8_t* w;        // tiles of this matrix (layer offset applied)
+  const uint16_t* x_t;     // bf16 [MT][K] in B order, rows >= M are padding
+  int rows, M, has_zeros;
   // epilogue operands
   uint16_t* h;             // RESID: bf16 [M][D] in/out
   uint16_t* q;             // QKV: bf16 [M][QD]
   uint16_t *kc, *vc;       // QKV: layer base of the caches
-  uint16_t* act_t;         // SWIGLU: bf16 [MT][FF] transposed
+  uint16_t* act_t;         // SWIGLU: bf16 [MT][FF] in B order
   float* logits;           // LOGITS: f32 [M][vocab]
   const int32_t* depth;
   const float* invf;
@@ -192,152 +283,186 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// bf16 pair ((nib_t - 8)/16, (nib_{t+4} - 8)/16) of a packed word: rotate the two nibbles to mantissa bits 3..6 of each
-// half, OR in 1.0, subtract 1.5
-__device__ __forceinline__ uint32_t a_pair(uint32_t w, int rot) {
-  const uint32_t v = (__funnelshift_r(w, w, rot) & 0x00780078u) | 0x3F803F80u;
+// low nibbles of a word's two halves (bits 0..3, 16..19) -> bf16 pair ((nib - 8) / 64, ...): the masked bits are the
+// subnormals nib * 2^-133; times 2^127 minus 1/8
+__device__ __forceinline__ uint32_t cvt_lo(uint32_t w) {
   uint32_t d;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(v), "r"(0x3FC03FC0u));
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(w & 0x000F000Fu), "r"(0x7F007F00u), "r"(0xBE00BE00u));
+  return d;
+}
+// nibbles in bits 4..7, 20..23 -> ((nib - 8) / 4, ...): 16 * nib * 2^-133 times 2^127 minus 2
+__device__ __forceinline__ uint32_t cvt_hi(uint32_t w) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(w & 0x00F000F0u), "r"(0x7F007F00u), "r"(0xC000C000u));
   return d;
 }
 
-// CTA: 32 weight rows (two m16 tiles) x all MT tokens; its 8 warps are 2 row tiles x 4 quarters of every K chunk (a
-// quarter never straddles a 128-column group). Every CTA re-reads the activations, so taller tiles halve that traffic;
-// wide chunks amortise the per-chunk barrier; the pipeline is as deep as shared memory allows, because the kernel is
-// latency-bound unless tens of KB of weights per SM are in flight.
-template <int MT>
-struct VCfg {
-  static constexpr int RT = 32;
-  static constexpr int KCMAX = MT <= 32 ? 512 : 256;            // widest K chunk whose activations still fit a stage
-  template <int KC>
-  static constexpr int stages() {
-    constexpr int stage = RT * (KC / 2 + 16) + MT * (KC * 2 + 32);
-    constexpr int budget = MT <= 16 ? 104 * 1024 : 200 * 1024;    // 2 CTAs per SM for the common 16-token case
-    return budget / stage < 2 ? 2 : (budget / stage > 8 ? 8 : budget / stage);
+// CTA: 32 weight rows x all MT tokens. Its 8 warps are 2 blocks of 16 rows x 4 roles; a role is a pair of column
+// ranges (the low- and high-nibble range of the same tile words) and a share of every chunk's steps. Every CTA
+// re-reads the activations, chunk by chunk, through the same cp.async pipeline as its weights; the pipeline is as
+// deep as shared memory allows, because the kernel is latency-bound unless tens of KB per SM are in flight.
+template <int MT, int K>
+struct VG {
+  using C = TCfg<K>;
+  static constexpr int RT = C::RT, NJ = C::NJ, ROWS = 32, TILES = ROWS / RT;
+  static constexpr int PG = NJ >= 2 ? NJ / 2 : 1;          // pairs of ranges
+  static constexpr int SPLIT = 4 / PG;                     // warps that share the steps of one (row block, pair)
+  static constexpr int stage_bytes(int nbc) { return TILES * nbc * 512 + MT * (NJ * 64 * nbc * 2 + 32); }
+  static constexpr int NBC = stage_bytes(2) <= 28 * 1024 ? 2 : 1;     // 4-step blocks per chunk
+  static constexpr int SPW = 4 * NBC / SPLIT;              // steps per warp per chunk
+  static constexpr int XSTRIDE = NJ * 64 * NBC * 2 + 32;   // bytes per token row in a stage (padding spreads the banks)
+  static constexpr int WBYTES = TILES * NBC * 512;
+  static constexpr int STAGE = WBYTES + MT * XSTRIDE;
+  static constexpr int BUDGET = MT <= 16 ? 100 * 1024 : 180 * 1024;   // 2 CTAs per SM for the common 16-token case
+  static constexpr int STAGES = BUDGET / STAGE < 2 ? 2 : (BUDGET / STAGE > 8 ? 8 : BUDGET / STAGE);
+  static constexpr int NCHUNK = C::BQ / NBC;
+  static constexpr int RED = 4 * ROWS * MT * 4;            // the roles' partial sums meet in shared memory
+  static constexpr int smem(bool hz) {
+    return (STAGES * STAGE > RED ? STAGES * STAGE : RED) + ROWS * C::G * 2 * (hz ? 2 : 1);
   }
+  static_assert(SPW >= 1 && C::BQ % NBC == 0 && PG * SPLIT == 4, "verify GEMM geometry");
 };
-template <int MT, int KC, int EPI, int HD>
+
+template <int MT, int K, int EPI, int HD>
 __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
-  constexpr int RT = VCfg<MT>::RT, NT = MT / 8, STAGES = VCfg<MT>::template stages<KC>();
-  constexpr int MTILES = RT / 16, KPARTS = 8 / MTILES;
-  constexpr int WSTRIDE = KC / 2 + 16;          // bytes per weight row in a stage (padding de-conflicts the A loads)
-  constexpr int XSTRIDE = KC * 2 + 32;          // bytes per token row in a stage
-  constexpr int STAGE_BYTES = RT * WSTRIDE + MT * XSTRIDE;
-  constexpr int QCOLS = KC / KPARTS, KSTEPS = QCOLS / 16;
-  static_assert(QCOLS % 16 == 0 && 128 % QCOLS == 0, "a warp's quarter of a chunk lies inside one group");
+  using V = VG<MT, K>;
+  using C = TCfg<K>;
+  constexpr int RT = V::RT, NT = MT / 8, STAGES = V::STAGES, NBC = V::NBC, SPW = V::SPW, ROWS = V::ROWS;
+  constexpr int G = C::G;
   extern __shared__ __align__(128) uint8_t vsm[];
-  uint16_t* s_scale = reinterpret_cast<uint16_t*>(vsm + STAGES * STAGE_BYTES);     // [RT][groups (+zeros)]
+  const bool hz = P.has_zeros != 0;
+  const int meta = G * (hz ? 2 : 1);
+  uint16_t* s_scale = reinterpret_cast<uint16_t*>(vsm + (V::STAGES * V::STAGE > V::RED ? V::STAGES * V::STAGE : V::RED));   // [ROWS][meta]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int mt = warp / KPARTS, kq = warp % KPARTS;
-  const int row0 = blockIdx.x * RT;
-  const int groups = P.K / 128, nchunk = P.K / KC;
-  const int meta = groups * (P.has_zeros ? 2 : 1);
+  const int mb = warp & 1, role = warp >> 1, pg = role % V::PG, kq = role / V::PG;
+  const int row0 = blockIdx.x * ROWS;
+  const int ntiles = (P.rows + RT - 1) / RT, tile0 = row0 / RT;
+  const int tile_b = C::tile(false) + (hz ? RT * G * 2 : 0);
 
   // scales (and zeros) of the 32 rows, once
-  for (int i = tid; i < RT * meta; i += 256) {
+  for (int i = tid; i < ROWS * meta; i += 256) {
     const int r = i / meta, j = i % meta;
-    const int row = min(row0 + r, P.rows - 1);
-    s_scale[i] = reinterpret_cast<const uint16_t*>(P.w + (size_t)row * P.rec + P.K / 2)[j];
+    const int tl = min(tile0 + r / RT, ntiles - 1);
+    const uint16_t* tm = reinterpret_cast<const uint16_t*>(P.w + (size_t)tl * tile_b + C::NIB);
+    s_scale[i] = j < G ? tm[j * RT + r % RT] : tm[RT * G + (j - G) * RT + r % RT];
   }
   auto issue = [&](int chunk, int stage) {
-    uint8_t* sw = vsm + stage * STAGE_BYTES;
-    uint8_t* sx = sw + RT * WSTRIDE;
-    constexpr int WCH = KC / 2 / 16;            // 16-byte pieces per weight row
-    for (int i = tid; i < RT * WCH; i += 256) {
-      const int r = i / WCH, c = i % WCH;
-      const int row = min(row0 + r, P.rows - 1);
-      cp_async16(sw + r * WSTRIDE + c * 16, P.w + (size_t)row * P.rec + (size_t)chunk * (KC / 2) + c * 16);
+    uint8_t* sw = vsm + stage * V::STAGE;
+    uint8_t* sx = sw + V::WBYTES;
+    for (int i = tid; i < V::TILES * NBC * 32; i += 256) {
+      const int p16 = i & 31, b = (i >> 5) % NBC, tl = (i >> 5) / NBC;
+      const int tg = min(tile0 + tl, ntiles - 1);
+      cp_async16(sw + ((tl * NBC + b) * 32 + p16) * 16, P.w + (size_t)tg * tile_b + (size_t)(chunk * NBC + b) * 512 + p16 * 16);
     }
-    constexpr int XCH = KC * 2 / 16;
-    for (int i = tid; i < MT * XCH; i += 256) {
-      const int m = i / XCH, c = i % XCH;
-      cp_async16(sx + m * XSTRIDE + c * 16, P.x_t + (size_t)m * P.K + (size_t)chunk * KC + c * 8);
+    constexpr int PCS = 64 * NBC * 2 / 16;      // 16-byte pieces per (token, range)
+    for (int i = tid; i < MT * V::NJ * PCS; i += 256) {
+      const int c = i % PCS, j = (i / PCS) % V::NJ, m = i / (PCS * V::NJ);
+      cp_async16(sx + m * V::XSTRIDE + j * (64 * NBC * 2) + c * 16,
+                 P.x_t + (size_t)m * K + j * (K / V::NJ) + chunk * (64 * NBC) + c * 8);
     }
   };
+  // this lane's two weight rows of the 16-row block and their word slots
+  const int row_lo = mb * 16 + g, row_hi = row_lo + 8;
+  const int slot_lo = RT == 16 ? 4 * g + t : 4 * (row_lo % RT + RT * pg) + t;
+  const int slot_hi = RT == 16 ? slot_lo : 4 * (row_hi % RT + RT * pg) + t;
+  const int tl_lo = RT == 16 ? mb : row_lo / RT, tl_hi = RT == 16 ? mb : row_hi / RT;
+  const int jA = pg, jB = pg + V::PG;                  // ranges of the low / high nibbles (RT == 16: one range)
   float ct[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; j++)
 #pragma unroll
     for (int e = 0; e < 4; e++) ct[j][e] = 0.f;
-  float xsum[NT][2];                              // asymmetric layout: sum of x per token over the warp's columns
   for (int s = 0; s < STAGES - 1; s++) {
-    if (s < nchunk) issue(s, s);
+    if (s < V::NCHUNK) issue(s, s);
     cp_async_commit();
   }
-  const int rot = (4 * t - 3) & 31;
-  for (int c = 0; c < nchunk; c++) {
+  for (int c = 0; c < V::NCHUNK; c++) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
-    if (c + STAGES - 1 < nchunk) issue(c + STAGES - 1, (c + STAGES - 1) % STAGES);
+    if (c + STAGES - 1 < V::NCHUNK) issue(c + STAGES - 1, (c + STAGES - 1) % STAGES);
     cp_async_commit();
-    const uint8_t* sw = vsm + (c % STAGES) * STAGE_BYTES;
-    const uint8_t* sx = sw + RT * WSTRIDE;
-    float cg[NT][4];
+    const uint8_t* sw = vsm + (c % STAGES) * V::STAGE;
+    const uint8_t* sx = sw + V::WBYTES;
+    const int sc0 = kq * SPW;                           // first chunk-local step of this warp
+    uint32_t w1[SPW], w2[SPW];
 #pragma unroll
-    for (int j = 0; j < NT; j++)
-#pragma unroll
-      for (int e = 0; e < 4; e++) cg[j][e] = 0.f;
-    if (P.has_zeros) {
-#pragma unroll
-      for (int j = 0; j < NT; j++) xsum[j][0] = xsum[j][1] = 0.f;
+    for (int k = 0; k < SPW; k++) {
+      const int sc = sc0 + k, b = sc >> 2, i = sc & 3;
+      w1[k] = *reinterpret_cast<const uint32_t*>(sw + ((tl_lo * NBC + b) * 32 + slot_lo) * 16 + i * 4);
+      w2[k] = RT == 16 ? w1[k] : *reinterpret_cast<const uint32_t*>(sw + ((tl_hi * NBC + b) * 32 + slot_hi) * 16 + i * 4);
     }
+    const int round = (c * NBC) >> 1;                   // the chunk lies inside one round (8 steps) of every range
 #pragma unroll
-    for (int ks = 0; ks < KSTEPS; ks++) {
-      const int colb = kq * QCOLS + ks * 16;      // first column of this k16 step inside the chunk
-      const uint2 w_lo = *reinterpret_cast<const uint2*>(sw + (mt * 16 + g) * WSTRIDE + colb / 2);
-      const uint2 w_hi = *reinterpret_cast<const uint2*>(sw + (mt * 16 + g + 8) * WSTRIDE + colb / 2);
-      uint32_t a[4];
-      a[0] = a_pair(w_lo.x, rot); a[1] = a_pair(w_hi.x, rot); a[2] = a_pair(w_lo.y, rot); a[3] = a_pair(w_hi.y, rot);
+    for (int pass = 0; pass < (RT == 16 ? 1 : 2); pass++) {
+      const int jr = pass == 0 ? jA : jB;
+      float cg[NT][4];
+#pragma unroll
+      for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) cg[j][e] = 0.f;
+      float xsum[NT][2];
+      if (hz) {
+#pragma unroll
+        for (int j = 0; j < NT; j++) xsum[j][0] = xsum[j][1] = 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < SPW; k++) {
+        const int sc = sc0 + k;
+        const int sl = (sc & ~3) | ((sc + jr) & 3);     // this range's local step inside the chunk
+        uint32_t a[4];
+        if (RT == 16) {
+          a[0] = cvt_lo(w1[k]); a[1] = cvt_hi(w1[k]); a[2] = cvt_lo(w1[k] >> 8); a[3] = cvt_hi(w1[k] >> 8);
+        } else if (pass == 0) {
+          a[0] = cvt_lo(w1[k]); a[1] = cvt_lo(w2[k]); a[2] = cvt_lo(w1[k] >> 8); a[3] = cvt_lo(w2[k] >> 8);
+        } else {
+          a[0] = cvt_hi(w1[k]); a[1] = cvt_hi(w2[k]); a[2] = cvt_hi(w1[k] >> 8); a[3] = cvt_hi(w2[k] >> 8);
+        }
+        const uint8_t* xw = sx + jr * (64 * NBC * 2) + sl * 32;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+          const uint2 b = *reinterpret_cast<const uint2*>(xw + (j * 8 + g) * V::XSTRIDE + t * 8);
+          mma_bf16(cg[j], a, b.x, b.y);
+        }
+        if (hz) {
+          // token sums for the z * sum(x) term: C fragment column pair (2t, 2t+1) of n-tile j = tokens j*8+2t, +1
+#pragma unroll
+          for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const uint4* xr = reinterpret_cast<const uint4*>(xw + (j * 8 + 2 * t + e) * V::XSTRIDE);
+              const uint4 v0 = xr[0], v1 = xr[1];
+              xsum[j][e] += bflo(v0.x) + bfhi(v0.x) + bflo(v0.y) + bfhi(v0.y) + bflo(v0.z) + bfhi(v0.z) + bflo(v0.w) + bfhi(v0.w) +
+                            bflo(v1.x) + bfhi(v1.x) + bflo(v1.y) + bfhi(v1.y) + bflo(v1.z) + bfhi(v1.z) + bflo(v1.w) + bfhi(v1.w);
+            }
+        }
+      }
+      const int grp = jr * C::RG + round;
+      // rows g / g+8 of the block; RT == 16 mixes low (x64) and high (x4) nibbles in one MMA
+      const float f_lo = (RT == 16 || pass == 0) ? 64.f : 4.f, f_hi = (RT == 16) ? 4.f : f_lo;
+      const float s_lo = bf2f(s_scale[row_lo * meta + grp]) * f_lo, s_hi = bf2f(s_scale[row_hi * meta + grp]) * f_hi;
 #pragma unroll
       for (int j = 0; j < NT; j++) {
-        const uint2 b = *reinterpret_cast<const uint2*>(sx + (j * 8 + g) * XSTRIDE + colb * 2 + t * 8);
-        mma_bf16(cg[j], a, b.x, b.y);
+        ct[j][0] = fmaf(s_lo, cg[j][0], ct[j][0]); ct[j][1] = fmaf(s_lo, cg[j][1], ct[j][1]);
+        ct[j][2] = fmaf(s_hi, cg[j][2], ct[j][2]); ct[j][3] = fmaf(s_hi, cg[j][3], ct[j][3]);
       }
-      if (P.has_zeros) {
-        // token sums for the z * sum(x) term: C fragment column pair (2t, 2t+1) of n-tile j = tokens j*8+2t, +1
+      if (hz) {
+        const float z_lo = bf2f(s_scale[row_lo * meta + G + grp]), z_hi = bf2f(s_scale[row_hi * meta + G + grp]);
 #pragma unroll
-        for (int j = 0; j < NT; j++)
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const uint4* xr = reinterpret_cast<const uint4*>(sx + (j * 8 + 2 * t + e) * XSTRIDE + colb * 2);
-            const uint4 v0 = xr[0], v1 = xr[1];
-            xsum[j][e] += bflo(v0.x) + bfhi(v0.x) + bflo(v0.y) + bfhi(v0.y) + bflo(v0.z) + bfhi(v0.z) + bflo(v0.w) + bfhi(v0.w) +
-                          bflo(v1.x) + bfhi(v1.x) + bflo(v1.y) + bfhi(v1.y) + bflo(v1.z) + bfhi(v1.z) + bflo(v1.w) + bfhi(v1.w);
-          }
-      }
-    }
-    const int grp = (c * KC + kq * QCOLS) >> 7;
-    const float s_lo = bf2f(s_scale[(mt * 16 + g) * meta + grp]) * 16.f;
-    const float s_hi = bf2f(s_scale[(mt * 16 + g + 8) * meta + grp]) * 16.f;
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-      ct[j][0] = fmaf(s_lo, cg[j][0], ct[j][0]); ct[j][1] = fmaf(s_lo, cg[j][1], ct[j][1]);
-      ct[j][2] = fmaf(s_hi, cg[j][2], ct[j][2]); ct[j][3] = fmaf(s_hi, cg[j][3], ct[j][3]);
-    }
-    if (P.has_zeros) {
-      const float z_lo = bf2f(s_scale[(mt * 16 + g) * meta + groups + grp]);
-      const float z_hi = bf2f(s_scale[(mt * 16 + g + 8) * meta + groups + grp]);
-#pragma unroll
-      for (int j = 0; j < NT; j++) {
-        ct[j][0] = fmaf(z_lo, xsum[j][0], ct[j][0]); ct[j][1] = fmaf(z_lo, xsum[j][1], ct[j][1]);
-        ct[j][2] = fmaf(z_hi, xsum[j][0], ct[j][2]); ct[j][3] = fmaf(z_hi, xsum[j][1], ct[j][3]);
+        for (int j = 0; j < NT; j++) {
+          ct[j][0] = fmaf(z_lo, xsum[j][0], ct[j][0]); ct[j][1] = fmaf(z_lo, xsum[j][1], ct[j][1]);
+          ct[j][2] = fmaf(z_hi, xsum[j][0], ct[j][2]); ct[j][3] = fmaf(z_hi, xsum[j][1], ct[j][3]);
+        }
       }
     }
   }
   cp_async_wait<0>();
   __syncthreads();
-  // ---- reduce the 4 K-quarters of each row tile through shared memory: y[r][m], r < 32, m < MT ----
-  float* red = reinterpret_cast<float*>(vsm);                     // [KPARTS][RT rows][MT]
+  // ---- the 4 roles of each row block meet in shared memory: y[r][m], r < 32, m < MT ----
+  float* red = reinterpret_cast<float*>(vsm);                     // [4 roles][ROWS][MT]
 #pragma unroll
   for (int j = 0; j < NT; j++) {
-    float* base = red + ((size_t)kq * RT + mt * 16) * MT + j * 8 + 2 * t;
+    float* base = red + ((size_t)role * ROWS + mb * 16) * MT + j * 8 + 2 * t;
     base[(size_t)g * MT] = ct[j][0]; base[(size_t)g * MT + 1] = ct[j][1];
     base[(size_t)(g + 8) * MT] = ct[j][2]; base[(size_t)(g + 8) * MT + 1] = ct[j][3];
   }
@@ -345,25 +470,26 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
   auto Y = [&](int r, int m) {
     float v = red[(size_t)r * MT + m];
 #pragma unroll
-    for (int k = 1; k < KPARTS; k++) v += red[((size_t)k * RT + r) * MT + m];
+    for (int k = 1; k < 4; k++) v += red[((size_t)k * ROWS + r) * MT + m];
     return v;
   };
+  constexpr int RTC = ROWS;
   if (EPI == EPI_RESID) {
-    for (int o = tid; o < RT * MT; o += 256) {
-      const int r = o % RT, m = o / RT, row = row0 + r;
+    for (int o = tid; o < RTC * MT; o += 256) {
+      const int r = o % RTC, m = o / RTC, row = row0 + r;
       if (row < P.rows && m < P.M) {
         uint16_t* hp = P.h + (size_t)m * P.out_ld + row;
         *hp = f2bf(bf2f(*hp) + Y(r, m) * P.resid);
       }
     }
   } else if (EPI == EPI_LOGITS) {
-    for (int o = tid; o < RT * MT; o += 256) {
-      const int r = o % RT, m = o / RT, row = row0 + r;
+    for (int o = tid; o < RTC * MT; o += 256) {
+      const int r = o % RTC, m = o / RTC, row = row0 + r;
       if (row < P.rows && m < P.M) P.logits[(size_t)m * P.out_ld + row] = Y(r, m) / P.logits_scaling;
     }
   } else if (EPI == EPI_SWIGLU) {
-    for (int o = tid; o < (RT / 2) * MT; o += 256) {
-      const int pr = o % (RT / 2), m = o / (RT / 2), row = row0 + 2 * pr;
+    for (int o = tid; o < (RTC / 2) * MT; o += 256) {
+      const int pr = o % (RTC / 2), m = o / (RTC / 2), row = row0 + 2 * pr;
       if (row < P.rows && m < P.M) {
         const float gg = rbf(Y(2 * pr, m)), uu = rbf(Y(2 * pr + 1, m));
         P.act_t[(size_t)m * P.out_ld + k16_pos(row >> 1)] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
@@ -372,8 +498,8 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
   } else {   // EPI_QKV: stream rows (2p, 2p+1) of a head are dims (p, p + HD/2); V rows keep their order
     constexpr int HP = HD / 2;
     const int QD = P.n_head * HD;
-    for (int o = tid; o < (RT / 2) * MT; o += 256) {
-      const int pr = o % (RT / 2), m = o / (RT / 2), rs = row0 + 2 * pr;
+    for (int o = tid; o < (RTC / 2) * MT; o += 256) {
+      const int pr = o % (RTC / 2), m = o / (RTC / 2), rs = row0 + 2 * pr;
       if (rs < P.rows && m < P.M) {
         const float a0 = Y(2 * pr, m), a1 = Y(2 * pr + 1, m);
         const int head = rs / HD, within = rs % HD;
@@ -402,12 +528,5 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
 }
 
 // dynamic shared memory of a launch: the stages (reused by the reduction) + `meta` bf16 scales/zeros per row
-template <int MT, int KC>
-constexpr int v_gemm_smem(int meta) {
-  constexpr int RT = VCfg<MT>::RT;
-  constexpr int stages = VCfg<MT>::template stages<KC>() * (RT * (KC / 2 + 16) + MT * (KC * 2 + 32));
-  constexpr int red = (8 / (RT / 16)) * RT * MT * 4;
-  return (stages > red ? stages : red) + ((RT * meta * 2 + 127) & ~127);
-}
 
 }  // namespace fb
