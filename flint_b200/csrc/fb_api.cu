@@ -151,58 +151,75 @@ cudaError_t launch_repack(const void* q, const void* s, const void* z, int layer
   return cudaGetLastError();
 }
 
+// launch with programmatic stream serialisation: the kernel may start while its predecessor drains (see pdl_wait)
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 template <int MT, int K, int EPI, int HD>
-cudaError_t launch_vgemm_k(const VGemmParams& p, cudaStream_t st) {
+cudaError_t launch_vgemm_k(const VGemmParams& p, int sms, cudaStream_t st) {
   static bool configured = false;
   using V = VG<MT, K>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem(true));
+    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem());
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  v_gemm<MT, K, EPI, HD><<<(p.rows + V::ROWS - 1) / V::ROWS, 256, V::smem(p.has_zeros != 0), st>>>(p);
-  return cudaGetLastError();
+  const int per_sm = (227 * 1024) / (V::smem() + 1024) >= 2 ? 2 : 1;      // persistent CTAs: as many as are resident
+  const int nrb = (p.rows + V::ROWS - 1) / V::ROWS;
+  const int grid = nrb < sms * per_sm ? nrb : sms * per_sm;
+  return launch_pdl(v_gemm<MT, K, EPI, HD>, dim3(grid), dim3(V::NTHR), V::smem(), st, p);
 }
 // the shapes the decode kernel table knows: K = model width for QKV / gate-up / LM head and O, FFN width for down
 template <int MT, int EPI>
-cudaError_t launch_vgemm_shape(const VGemmParams& p, int k, int hd, cudaStream_t st) {
+cudaError_t launch_vgemm_shape(const VGemmParams& p, int k, int hd, int sms, cudaStream_t st) {
   if constexpr (EPI == EPI_QKV) {
-    if (k == 512 && hd == 64) return launch_vgemm_k<MT, 512, EPI, 64>(p, st);
-    if (k == 2560 && hd == 80) return launch_vgemm_k<MT, 2560, EPI, 80>(p, st);
-    if (k == 2560 && hd == 64) return launch_vgemm_k<MT, 2560, EPI, 64>(p, st);
-    if (k == 4096 && hd == 128) return launch_vgemm_k<MT, 4096, EPI, 128>(p, st);
+    if (k == 512 && hd == 64) return launch_vgemm_k<MT, 512, EPI, 64>(p, sms, st);
+    if (k == 2560 && hd == 80) return launch_vgemm_k<MT, 2560, EPI, 80>(p, sms, st);
+    if (k == 2560 && hd == 64) return launch_vgemm_k<MT, 2560, EPI, 64>(p, sms, st);
+    if (k == 4096 && hd == 128) return launch_vgemm_k<MT, 4096, EPI, 128>(p, sms, st);
     return cudaErrorInvalidValue;
   } else {
     switch (k) {
-      case 512: return launch_vgemm_k<MT, 512, EPI, 64>(p, st);
-      case 2560: return launch_vgemm_k<MT, 2560, EPI, 64>(p, st);
-      case 4096: return launch_vgemm_k<MT, 4096, EPI, 64>(p, st);
+      case 512: return launch_vgemm_k<MT, 512, EPI, 64>(p, sms, st);
+      case 2560: return launch_vgemm_k<MT, 2560, EPI, 64>(p, sms, st);
+      case 4096: return launch_vgemm_k<MT, 4096, EPI, 64>(p, sms, st);
     }
     if constexpr (EPI == EPI_RESID) {
       switch (k) {
-        case 1408: return launch_vgemm_k<MT, 1408, EPI_RESID, 64>(p, st);
-        case 8192: return launch_vgemm_k<MT, 8192, EPI_RESID, 64>(p, st);
-        case 14336: return launch_vgemm_k<MT, 14336, EPI_RESID, 64>(p, st);
+        case 1408: return launch_vgemm_k<MT, 1408, EPI_RESID, 64>(p, sms, st);
+        case 8192: return launch_vgemm_k<MT, 8192, EPI_RESID, 64>(p, sms, st);
+        case 14336: return launch_vgemm_k<MT, 14336, EPI_RESID, 64>(p, sms, st);
       }
     }
     return cudaErrorInvalidValue;
   }
 }
 template <int EPI>
-cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int k, int hd, cudaStream_t st) {
+cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int k, int hd, int sms, cudaStream_t st) {
   switch (mt) {
-    case 16: return launch_vgemm_shape<16, EPI>(p, k, hd, st);
-    case 32: return launch_vgemm_shape<32, EPI>(p, k, hd, st);
-    case 64: return launch_vgemm_shape<64, EPI>(p, k, hd, st);
+    case 16: return launch_vgemm_shape<16, EPI>(p, k, hd, sms, st);
+    case 32: return launch_vgemm_shape<32, EPI>(p, k, hd, sms, st);
+    case 64: return launch_vgemm_shape<64, EPI>(p, k, hd, sms, st);
   }
   return cudaErrorInvalidValue;
 }
 cudaError_t launch_vnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D, int M, float eps,
                          cudaStream_t st) {
   if (D % 16 || D > 8 * 256 * 2) return cudaErrorInvalidValue;
-  if (D <= 8 * 256) v_rmsnorm<1><<<M, 256, 0, st>>>(h, w, xn_t, xn_nat, D, eps);
-  else v_rmsnorm<2><<<M, 256, 0, st>>>(h, w, xn_t, xn_nat, D, eps);
-  return cudaGetLastError();
+  if (D <= 8 * 256) return launch_pdl(v_rmsnorm<1>, dim3(M), dim3(256), 0, st, h, w, xn_t, xn_nat, D, eps);
+  return launch_pdl(v_rmsnorm<2>, dim3(M), dim3(256), 0, st, h, w, xn_t, xn_nat, D, eps);
 }
 constexpr int kVSpans = 32;       // most spans of positions a kv head's attention is cut into
 
@@ -216,10 +233,11 @@ cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc,
   S = (T + span - 1) / span;
 #define FB_VATTN(HD_, R_)                                                                                               \
   if (d.head_dim == HD_ && c->rgqa == R_) {                                                                             \
-    v_attn_mma<HD_, R_><<<dim3(d.n_kv_head, S), 128, 0, st>>>(q, kc, vc, amask, c->vpart, d.n_head, d.n_kv_head, pos, M, \
-                                                              d.attn_scale, span);                                      \
-    v_attn_merge<HD_, R_><<<dim3(M, d.n_kv_head), 256, 0, st>>>(c->vpart, ao, d.n_head, d.n_kv_head, M, S);              \
-    return cudaGetLastError();                                                                                          \
+    cudaError_t e = launch_pdl(v_attn_mma<HD_, R_>, dim3(d.n_kv_head, S), dim3(128), 0, st, q, kc, vc, amask, c->vpart,  \
+                               d.n_head, d.n_kv_head, pos, M, d.attn_scale, span);                                      \
+    if (e != cudaSuccess) return e;                                                                                     \
+    return launch_pdl(v_attn_merge<HD_, R_>, dim3(M, d.n_kv_head), dim3(256), 0, st, (const float*)c->vpart, ao, d.n_head, \
+                      d.n_kv_head, M, S);                                                                               \
   }
   FB_VATTN(64, 4) FB_VATTN(80, 4) FB_VATTN(64, 5) FB_VATTN(128, 4)
 #undef FB_VATTN
@@ -573,9 +591,8 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   const bool hz = d.has_zeros != 0;
   const size_t strQ = (size_t)pad_rows(QKV, D) * rec_bytes_of(D, hz), strO = (size_t)pad_rows(D, QD) * rec_bytes_of(QD, hz),
                strG = (size_t)pad_rows(2 * FF, D) * rec_bytes_of(D, hz), strF = (size_t)pad_rows(D, FF) * rec_bytes_of(FF, hz);
-  v_embed<<<M, 256, 0, st>>>(d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh, D, d.vocab, d.emb_mult,
-                             &c->status->code);
-  FB_CUDA(c, cudaGetLastError());
+  FB_CUDA(c, launch_pdl(v_embed, dim3(M), dim3(256), 0, st, d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh,
+                        D, d.vocab, d.emb_mult, &c->status->code));
   VGemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.has_zeros = hz; p.depth = d_depth; p.invf = c->invf; p.n_head = d.n_head; p.nkv = d.n_kv_head; p.pos = pos;
@@ -586,21 +603,21 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
     p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
     p.q = c->vq; p.kc = kcl; p.vc = vcl;
-    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, c->sm_count, st));
     FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, st));
     p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, c->sm_count, st));
     FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
     p.w = c->w_gu + l * strG; p.x_t = c->vxn; p.rows = 2 * FF; p.act_t = c->vact;
     p.out_ld = FF;
-    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, c->sm_count, st));
     p.w = c->w_d + l * strF; p.x_t = c->vact; p.rows = D; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, FF, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, FF, HD, c->sm_count, st));
   }
   FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, M, d.rms_eps, st));
   if (d_logits) {
     p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.logits = d_logits; p.out_ld = d.vocab;
-    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, D, HD, st));
+    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, D, HD, c->sm_count, st));
   }
   FB_CUDA(c, cudaGetLastError());
   return FB_OK;

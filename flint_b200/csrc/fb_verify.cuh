@@ -17,6 +17,12 @@
 
 namespace fb {
 
+// Programmatic dependent launch: every kernel of the verify chain is launched with the stream-serialisation attribute.
+// pdl_trigger() lets the next kernel's CTAs start (and prefetch what does not depend on this kernel) once every CTA of
+// this kernel has called it; pdl_wait() returns when the previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __host__ __device__ __forceinline__ int k16_pos(int col) {       // where column `col` lives in B order
   const int c = col & 15;
   return (col & ~15) + (((c & 7) >> 1) << 2) + ((c >> 3) << 1) + (c & 1);
@@ -27,6 +33,8 @@ __host__ __device__ __forceinline__ int k16_pos(int col) {       // where column
 __global__ void v_embed(const int32_t* tokens, const uint16_t* embed, const uint16_t* h_in, uint16_t* h, int D, int vocab,
                         float mult, int* status_code) {
   const int m = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
   int tok = 0;
   if (!h_in) {
     tok = tokens[m];
@@ -48,12 +56,19 @@ __global__ void __launch_bounds__(256) v_rmsnorm(const uint16_t* h, const uint16
   __shared__ float red[8];
   uint4 hv[NV], ww[NV];
   float ss = 0.f;
+  pdl_trigger();
+#pragma unroll
+  for (int k = 0; k < NV; k++) {       // the norm weights do not depend on the previous kernel
+    const int i = tid + k * 256;
+    ww[k] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) ww[k] = __ldg(wv + i);
+  }
+  pdl_wait();
 #pragma unroll
   for (int k = 0; k < NV; k++) {
     const int i = tid + k * 256;
     hv[k] = make_uint4(0, 0, 0, 0);
-    ww[k] = make_uint4(0, 0, 0, 0);
-    if (i < nvec) { hv[k] = hm[i]; ww[k] = __ldg(wv + i); }
+    if (i < nvec) hv[k] = hm[i];
     const uint32_t p[4] = {hv[k].x, hv[k].y, hv[k].z, hv[k].w};
 #pragma unroll
     for (int e = 0; e < 4; e++) { ss = fmaf(bflo(p[e]), bflo(p[e]), ss); ss = fmaf(bfhi(p[e]), bfhi(p[e]), ss); }
@@ -113,6 +128,8 @@ __global__ void __launch_bounds__(128) v_attn_mma(const uint16_t* q, const uint1
   const int kvh = blockIdx.x, sp = blockIdx.y, S = gridDim.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int T = pos + M, QD = n_head * HD, rows = M * R;
+  pdl_trigger();
+  pdl_wait();
   const int t_begin = sp * span, t_end = min(T, t_begin + span);
   const int ntile = (rows + 15) / 16;
   for (int mt0 = 0; mt0 < ntile; mt0 += 4) {
@@ -236,22 +253,33 @@ __global__ void __launch_bounds__(128) v_attn_mma(const uint16_t* q, const uint1
   }
 }
 
-// one CTA per (token, kv head): combine the spans' partials, write bf16 in B order
+// one CTA per (token, kv head): combine the spans' partials, write bf16 in B order (S <= 32 spans)
 template <int HD, int R>
 __global__ void __launch_bounds__(256) v_attn_merge(const float* part, uint16_t* ao_t, int n_head, int nkv, int M, int S) {
-  constexpr int PW = HD + 2;
+  constexpr int PW = HD + 2, MAXS = 32;
   const int m = blockIdx.x, kvh = blockIdx.y, rows = M * R, QD = n_head * HD;
+  pdl_trigger();
+  pdl_wait();
   for (int o = threadIdx.x; o < R * HD; o += blockDim.x) {
     const int r = o / HD, d = o % HD, row = m * R + r;
     const float* p0 = part + ((size_t)kvh * S * rows + row) * PW;
+    float pm[MAXS], pl[MAXS], pa[MAXS];            // all loads are issued before the first one is used
+#pragma unroll
+    for (int s2 = 0; s2 < MAXS; s2++) {
+      const float* ps = p0 + (size_t)(s2 < S ? s2 : 0) * rows * PW;
+      pm[s2] = s2 < S ? ps[HD] : -1e30f;
+      pl[s2] = s2 < S ? ps[HD + 1] : 0.f;
+      pa[s2] = s2 < S ? ps[d] : 0.f;
+    }
     float gm = -1e30f;
-    for (int s2 = 0; s2 < S; s2++) gm = fmaxf(gm, p0[(size_t)s2 * rows * PW + HD]);
+#pragma unroll
+    for (int s2 = 0; s2 < MAXS; s2++) gm = fmaxf(gm, pm[s2]);
     float A = 0.f, Dn = 0.f;
-    for (int s2 = 0; s2 < S; s2++) {
-      const float* ps = p0 + (size_t)s2 * rows * PW;
-      const float e = __expf(ps[HD] - gm);
-      Dn = fmaf(ps[HD + 1], e, Dn);
-      A = fmaf(ps[d], e, A);
+#pragma unroll
+    for (int s2 = 0; s2 < MAXS; s2++) {
+      const float e = __expf(pm[s2] - gm);
+      Dn = fmaf(pl[s2], e, Dn);
+      A = fmaf(pa[s2], e, A);
     }
     ao_t[(size_t)m * QD + k16_pos((kvh * R + r) * HD + d)] = f2bf(A / Dn);
   }
@@ -297,71 +325,102 @@ __device__ __forceinline__ uint32_t cvt_hi(uint32_t w) {
   return d;
 }
 
-// CTA: 32 weight rows x all MT tokens. Its 8 warps are 2 blocks of 16 rows x 4 roles; a role is a pair of column
-// ranges (the low- and high-nibble range of the same tile words) and a share of every chunk's steps. Every CTA
-// re-reads the activations, chunk by chunk, through the same cp.async pipeline as its weights; the pipeline is as
-// deep as shared memory allows, because the kernel is latency-bound unless tens of KB per SM are in flight.
+// Persistent CTAs: CTA b takes the 32-row blocks b, b + grid, ... of the matrix and runs one cp.async pipeline over all
+// their chunks, so the weights of the next block are already in flight while the epilogue of the current one runs.
+// The 8 warps are 2 blocks of 16 rows x 4 roles; a role is a pair of column ranges (the low- and high-nibble range of
+// the same tile words) and a share of every chunk's steps. The activations of all MT tokens stay resident in shared
+// memory for the whole kernel when they fit (XRES); otherwise their chunks travel through the pipeline with the weights.
 template <int MT, int K>
 struct VG {
   using C = TCfg<K>;
   static constexpr int RT = C::RT, NJ = C::NJ, ROWS = 32, TILES = ROWS / RT;
+  static constexpr int NW = MT <= 16 ? 16 : 8;             // warps: few tokens leave little work per warp, so use more
+  static constexpr int NROLE = NW / 2, NTHR = NW * 32;
   static constexpr int PG = NJ >= 2 ? NJ / 2 : 1;          // pairs of ranges
-  static constexpr int SPLIT = 4 / PG;                     // warps that share the steps of one (row block, pair)
-  static constexpr int stage_bytes(int nbc) { return TILES * nbc * 512 + MT * (NJ * 64 * nbc * 2 + 32); }
-  static constexpr int NBC = stage_bytes(2) <= 28 * 1024 ? 2 : 1;     // 4-step blocks per chunk
+  static constexpr int SPLIT = NROLE / PG;                 // warps that share the steps of one (row block, pair)
+  static constexpr int XRS = K * 2 + 32;                   // resident activations: bytes per token row
+  static constexpr bool XRES = MT * XRS <= 168 * 1024;
+  static constexpr int stage_bytes(int nbc) { return TILES * nbc * 512 + (XRES ? 0 : MT * (NJ * 64 * nbc * 2 + 32)); }
+  static constexpr int NBC = (C::BQ % 2 == 0 && (stage_bytes(2) <= 28 * 1024 || SPLIT > 4)) ? 2 : 1;   // 4-step blocks per chunk
   static constexpr int SPW = 4 * NBC / SPLIT;              // steps per warp per chunk
-  static constexpr int XSTRIDE = NJ * 64 * NBC * 2 + 32;   // bytes per token row in a stage (padding spreads the banks)
+  static constexpr int XSTRIDE = NJ * 64 * NBC * 2 + 32;   // streamed activations: bytes per token row in a stage
   static constexpr int WBYTES = TILES * NBC * 512;
-  static constexpr int STAGE = WBYTES + MT * XSTRIDE;
-  static constexpr int BUDGET = MT <= 16 ? 100 * 1024 : 180 * 1024;   // 2 CTAs per SM for the common 16-token case
+  static constexpr int STAGE = stage_bytes(NBC);
+  static constexpr int RED = NROLE * ROWS * MT * 4;        // the roles' partial sums meet in shared memory
+  static constexpr int XBYTES = XRES ? MT * XRS : 0;
+  static constexpr int MB1 = ROWS * C::G * 2 * 2;          // one block's scales and zeros
+  static constexpr int BUDGET = 216 * 1024 - XBYTES - RED - 2 * MB1;
   static constexpr int STAGES = BUDGET / STAGE < 2 ? 2 : (BUDGET / STAGE > 8 ? 8 : BUDGET / STAGE);
   static constexpr int NCHUNK = C::BQ / NBC;
-  static constexpr int RED = 4 * ROWS * MT * 4;            // the roles' partial sums meet in shared memory
-  static constexpr int smem(bool hz) {
-    return (STAGES * STAGE > RED ? STAGES * STAGE : RED) + ROWS * C::G * 2 * (hz ? 2 : 1);
-  }
-  static_assert(SPW >= 1 && C::BQ % NBC == 0 && PG * SPLIT == 4, "verify GEMM geometry");
+  static constexpr int MDEPTH = (STAGES - 1) / NCHUNK + 2;  // scale blocks in flight
+  static constexpr int smem() { return STAGES * STAGE + XBYTES + RED + MDEPTH * MB1; }
+  static_assert(SPW >= 1 && SPW * SPLIT == 4 * NBC && C::BQ % NBC == 0 && PG * SPLIT == NROLE, "verify GEMM geometry");
+  static_assert(smem() <= 227 * 1024, "verify GEMM shared memory");
 };
 
 template <int MT, int K, int EPI, int HD>
-__global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
+__global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
   using V = VG<MT, K>;
   using C = TCfg<K>;
-  constexpr int RT = V::RT, NT = MT / 8, STAGES = V::STAGES, NBC = V::NBC, SPW = V::SPW, ROWS = V::ROWS;
+  constexpr int RT = V::RT, NT = MT / 8, STAGES = V::STAGES, NBC = V::NBC, SPW = V::SPW, ROWS = V::ROWS, NCHUNK = V::NCHUNK;
   constexpr int G = C::G;
+  constexpr bool XRES = V::XRES;
+  constexpr int NTHR = V::NTHR;
   extern __shared__ __align__(128) uint8_t vsm[];
   const bool hz = P.has_zeros != 0;
-  const int meta = G * (hz ? 2 : 1);
-  uint16_t* s_scale = reinterpret_cast<uint16_t*>(vsm + (V::STAGES * V::STAGE > V::RED ? V::STAGES * V::STAGE : V::RED));   // [ROWS][meta]
+  const int mbytes = RT * G * 2 * (hz ? 2 : 1);        // a tile's scale (and zero) block: bf16 [G][RT] (, [G][RT])
+  uint8_t* s_x = vsm + STAGES * V::STAGE;               // [MT][XRS] resident activations
+  float* red = reinterpret_cast<float*>(s_x + V::XBYTES);   // [roles][ROWS][MT]
+  uint8_t* s_meta = reinterpret_cast<uint8_t*>(red) + V::RED;   // [MDEPTH][TILES][mbytes]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int mb = warp & 1, role = warp >> 1, pg = role % V::PG, kq = role / V::PG;
-  const int row0 = blockIdx.x * ROWS;
-  const int ntiles = (P.rows + RT - 1) / RT, tile0 = row0 / RT;
-  const int tile_b = C::tile(false) + (hz ? RT * G * 2 : 0);
+  const int ntiles = (P.rows + RT - 1) / RT, nrb = (P.rows + ROWS - 1) / ROWS;
+  const int tile_b = C::NIB + mbytes;
+  const int nmine = (int)blockIdx.x < nrb ? (nrb - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int nitems = nmine * NCHUNK;
 
-  // scales (and zeros) of the 32 rows, once
-  for (int i = tid; i < ROWS * meta; i += 256) {
-    const int r = i / meta, j = i % meta;
-    const int tl = min(tile0 + r / RT, ntiles - 1);
-    const uint16_t* tm = reinterpret_cast<const uint16_t*>(P.w + (size_t)tl * tile_b + C::NIB);
-    s_scale[i] = j < G ? tm[j * RT + r % RT] : tm[RT * G + (j - G) * RT + r % RT];
-  }
-  auto issue = [&](int chunk, int stage) {
-    uint8_t* sw = vsm + stage * V::STAGE;
-    uint8_t* sx = sw + V::WBYTES;
-    for (int i = tid; i < V::TILES * NBC * 32; i += 256) {
+  auto issue_w = [&](int n) {
+    const int bi = n / NCHUNK, chunk = n % NCHUNK, tile0 = ((int)blockIdx.x + bi * (int)gridDim.x) * V::TILES;
+    uint8_t* sw = vsm + (n % STAGES) * V::STAGE;
+    for (int i = tid; i < V::TILES * NBC * 32; i += NTHR) {
       const int p16 = i & 31, b = (i >> 5) % NBC, tl = (i >> 5) / NBC;
       const int tg = min(tile0 + tl, ntiles - 1);
       cp_async16(sw + ((tl * NBC + b) * 32 + p16) * 16, P.w + (size_t)tg * tile_b + (size_t)(chunk * NBC + b) * 512 + p16 * 16);
     }
+    if (chunk == 0) {                                   // the block's scales travel with its first chunk
+      uint8_t* sm = s_meta + (bi % V::MDEPTH) * V::MB1;
+      for (int i = tid; i < V::TILES * (mbytes / 16); i += NTHR) {
+        const int tl = i / (mbytes / 16), pc = i % (mbytes / 16);
+        cp_async16(sm + tl * mbytes + pc * 16, P.w + (size_t)min(tile0 + tl, ntiles - 1) * tile_b + C::NIB + pc * 16);
+      }
+    }
+  };
+  auto issue_x = [&](int n) {                           // streamed activations only
+    const int chunk = n % NCHUNK;
+    uint8_t* sx = vsm + (n % STAGES) * V::STAGE + V::WBYTES;
     constexpr int PCS = 64 * NBC * 2 / 16;      // 16-byte pieces per (token, range)
-    for (int i = tid; i < MT * V::NJ * PCS; i += 256) {
+    for (int i = tid; i < MT * V::NJ * PCS; i += NTHR) {
       const int c = i % PCS, j = (i / PCS) % V::NJ, m = i / (PCS * V::NJ);
       cp_async16(sx + m * V::XSTRIDE + j * (64 * NBC * 2) + c * 16,
                  P.x_t + (size_t)m * K + j * (K / V::NJ) + chunk * (64 * NBC) + c * 8);
     }
   };
+  // weights and scales do not depend on the previous kernel: they are in flight before its results are awaited
+  pdl_trigger();
+  for (int s = 0; s < STAGES - 1; s++)
+    if (s < nitems) issue_w(s);
+  pdl_wait();
+  if (XRES) {
+    for (int i = tid; i < MT * (K / 8); i += NTHR) {
+      const int m = i / (K / 8), c = i % (K / 8);
+      cp_async16(s_x + m * V::XRS + c * 16, P.x_t + (size_t)m * K + c * 8);
+    }
+  }
+  for (int s = 0; s < STAGES - 1; s++) {
+    if (!XRES && s < nitems) issue_x(s);
+    cp_async_commit();
+  }
   // this lane's two weight rows of the 16-row block and their word slots
   const int row_lo = mb * 16 + g, row_hi = row_lo + 8;
   const int slot_lo = RT == 16 ? 4 * g + t : 4 * (row_lo % RT + RT * pg) + t;
@@ -373,17 +432,18 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
   for (int j = 0; j < NT; j++)
 #pragma unroll
     for (int e = 0; e < 4; e++) ct[j][e] = 0.f;
-  for (int s = 0; s < STAGES - 1; s++) {
-    if (s < V::NCHUNK) issue(s, s);
-    cp_async_commit();
-  }
-  for (int c = 0; c < V::NCHUNK; c++) {
+  for (int n = 0; n < nitems; n++) {
+    const int c = n % NCHUNK, bi = n / NCHUNK;
     cp_async_wait<STAGES - 2>();
     __syncthreads();
-    if (c + STAGES - 1 < V::NCHUNK) issue(c + STAGES - 1, (c + STAGES - 1) % STAGES);
+    if (n + STAGES - 1 < nitems) {
+      issue_w(n + STAGES - 1);
+      if (!XRES) issue_x(n + STAGES - 1);
+    }
     cp_async_commit();
-    const uint8_t* sw = vsm + (c % STAGES) * V::STAGE;
-    const uint8_t* sx = sw + V::WBYTES;
+    const uint8_t* sw = vsm + (n % STAGES) * V::STAGE;
+    const uint8_t* sx = XRES ? s_x : sw + V::WBYTES;
+    const uint8_t* sm = s_meta + (bi % V::MDEPTH) * V::MB1;
     const int sc0 = kq * SPW;                           // first chunk-local step of this warp
     uint32_t w1[SPW], w2[SPW];
 #pragma unroll
@@ -406,6 +466,9 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
 #pragma unroll
         for (int j = 0; j < NT; j++) xsum[j][0] = xsum[j][1] = 0.f;
       }
+      // first byte of this range's columns of the chunk inside a token row
+      const int xoff = XRES ? (jr * (K / V::NJ) + c * (64 * NBC)) * 2 : jr * (64 * NBC * 2);
+      constexpr int XS = XRES ? V::XRS : V::XSTRIDE;
 #pragma unroll
       for (int k = 0; k < SPW; k++) {
         const int sc = sc0 + k;
@@ -418,10 +481,10 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
         } else {
           a[0] = cvt_hi(w1[k]); a[1] = cvt_hi(w2[k]); a[2] = cvt_hi(w1[k] >> 8); a[3] = cvt_hi(w2[k] >> 8);
         }
-        const uint8_t* xw = sx + jr * (64 * NBC * 2) + sl * 32;
+        const uint8_t* xw = sx + xoff + sl * 32;
 #pragma unroll
         for (int j = 0; j < NT; j++) {
-          const uint2 b = *reinterpret_cast<const uint2*>(xw + (j * 8 + g) * V::XSTRIDE + t * 8);
+          const uint2 b = *reinterpret_cast<const uint2*>(xw + (j * 8 + g) * XS + t * 8);
           mma_bf16(cg[j], a, b.x, b.y);
         }
         if (hz) {
@@ -430,7 +493,7 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
           for (int j = 0; j < NT; j++)
 #pragma unroll
             for (int e = 0; e < 2; e++) {
-              const uint4* xr = reinterpret_cast<const uint4*>(xw + (j * 8 + 2 * t + e) * V::XSTRIDE);
+              const uint4* xr = reinterpret_cast<const uint4*>(xw + (j * 8 + 2 * t + e) * XS);
               const uint4 v0 = xr[0], v1 = xr[1];
               xsum[j][e] += bflo(v0.x) + bfhi(v0.x) + bflo(v0.y) + bfhi(v0.y) + bflo(v0.z) + bfhi(v0.z) + bflo(v0.w) + bfhi(v0.w) +
                             bflo(v1.x) + bfhi(v1.x) + bflo(v1.y) + bfhi(v1.y) + bflo(v1.z) + bfhi(v1.z) + bflo(v1.w) + bfhi(v1.w);
@@ -440,14 +503,16 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
       const int grp = jr * C::RG + round;
       // rows g / g+8 of the block; RT == 16 mixes low (x64) and high (x4) nibbles in one MMA
       const float f_lo = (RT == 16 || pass == 0) ? 64.f : 4.f, f_hi = (RT == 16) ? 4.f : f_lo;
-      const float s_lo = bf2f(s_scale[row_lo * meta + grp]) * f_lo, s_hi = bf2f(s_scale[row_hi * meta + grp]) * f_hi;
+      const uint16_t* m_lo = reinterpret_cast<const uint16_t*>(sm + (row_lo / RT) * mbytes) + row_lo % RT;
+      const uint16_t* m_hi = reinterpret_cast<const uint16_t*>(sm + (row_hi / RT) * mbytes) + row_hi % RT;
+      const float s_lo = bf2f(m_lo[grp * RT]) * f_lo, s_hi = bf2f(m_hi[grp * RT]) * f_hi;
 #pragma unroll
       for (int j = 0; j < NT; j++) {
         ct[j][0] = fmaf(s_lo, cg[j][0], ct[j][0]); ct[j][1] = fmaf(s_lo, cg[j][1], ct[j][1]);
         ct[j][2] = fmaf(s_hi, cg[j][2], ct[j][2]); ct[j][3] = fmaf(s_hi, cg[j][3], ct[j][3]);
       }
       if (hz) {
-        const float z_lo = bf2f(s_scale[row_lo * meta + G + grp]), z_hi = bf2f(s_scale[row_hi * meta + G + grp]);
+        const float z_lo = bf2f(m_lo[(G + grp) * RT]), z_hi = bf2f(m_hi[(G + grp) * RT]);
 #pragma unroll
         for (int j = 0; j < NT; j++) {
           ct[j][0] = fmaf(z_lo, xsum[j][0], ct[j][0]); ct[j][1] = fmaf(z_lo, xsum[j][1], ct[j][1]);
@@ -455,78 +520,77 @@ __global__ void __launch_bounds__(256) v_gemm(const VGemmParams P) {
         }
       }
     }
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  // ---- the 4 roles of each row block meet in shared memory: y[r][m], r < 32, m < MT ----
-  float* red = reinterpret_cast<float*>(vsm);                     // [4 roles][ROWS][MT]
+    if (c != NCHUNK - 1) continue;
+    // ---- the block is complete: its 4 roles meet in shared memory: y[r][m], r < 32, m < MT ----
+    const int row0 = ((int)blockIdx.x + bi * (int)gridDim.x) * ROWS;
 #pragma unroll
-  for (int j = 0; j < NT; j++) {
-    float* base = red + ((size_t)role * ROWS + mb * 16) * MT + j * 8 + 2 * t;
-    base[(size_t)g * MT] = ct[j][0]; base[(size_t)g * MT + 1] = ct[j][1];
-    base[(size_t)(g + 8) * MT] = ct[j][2]; base[(size_t)(g + 8) * MT + 1] = ct[j][3];
-  }
-  __syncthreads();
-  auto Y = [&](int r, int m) {
-    float v = red[(size_t)r * MT + m];
+    for (int j = 0; j < NT; j++) {
+      float* base = red + ((size_t)role * ROWS + mb * 16) * MT + j * 8 + 2 * t;
+      base[(size_t)g * MT] = ct[j][0]; base[(size_t)g * MT + 1] = ct[j][1];
+      base[(size_t)(g + 8) * MT] = ct[j][2]; base[(size_t)(g + 8) * MT + 1] = ct[j][3];
 #pragma unroll
-    for (int k = 1; k < 4; k++) v += red[((size_t)k * ROWS + r) * MT + m];
-    return v;
-  };
-  constexpr int RTC = ROWS;
-  if (EPI == EPI_RESID) {
-    for (int o = tid; o < RTC * MT; o += 256) {
-      const int r = o % RTC, m = o / RTC, row = row0 + r;
-      if (row < P.rows && m < P.M) {
-        uint16_t* hp = P.h + (size_t)m * P.out_ld + row;
-        *hp = f2bf(bf2f(*hp) + Y(r, m) * P.resid);
+      for (int e = 0; e < 4; e++) ct[j][e] = 0.f;
+    }
+    __syncthreads();
+    auto Y = [&](int r, int m) {
+      float v = red[(size_t)r * MT + m];
+  #pragma unroll
+      for (int k = 1; k < V::NROLE; k++) v += red[((size_t)k * ROWS + r) * MT + m];
+      return v;
+    };
+      if (EPI == EPI_RESID) {
+      for (int o = tid; o < ROWS * MT; o += NTHR) {
+        const int r = o % ROWS, m = o / ROWS, row = row0 + r;
+        if (row < P.rows && m < P.M) {
+          uint16_t* hp = P.h + (size_t)m * P.out_ld + row;
+          *hp = f2bf(bf2f(*hp) + Y(r, m) * P.resid);
+        }
       }
-    }
-  } else if (EPI == EPI_LOGITS) {
-    for (int o = tid; o < RTC * MT; o += 256) {
-      const int r = o % RTC, m = o / RTC, row = row0 + r;
-      if (row < P.rows && m < P.M) P.logits[(size_t)m * P.out_ld + row] = Y(r, m) / P.logits_scaling;
-    }
-  } else if (EPI == EPI_SWIGLU) {
-    for (int o = tid; o < (RTC / 2) * MT; o += 256) {
-      const int pr = o % (RTC / 2), m = o / (RTC / 2), row = row0 + 2 * pr;
-      if (row < P.rows && m < P.M) {
-        const float gg = rbf(Y(2 * pr, m)), uu = rbf(Y(2 * pr + 1, m));
-        P.act_t[(size_t)m * P.out_ld + k16_pos(row >> 1)] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
+    } else if (EPI == EPI_LOGITS) {
+      for (int o = tid; o < ROWS * MT; o += NTHR) {
+        const int r = o % ROWS, m = o / ROWS, row = row0 + r;
+        if (row < P.rows && m < P.M) P.logits[(size_t)m * P.out_ld + row] = Y(r, m) / P.logits_scaling;
       }
-    }
-  } else {   // EPI_QKV: stream rows (2p, 2p+1) of a head are dims (p, p + HD/2); V rows keep their order
-    constexpr int HP = HD / 2;
-    const int QD = P.n_head * HD;
-    for (int o = tid; o < (RTC / 2) * MT; o += 256) {
-      const int pr = o % (RTC / 2), m = o / (RTC / 2), rs = row0 + 2 * pr;
-      if (rs < P.rows && m < P.M) {
-        const float a0 = Y(2 * pr, m), a1 = Y(2 * pr + 1, m);
-        const int head = rs / HD, within = rs % HD;
-        if (head < P.n_head + P.nkv) {
-          const int i = within >> 1;
-          const float x0 = rbf(a0), x1 = rbf(a1);
-          float sn, cs;
-          sincosf((float)(P.pos + P.depth[m]) * P.invf[i], &sn, &cs);
-          const uint16_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
-          if (head < P.n_head) {
-            P.q[(size_t)m * QD + head * HD + i] = y0;
-            P.q[(size_t)m * QD + head * HD + i + HP] = y1;
+    } else if (EPI == EPI_SWIGLU) {
+      for (int o = tid; o < (ROWS / 2) * MT; o += NTHR) {
+        const int pr = o % (ROWS / 2), m = o / (ROWS / 2), row = row0 + 2 * pr;
+        if (row < P.rows && m < P.M) {
+          const float gg = rbf(Y(2 * pr, m)), uu = rbf(Y(2 * pr + 1, m));
+          P.act_t[(size_t)m * P.out_ld + k16_pos(row >> 1)] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
+        }
+      }
+    } else {   // EPI_QKV: stream rows (2p, 2p+1) of a head are dims (p, p + HD/2); V rows keep their order
+      constexpr int HP = HD / 2;
+      const int QD = P.n_head * HD;
+      for (int o = tid; o < (ROWS / 2) * MT; o += NTHR) {
+        const int pr = o % (ROWS / 2), m = o / (ROWS / 2), rs = row0 + 2 * pr;
+        if (rs < P.rows && m < P.M) {
+          const float a0 = Y(2 * pr, m), a1 = Y(2 * pr + 1, m);
+          const int head = rs / HD, within = rs % HD;
+          if (head < P.n_head + P.nkv) {
+            const int i = within >> 1;
+            const float x0 = rbf(a0), x1 = rbf(a1);
+            float sn, cs;
+            sincosf((float)(P.pos + P.depth[m]) * P.invf[i], &sn, &cs);
+            const uint16_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
+            if (head < P.n_head) {
+              P.q[(size_t)m * QD + head * HD + i] = y0;
+              P.q[(size_t)m * QD + head * HD + i + HP] = y1;
+            } else {
+              uint16_t* kr = P.kc + ((size_t)(P.pos + m) * P.nkv + (head - P.n_head)) * HD;
+              kr[i] = y0;
+              kr[i + HP] = y1;
+            }
           } else {
-            uint16_t* kr = P.kc + ((size_t)(P.pos + m) * P.nkv + (head - P.n_head)) * HD;
-            kr[i] = y0;
-            kr[i + HP] = y1;
+            uint16_t* vr = P.vc + ((size_t)(P.pos + m) * P.nkv + (head - P.n_head - P.nkv)) * HD;
+            vr[within] = f2bf(a0);
+            vr[within + 1] = f2bf(a1);
           }
-        } else {
-          uint16_t* vr = P.vc + ((size_t)(P.pos + m) * P.nkv + (head - P.n_head - P.nkv)) * HD;
-          vr[within] = f2bf(a0);
-          vr[within + 1] = f2bf(a1);
         }
       }
     }
   }
+  cp_async_wait<0>();
 }
-
-// dynamic shared memory of a launch: the stages (reused by the reduction) + `meta` bf16 scales/zeros per row
 
 }  // namespace fb
