@@ -252,4 +252,4 @@ def verify_mega_launch(Wqkv, s_qkv, Wo, s_o, n1, Wgu, s_gu, Wd, s_d, n2, nf, Wlm
 def decode_occupancy():
     """[registers/thread, blocks/SM, #SMs, warps/SM, total warps] (reference: kernels/megakernel_decode.cu:239-245)."""
     c = query(torch.cuda.current_device())
-    return [c["regs_decode_kernel"], 1, c["sm_count"], 13, 13 * c["sm_count"]]
+    return [c["regs_decode_kernel"], 1, c["sm_count"], 15, 15 * c["sm_count"]]

@@ -2,7 +2,7 @@
 
     python -m flint_b200.gemv_bench --rows 400000 --k 2560 --iters 5
 
-Prints one line per iteration: device time (CUDA events) and bytes of weight records streamed per second.
+Prints one line per iteration: device time (CUDA events) and bytes of weight tiles streamed per second.
 Also the small, self-contained launch that the ncu captures under profiles/ are taken from.
 """
 import argparse
@@ -40,7 +40,7 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        print(f"iter {it}: {ms * 1e3:.1f} us  {nb / ms / 1e6:.0f} GB/s  ({nb / 1e6:.0f} MB of records, status {int(status[0])})")
+        print(f"iter {it}: {ms * 1e3:.1f} us  {nb / ms / 1e6:.0f} GB/s  ({nb / 1e6:.0f} MB of tiles, status {int(status[0])})")
 
 
 if __name__ == "__main__":

@@ -24,7 +24,7 @@ enum {
   FB_ERR_SHAPE = 2,        /* model shape this build has no kernel for */
   FB_ERR_CUDA = 3,         /* a CUDA runtime call failed; fb_last_status() carries the cudaError_t */
   FB_ERR_STATE = 4,        /* weights / KV cache not bound yet, or context poisoned by an earlier device error */
-  FB_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out (grid barrier, copy barrier, peer flag) */
+  FB_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out (copy barrier, arrival flag, tagged word, peer word) */
   FB_ERR_RANGE = 6         /* pos / M / token outside the bound cache or vocabulary */
 };
 
@@ -149,7 +149,7 @@ int fb_gemv(const void* d_stream_in, int32_t rows, int32_t k, int32_t has_zeros,
  * library this calls.
  *   inputs   : d_q int32 [rows, k/8], d_s bf16 [rows, k/128], d_z bf16 [rows, k/128] or NULL (caller layout), d_x bf16 [k]
  *   outputs  : d_y f32 [rows]; d_status int32[8] (cleared by this call; word 0 becomes FB_ERR_TIMEOUT if a wait ran out)
- *   limit    : rows * (k/2 + 16-byte-padded k/64 [x2 with zeros]) <= 9 MiB, else FB_ERR_RANGE (nothing is launched);
+ *   limit    : fb_stream_bytes(rows, k, zeros) <= 9 MiB, else FB_ERR_RANGE (nothing is launched);
  *              k must be one of the widths fb_gemv supports, else FB_ERR_SHAPE
  *   set-up   : the first call on a device resolves the array's device address; make that first call before any stream
  *              capture begins on that device
@@ -165,8 +165,7 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
  *   what 2: value = device pointer to int64[sm_count * n_layer * 16] (0 = off): %globaltimer stamps (ns) of every CTA
  *           at the phase boundaries of every layer, the run-time replacement of the reference's -DNOSYNC/-DNOATTN diagnostic
  *           builds (reference: kernels/megakernel_decode.cu:15-24)
- *   what 4: bulk weight copies one CTA keeps in flight at once (1..8, default 4)
- *   what 3: kernel flavour: 2 = phases chained by tagged data words (default), 1 = phases separated by grid barriers */
+ *   what 4: bulk weight copies one CTA keeps in flight at once (1..4, default 4) */
 int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
 
 #ifdef __cplusplus
