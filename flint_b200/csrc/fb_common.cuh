@@ -10,6 +10,9 @@
 namespace fb {
 
 // ------------------------------------------------------------------------------------------------ constants
+#ifndef FB_ACC2
+#define FB_ACC2 0     // 1: two accumulator sets per tile product (shorter dependent MMA chain); measured 8 % slower on
+#endif                // the stand-alone GEMV and no faster in the decode kernel: other warps already hide the chain
 #ifndef FB_CW
 #define FB_CW 14      // 14 consumers + 1 producer = 15 warps -> at most 4 per scheduler -> 128 registers per thread
 #endif
@@ -301,7 +304,7 @@ __device__ __forceinline__ void tile_dot(const uint8_t* tile, int slice, const X
   const uint32_t ml = tb + C::NIB + (uint32_t)(jl * C::RG * RT + rl) * 2;
   const uint32_t mh = tb + C::NIB + (uint32_t)(jh * C::RG * RT + rh) * 2;
   const uint32_t fl = smem_u32(x.xf) + (uint32_t)(jl * C::RG) * 16, fh = smem_u32(x.xf) + (uint32_t)(jh * C::RG) * 16;
-  float ct[4] = {0.f, 0.f, 0.f, 0.f}, cg[4], ch[4];      // two accumulator sets halve the dependent MMA chain
+  float ct[4] = {0.f, 0.f, 0.f, 0.f}, cg[4], ch[4];
   float zl = 0.f, zh = 0.f;
   uint4 w4 = lds128(wa);
   uint2 xb[4];
@@ -323,7 +326,7 @@ __device__ __forceinline__ void tile_dot(const uint8_t* tile, int slice, const X
     for (int i = 0; i < 4; i++) {
       const uint32_t w2 = ws[i] >> 8;
       const uint32_t a[4] = {ws[i] & 0x000F000Fu, ws[i] & 0x00F000F0u, w2 & 0x000F000Fu, w2 & 0x00F000F0u};
-      if (i & 1) {
+      if (FB_ACC2 && (i & 1)) {
         if (first && i == 1) mma_f16_first(ch, a, xb[i].x, xb[i].y);
         else mma_f16(ch, a, xb[i].x, xb[i].y);
       } else {
@@ -337,8 +340,9 @@ __device__ __forceinline__ void tile_dot(const uint8_t* tile, int slice, const X
       const float4 Fl = lds128f(fl + ro * 16), Fh = lds128f(fh + ro * 16);
       const float sl = lds_bf16(ml + ro * RT * 2), sh = lds_bf16(mh + ro * RT * 2);
       const float sl2 = sl * Fl.x, sh2 = sh * Fh.y;
-      ct[0] = fmaf(sl2, cg[0] + ch[0], ct[0]); ct[1] = fmaf(sl2, cg[1] + ch[1], ct[1]);
-      ct[2] = fmaf(sh2, cg[2] + ch[2], ct[2]); ct[3] = fmaf(sh2, cg[3] + ch[3], ct[3]);
+      if (FB_ACC2) { cg[0] += ch[0]; cg[1] += ch[1]; cg[2] += ch[2]; cg[3] += ch[3]; }
+      ct[0] = fmaf(sl2, cg[0], ct[0]); ct[1] = fmaf(sl2, cg[1], ct[1]);
+      ct[2] = fmaf(sh2, cg[2], ct[2]); ct[3] = fmaf(sh2, cg[3], ct[3]);
       if (closes) {                                              // once per (row, group): offset and zero point
         zl = fmaf(sl, Fl.z, zl);
         zh = fmaf(sh, Fh.z, zh);

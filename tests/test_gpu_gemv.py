@@ -52,10 +52,25 @@ def test_streaming_layout_dequant_bit_exact(asym, order):
     assert np.array_equal(out.cpu().numpy().view(np.uint32), ref.view(np.uint32))
 
 
-@pytest.mark.parametrize("k", [512, 1408, 2560, 4096, 8192, 14336])
+@pytest.mark.parametrize("k", [512, 640, 1280, 14336])          # tile heights 4, 16, 8, 2
+@pytest.mark.parametrize("asym", [False, True])
+def test_streaming_layout_every_tile_height(k, asym):
+    """Rows that do not fill the last tile: the padding rows must not leak into the rows that exist."""
+    lib = _lib.load()
+    rows = 37
+    q, s, z = _mat(rows, k, 11, asym)
+    st = _repack(lib, q.cuda(), s.cuda(), z.cuda() if z is not None else None)
+    out = torch.empty(rows, k, dtype=torch.float32, device="cuda")
+    _lib.check(lib.fb_dequant(_p(st), rows, k, int(asym), 0, 0, 0, _p(out), None), "fb_dequant")
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), O.c_dequant(q, s, z).view(np.uint32))
+
+
+@pytest.mark.parametrize("k", [512, 640, 1024, 1280, 1408, 1792, 2048, 2560, 3584, 4096, 7168, 8192, 14336])
 @pytest.mark.parametrize("asym", [False, True])
 def test_gemv_vs_oracle(k, asym):
-    """Every K the decode kernels are built for; row counts that are ragged against 148 CTAs and the tile sizes.
+    """Every K the decode kernels are built for (tensor-parallel slices included); row counts that are ragged against
+    148 CTAs and the tile sizes.
     Same criterion family as the reference's GEMV check (reference: bench/int4_kernel_test.py:80-91), tightened:
     the reference accepts rel-L2 < 0.02, fp32 accumulation over identical dequantised weights gives < 1e-5."""
     lib = _lib.load()
@@ -74,6 +89,31 @@ def test_gemv_vs_oracle(k, asym):
         got = y.cpu().numpy()
         scale = np.abs(ref).max() + 1e-6
         assert np.abs(got - ref).max() / scale < 2e-5, (k, rows, np.abs(got - ref).max(), scale)
+
+
+@pytest.mark.parametrize("e", [-100, 60, 100])
+def test_gemv_power_of_two_activations_are_exact(e):
+    """The kernel multiplies fp16 copies of the activations; a power of two per group of 128 columns keeps that exact
+    over the whole bf16 range: scaling x by 2^e (one group by a different power) scales y by exactly 2^e."""
+    lib = _lib.load()
+    rows, k = 300, 2560
+    q, s, z = _mat(rows, k, 21, True)
+    x = torch.randn(k, generator=torch.Generator().manual_seed(6)).bfloat16()
+    x[128:256] *= 2.0 ** -20            # one group far below the others
+    x[512:640] = 0                      # and an all-zero group
+    st = _repack(lib, q.cuda(), s.cuda(), z.cuda())
+    ys = []
+    for f in (1.0, 2.0 ** e):
+        dx = (x.float() * f).bfloat16().cuda()
+        y = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        status = torch.zeros(8, dtype=torch.int32, device="cuda")
+        _lib.check(lib.fb_gemv(_p(st), rows, k, 1, 0, 0, 0, _p(dx), _p(y), _p(status), None), "fb_gemv")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        ys.append(y.cpu().numpy().astype(np.float64))
+    assert np.array_equal(ys[0] * 2.0 ** e, ys[1])
+    ref = O.c_gemv(q, s, z, x)[0]
+    assert np.abs(ys[0] - ref).max() < 2e-5 * (np.abs(ref).max() + 1e-6)
 
 
 def test_gemv_permuted_rows_land_in_source_order():
