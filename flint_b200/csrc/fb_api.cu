@@ -36,7 +36,7 @@ struct fb_ctx {
   bool peers_open[8];
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   float* vpart;                                                     // verify attention: per-span partials
-  int max_fly;
+  int max_fly, poll_words;
 };
 
 namespace {
@@ -377,6 +377,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (!c) return FB_ERR_ARG;
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
+  if (what == 5) { c->poll_words = value != 0; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -562,7 +563,7 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   if (c->tag_base > 0xffffffffu - 2 * span) c->tag_base = 8;      // tags never reach 0 (the value of fresh buffers)
   Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
   Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
-  Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly;
+  Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly; Q.poll_words = c->poll_words;
   Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox;
   for (int p = 0; p < c->tp_size; p++) {
     if (!c->peer_inbox[p]) return FB_ERR_STATE;       /* fb_tp_connect has not been called */

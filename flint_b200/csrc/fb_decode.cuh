@@ -12,6 +12,10 @@
 #pragma once
 #include "fb_pipe.cuh"
 
+#ifndef FB_ATTN_BATCH
+#define FB_ATTN_BATCH 2      // K/V positions a lane group loads before it uses any of them
+#endif
+
 namespace fb {
 
 // GQA flash-decode geometry: a row of K or V (HD bf16) is spread over HD/8 lanes (16 bytes each); a warp handles
@@ -165,7 +169,8 @@ __device__ __forceinline__ void stage_norm_ll(const uint64_t* hll, const uint32_
     wv[k] = pr < npairs ? __ldg(reinterpret_cast<const uint2*>(gw) + pr) : make_uint2(0, 0);
   }
   if (!have_h) {      // layer 0 finds the raw residual (bf16, natural order) already in place
-    wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+    if (nflags > 0) wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+    else named_bar_sync(kBarConsumers, kConsumerThreads);     // every warp has left the phase that read the activations
     if (dbg && tid_c == 0) dbg[10] = (long long)globaltimer_ns();
     ll_gather<MAXP>(hll, D / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
     if (dbg && tid_c == 0) dbg[11] = (long long)globaltimer_ns();
@@ -211,7 +216,8 @@ __device__ __forceinline__ void stage_plain_ll(const uint64_t* src, const uint32
                                                const Smem& sm, int tid_c, const WaitCtl& wc, int layer) {
   uint32_t* xs32 = reinterpret_cast<uint32_t*>(sm.xh);
   const int npairs = K / 4, lane = tid_c & 31;
-  wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+  if (nflags > 0) wait_flags(flags, nflags, tag, tid_c >> 5, lane, wc, layer);
+  else named_bar_sync(kBarConsumers, kConsumerThreads);
   ll_gather<MAXP>(src, K / 2, tag, xs32, tid_c, kConsumerThreads, wc, layer);
   // a thread converts exactly the words it gathered itself
 #pragma unroll
@@ -303,7 +309,7 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
 #pragma unroll
       for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
     }
-    constexpr int BATCH = 2;
+    constexpr int BATCH = FB_ATTN_BATCH;
     const int stride = kConsumerWarps * C::PPW;
     for (int tb = t0 + cw * C::PPW; tb < t1; tb += BATCH * stride) {
       uint2 klo[BATCH], khi[BATCH], vlo[BATCH], vhi[BATCH];
@@ -327,6 +333,18 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
             khi[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off + HP));
             vlo[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off));
             vhi[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off + HP));
+          }
+        }
+      }
+      // long chunks: ask L2 for the rows this warp will load two rounds from now (costs no registers)
+      if (sl < (HD * 2 + 63) / 64) {
+#pragma unroll
+        for (int j = 0; j < BATCH; j++) {
+          const int tp = tb + (2 * BATCH + j) * stride + seg;
+          if (tp < t1) {
+            const size_t off = ((size_t)tp * a.nkv + kvh) * HD;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.kc + off) + sl * 64));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.vc + off) + sl * 64));
           }
         }
       }
@@ -470,6 +488,7 @@ struct Decode2Params {
   float eps, attn_scale, resid, emb_mult, logits_scaling;
   long long* prof;
   unsigned max_fly;
+  int32_t poll_words;         // 1: consumers poll the tagged words themselves instead of waiting for arrival flags first
   // tensor parallelism: this GPU holds a slice of every matrix (heads, FFN columns, vocabulary rows); the partial sums
   // of the K-sharded O and down projections are exchanged by peer stores into every rank's inbox
   int32_t tp_size, tp_rank, vocab_base;
@@ -507,6 +526,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
   static_assert(CG::RT % 4 == 0, "the SwiGLU epilogue packs rows (g, u, g', u') into one tagged word");
   const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
   const int QKV = (P.n_head + 2 * P.n_kv) * HD;
+  const int FG = P.poll_words ? 0 : G, FKV = P.poll_words ? 0 : P.n_kv;     // arrival flags to wait for
   constexpr int recD = rec_bytes_of(KDIM, HZ), recO = rec_bytes_of(KOUT, HZ), recF = rec_bytes_of(KFFN, HZ);
   const size_t strQ = (size_t)pad_rows(QKV, KDIM) * recD, strO = (size_t)pad_rows(D, KOUT) * recO,
                strG = (size_t)pad_rows(2 * FF, KDIM) * recD, strF = (size_t)pad_rows(D, KFFN) * recF;
@@ -617,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
           asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(base) + seg * 64));
         }
       }
-      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
                             sm, tid_c, wc, l, l == 0, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       FB_STAMP(1);
       consume_tiles<CQ, HZ>(pipe, q1 - q0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
@@ -660,7 +680,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       FB_STAMP(3);
       // ================= O projection + residual =================
       {
-        stage_plain_ll<MAXP_O>(P.ao_ll, P.ao_flags, P.n_kv, tg_att, KOUT, sm, tid_c, wc, l);
+        stage_plain_ll<MAXP_O>(P.ao_ll, P.ao_flags, FKV, tg_att, KOUT, sm, tid_c, wc, l);
         FB_STAMP(4);
         consume_tiles<CO, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_o, 0); });
@@ -669,7 +689,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       }
       FB_STAMP(5);
       // ================= gate/up + SwiGLU =================
-      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm, tid_c, wc, l, false);
+      stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm, tid_c, wc, l, false);
       FB_STAMP(6);
       consume_tiles<CG, HZ>(pipe, g1 - g0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
         // rows (g_i, u_i, g_{i+1}, u_{i+1}) -> act[i], act[i+1] -> one tagged word
@@ -688,7 +708,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       FB_STAMP(7);
       // ================= down projection + residual =================
       {
-        stage_plain_ll<MAXP_F>(P.act_ll, P.act_flags, G, tg_gu, FF, sm, tid_c, wc, l);
+        stage_plain_ll<MAXP_F>(P.act_ll, P.act_flags, FG, tg_gu, FF, sm, tid_c, wc, l);
         FB_STAMP(8);
         consume_tiles<CF, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_dn, 1); });
@@ -699,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     }
 #undef FB_STAMP
     // ================= final norm + LM head + arg-max =================
-    stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, G, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm, tid_c, wc, L, false);
+    stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm, tid_c, wc, L, false);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     consume_tiles<CG, HZ>(pipe, l1 - l0, xs_, qs_, cw, lane, wc, L, [&](int row0, float c, int nvalid) {

@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--config", default="granite-3b-class")
     ap.add_argument("--cached", type=int, default=200, help="positions already in the KV cache")
     ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--poll-words", type=int, default=-1, help="1: poll tagged words directly, 0: wait for arrival flags first")
     ap.add_argument("--chunks", type=int, default=0, help="attention chunks per kv head (0: the library's choice)")
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
@@ -30,10 +31,16 @@ def main():
     eng = DecodeEngine(cfg, W, max_seq=max(cfg.block_size, a.cached + a.steps + 8))
     if a.chunks:
         eng.set_option(1, a.chunks)
+    if a.poll_words >= 0:
+        eng.set_option(5, a.poll_words)
     G = query(torch.cuda.current_device())["sm_count"]
     prof = torch.zeros(G * cfg.n_layer * 16, dtype=torch.int64, device="cuda")
-    for pos in range(a.cached):
-        eng.decode(5 + pos, pos, want_logits=False)
+    if a.cached > 2048:      # long contexts: seeded random keys and values instead of decoding every position
+        eng.kc[:, :a.cached].normal_()
+        eng.vc[:, :a.cached].normal_()
+    else:
+        for pos in range(a.cached):
+            eng.decode(5 + pos, pos, want_logits=False)
     nxt = torch.zeros(a.steps + 1, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

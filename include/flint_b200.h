@@ -165,7 +165,8 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
  *   what 2: value = device pointer to int64[sm_count * n_layer * 16] (0 = off): %globaltimer stamps (ns) of every CTA
  *           at the phase boundaries of every layer, the run-time replacement of the reference's -DNOSYNC/-DNOATTN diagnostic
  *           builds (reference: kernels/megakernel_decode.cu:15-24)
- *   what 4: bulk weight copies one CTA keeps in flight at once (1..4, default 4) */
+ *   what 4: bulk weight copies one CTA keeps in flight at once (1..4, default 4)
+ *   what 5: 1 = consumers poll the tagged activation words directly; 0 = they wait for the producers' arrival flags first */
 int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
 
 #ifdef __cplusplus
