@@ -91,11 +91,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_oracle_toks(cfg, packed_cpu, steps: int, pos0: int):
+def cpu_oracle_toks(cfg, packed_cpu, steps: int, pos0: int, warmup: int = 1):
     """Time `steps` decode steps of the CPU oracle (all host threads) at positions pos0.. ; returns tok/s."""
     from oracle import oracle as O
     m = O.OracleModel(cfg, packed_cpu, max_seq=pos0 + steps + 1)
-    m.decode(1, 0)                                   # warm: page the weights in
+    for _ in range(max(1, warmup)):
+        m.decode(1, 0)                               # warm: page the weights in
     tok = 7
     t0 = time.perf_counter()
     for i in range(steps):
@@ -111,7 +112,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="flint_b200")
     ap.add_argument("--config", default="granite-3b-class")
-    ap.add_argument("--cpu-steps", type=int, default=6)
+    ap.add_argument("--cpu-steps", type=int, default=100, help="decode steps of the CPU baseline sample (about 10 s of CPU work)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompts are for profiler captures only")
     a = ap.parse_args()
@@ -133,11 +134,11 @@ def main():
         P = packing.synth_packed(cfg, 0, device="cuda" if torch.cuda.is_available() else "cpu")
         Pc = {k: v.cpu() for k, v in P.items()}
         del P
-        n = max(1, min(a.steps, a.cpu_steps))
-        tps, dt = cpu_oracle_toks(cfg, Pc, n, plen)
+        n = max(1, min(a.steps, 2000))               # one step = one decode token on the host cores (~0.1 s for the 3B model)
+        tps, dt = cpu_oracle_toks(cfg, Pc, n, plen, a.warmup)
         cores = os.cpu_count()
         line = {"impl": "reference", "metric": metric, "value": tps, "unit": unit, "n_gpus": a.gpus, "steps": n,
-                "warmup": 1, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
+                "warmup": max(1, a.warmup), "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
                 "config": {"workload": workload},
                 "cpu_baseline": {"value": tps, "unit": unit, "cores": cores, "kind": "port",
