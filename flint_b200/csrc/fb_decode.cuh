@@ -348,13 +348,12 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
           }
         }
       }
+      // scores of the whole batch first (independent chains), then ONE rescale per head and batch
+      float sc[BATCH][R];
 #pragma unroll
       for (int j = 0; j < BATCH; j++) {
-        if (tb + j * stride >= t1) break;     // warp-uniform
         const float kf[8] = {bflo(klo[j].x), bfhi(klo[j].x), bflo(klo[j].y), bfhi(klo[j].y),
                              bflo(khi[j].x), bfhi(khi[j].x), bflo(khi[j].y), bfhi(khi[j].y)};
-        const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
-                             bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
 #pragma unroll
         for (int r = 0; r < R; r++) {
           float s = 0.f;
@@ -362,15 +361,31 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
           for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
 #pragma unroll
           for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          s *= a.scale;
-          if (valid[j]) {
-            const float m2 = fmaxf(m[r], s);
-            const float corr = __expf(m[r] - m2), w = __expf(s - m2);
-            den[r] = den[r] * corr + w;
+          sc[j][r] = valid[j] ? s * a.scale : -INFINITY;
+        }
+      }
 #pragma unroll
-            for (int e = 0; e < 8; e++) acc[r][e] = acc[r][e] * corr + w * vf[e];
-            m[r] = m2;
-          }
+      for (int r = 0; r < R; r++) {
+        float mb = sc[0][r];
+#pragma unroll
+        for (int j = 1; j < BATCH; j++) mb = fmaxf(mb, sc[j][r]);
+        const float m2 = fmaxf(m[r], mb);                 // finite: m starts at -1e30
+        const float corr = __expf(m[r] - m2);
+        den[r] *= corr;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[r][e] *= corr;
+        m[r] = m2;
+      }
+#pragma unroll
+      for (int j = 0; j < BATCH; j++) {
+        const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
+                             bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const float w = __expf(sc[j][r] - m[r]);        // 0 for a position that does not exist
+          den[r] += w;
+#pragma unroll
+          for (int e = 0; e < 8; e++) acc[r][e] = fmaf(w, vf[e], acc[r][e]);
         }
       }
     }
