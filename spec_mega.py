@@ -66,11 +66,18 @@ def main():
         return (time.perf_counter() - t0) / n
 
     t_ver = timed(lambda: eng.verify(toks, a.cache, dp, am))
-    t_draft = timed(lambda: [draft(feat, emb, torch.arange(32, device="cuda")) for _ in range(5)])   # depth-5 rollout
+    pos32 = torch.arange(32, device="cuda")
+    rollout = lambda: [draft(feat, emb, pos32) for _ in range(5)]                                    # depth-5 rollout
+    t_draft_eager = timed(rollout)
+    g = torch.cuda.CUDAGraph()                       # the reference replays its draft from a CUDA graph too
+    with torch.cuda.graph(g):
+        rollout()
+    t_draft = timed(g.replay)
     path = [0] + list(range(1, a.forced_accept + 1))
     src, dst = kv_moves([0] + [p + 3 for p in path[1:]], a.cache)
     t_mv = timed(lambda: eng.kv_move(src, dst)) if src else 0.0
-    print(f"verify M={a.nodes}: {t_ver * 1e3:.2f} ms   draft rollout: {t_draft * 1e3:.2f} ms   kv move: {t_mv * 1e3:.3f} ms")
+    print(f"verify M={a.nodes}: {t_ver * 1e3:.2f} ms   draft rollout: {t_draft * 1e3:.2f} ms graphed ({t_draft_eager * 1e3:.2f} ms eager)"
+          f"   kv move: {t_mv * 1e3:.3f} ms")
     for acc in range(1, 6):
         print(f"forced accepted length {acc}: {(acc + 1) / (t_draft + t_ver + t_mv):.0f} tok/s")
 
