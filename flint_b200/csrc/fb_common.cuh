@@ -22,7 +22,6 @@ constexpr int kThreads = kConsumerThreads + 32;    // + one producer warp (lane 
 constexpr int kStages = 8;                         // ring depth: 8 x 22.5 KB = 180 KB of weights in flight per SM
 constexpr int kStageBytes = 23040;                 // a stage holds whole tiles (4 tiles of K = 2560, 1 of K = 8192 ...)
 constexpr int kScratchBytes = 40960;               // activations of the phase (<= 14336 fp16), then attention scratch
-constexpr int kXBytes = 28672;
 constexpr int kTailBytes = 6144;                   // mbarriers, flags, reductions, slice partials, owned rows, group factors
 constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + kTailBytes;
 constexpr int kMaxOwnRows = 64;                    // rows of the residual stream one CTA may own
@@ -40,7 +39,7 @@ struct DevStatus {
   int pad;
 };
 
-enum Where { W_FULL = 2, W_EMPTY = 3, W_DRAIN = 4, W_FLAG = 5, W_LANDED = 6 };
+enum Where { W_FULL = 2, W_EMPTY = 3, W_FLAG = 5, W_LANDED = 6 };
 
 // ------------------------------------------------------------------------------------------------ small helpers
 __device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
@@ -61,11 +60,6 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 // loads that must see data written by other SMs during this launch: L2 is the point of coherence
-__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ uint32_t ld_cg_u32(const void* p) {
   uint32_t v;
   asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -75,19 +69,6 @@ __device__ __forceinline__ uint16_t ld_cg_u16(const void* p) {
   uint16_t v;
   asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p) : "memory");
   return v;
-}
-__device__ __forceinline__ float ld_cg_f32(const void* p) {
-  float v;
-  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_acquire_u32(const unsigned* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_add(unsigned* p, unsigned v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ int ld_volatile_s32(const int* p) {
   int v;

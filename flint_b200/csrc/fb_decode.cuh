@@ -36,11 +36,6 @@ __device__ __forceinline__ void ll_store(uint64_t* p, uint32_t payload, uint32_t
 __device__ __forceinline__ void ll_load2(const uint64_t* p, uint64_t& a, uint64_t& b) {
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
-__device__ __forceinline__ uint64_t ll_load1(const uint64_t* p) {
-  uint64_t a;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
-  return a;
-}
 
 // words exchanged between GPUs (peer stores over NVLink, polled in local memory): system scope
 __device__ __forceinline__ void ll_store_sys(uint64_t* p, uint32_t payload, uint32_t tag) {

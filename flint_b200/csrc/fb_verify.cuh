@@ -105,6 +105,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_bf16_first(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
@@ -380,14 +385,25 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
   const int nmine = (int)blockIdx.x < nrb ? (nrb - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nitems = nmine * NCHUNK;
 
+  // every thread copies the same pieces of every chunk: (tile, block, 16-byte piece) -> fixed source and destination offsets
+  constexpr int WPIECES = V::TILES * NBC * 32, WPT = (WPIECES + NTHR - 1) / NTHR;
+  int wtile[WPT], wsrc[WPT], wdst[WPT];
+#pragma unroll
+  for (int k = 0; k < WPT; k++) {
+    const int i = tid + k * NTHR;
+    const int p16 = i & 31, b = (i >> 5) % NBC, tl = (i >> 5) / NBC;
+    wtile[k] = i < WPIECES ? tl : -1;
+    wsrc[k] = b * 512 + p16 * 16;
+    wdst[k] = ((tl * NBC + b) * 32 + p16) * 16;
+  }
   auto issue_w = [&](int n) {
     const int bi = n / NCHUNK, chunk = n % NCHUNK, tile0 = ((int)blockIdx.x + bi * (int)gridDim.x) * V::TILES;
     uint8_t* sw = vsm + (n % STAGES) * V::STAGE;
-    for (int i = tid; i < V::TILES * NBC * 32; i += NTHR) {
-      const int p16 = i & 31, b = (i >> 5) % NBC, tl = (i >> 5) / NBC;
-      const int tg = min(tile0 + tl, ntiles - 1);
-      cp_async16(sw + ((tl * NBC + b) * 32 + p16) * 16, P.w + (size_t)tg * tile_b + (size_t)(chunk * NBC + b) * 512 + p16 * 16);
-    }
+    const uint8_t* src = P.w + (size_t)chunk * (NBC * 512);
+#pragma unroll
+    for (int k = 0; k < WPT; k++)
+      if (wtile[k] >= 0)
+        cp_async16(sw + wdst[k], src + (size_t)min(tile0 + wtile[k], ntiles - 1) * tile_b + wsrc[k]);
     if (chunk == 0) {                                   // the block's scales travel with its first chunk
       uint8_t* sm = s_meta + (bi % V::MDEPTH) * V::MB1;
       for (int i = tid; i < V::TILES * (mbytes / 16); i += NTHR) {
@@ -427,6 +443,7 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
   const int slot_hi = RT == 16 ? slot_lo : 4 * (row_hi % RT + RT * pg) + t;
   const int tl_lo = RT == 16 ? mb : row_lo / RT, tl_hi = RT == 16 ? mb : row_hi / RT;
   const int jA = pg, jB = pg + V::PG;                  // ranges of the low / high nibbles (RT == 16: one range)
+  const int moff_lo = (row_lo / RT) * mbytes + (row_lo % RT) * 2, moff_hi = (row_hi / RT) * mbytes + (row_hi % RT) * 2;
   float ct[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; j++)
@@ -456,11 +473,7 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
 #pragma unroll
     for (int pass = 0; pass < (RT == 16 ? 1 : 2); pass++) {
       const int jr = pass == 0 ? jA : jB;
-      float cg[NT][4];
-#pragma unroll
-      for (int j = 0; j < NT; j++)
-#pragma unroll
-        for (int e = 0; e < 4; e++) cg[j][e] = 0.f;
+      float cg[NT][4];                                  // the first step's MMA starts them from zero
       float xsum[NT][2];
       if (hz) {
 #pragma unroll
@@ -485,7 +498,8 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
 #pragma unroll
         for (int j = 0; j < NT; j++) {
           const uint2 b = *reinterpret_cast<const uint2*>(xw + (j * 8 + g) * XS + t * 8);
-          mma_bf16(cg[j], a, b.x, b.y);
+          if (k == 0) mma_bf16_first(cg[j], a, b.x, b.y);
+          else mma_bf16(cg[j], a, b.x, b.y);
         }
         if (hz) {
           // token sums for the z * sum(x) term: C fragment column pair (2t, 2t+1) of n-tile j = tokens j*8+2t, +1
@@ -503,8 +517,8 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
       const int grp = jr * C::RG + round;
       // rows g / g+8 of the block; RT == 16 mixes low (x64) and high (x4) nibbles in one MMA
       const float f_lo = (RT == 16 || pass == 0) ? 64.f : 4.f, f_hi = (RT == 16) ? 4.f : f_lo;
-      const uint16_t* m_lo = reinterpret_cast<const uint16_t*>(sm + (row_lo / RT) * mbytes) + row_lo % RT;
-      const uint16_t* m_hi = reinterpret_cast<const uint16_t*>(sm + (row_hi / RT) * mbytes) + row_hi % RT;
+      const uint16_t* m_lo = reinterpret_cast<const uint16_t*>(sm + moff_lo);
+      const uint16_t* m_hi = reinterpret_cast<const uint16_t*>(sm + moff_hi);
       const float s_lo = bf2f(m_lo[grp * RT]) * f_lo, s_hi = bf2f(m_hi[grp * RT]) * f_hi;
 #pragma unroll
       for (int j = 0; j < NT; j++) {

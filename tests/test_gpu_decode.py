@@ -125,15 +125,19 @@ def test_chained_device_tokens_match_host_loop():
 
 
 def test_determinism_bitwise():
+    """Two contexts give the same bits; so does the hand-over variant that polls the tagged words directly instead of
+    waiting for arrival flags first (it changes when data is looked at, never the arithmetic)."""
     cfg = ModelArgs.from_name("tiny")
     W = _to_cuda(packing.synth_packed(cfg, 0))
     outs = []
-    for _ in range(2):
+    for poll in (0, 0, 1):
         e = DecodeEngine(cfg, W, max_seq=32)
+        e.set_option(5, poll)
         lg = [e.decode(t, p).clone() for p, t in enumerate([1, 2, 3, 4, 5])]
         e.check()
         outs.append(torch.stack(lg))
     assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2])
 
 
 def test_wait_runs_out_reports_timeout_and_context_survives():
