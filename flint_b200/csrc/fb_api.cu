@@ -167,19 +167,28 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
-template <int MT, int K, int EPI, int HD>
-cudaError_t launch_vgemm_k(const VGemmParams& p, int sms, cudaStream_t st) {
+template <int MT, int K, int EPI, int HD, int ROWS>
+cudaError_t launch_vgemm_r(const VGemmParams& p, int sms, cudaStream_t st) {
   static bool configured = false;
-  using V = VG<MT, K>;
+  using V = VG<MT, K, ROWS>;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem());
+    cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem());
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int per_sm = (227 * 1024) / (V::smem() + 1024) >= 2 ? 2 : 1;      // persistent CTAs: as many as are resident
   const int nrb = (p.rows + V::ROWS - 1) / V::ROWS;
   const int grid = nrb < sms * per_sm ? nrb : sms * per_sm;
-  return launch_pdl(v_gemm<MT, K, EPI, HD>, dim3(grid), dim3(V::NTHR), V::smem(), st, p);
+  return launch_pdl(v_gemm<MT, K, EPI, HD, ROWS>, dim3(grid), dim3(V::NTHR), V::smem(), st, p);
+}
+template <int MT, int K, int EPI, int HD>
+cudaError_t launch_vgemm_k(const VGemmParams& p, int sms, cudaStream_t st) {
+  // tall matrices (gate/up, LM head) with few tokens: 64-row blocks halve the per-chunk overhead per MMA and still
+  // give every SM at least one block
+  if constexpr (MT == 16 && (EPI == EPI_SWIGLU || EPI == EPI_LOGITS)) {
+    if (p.rows >= 64 * sms) return launch_vgemm_r<MT, K, EPI, HD, 64>(p, sms, st);
+  }
+  return launch_vgemm_r<MT, K, EPI, HD, 32>(p, sms, st);
 }
 // the shapes the decode kernel table knows: K = model width for QKV / gate-up / LM head and O, FFN width for down
 template <int MT, int EPI>

@@ -332,15 +332,15 @@ __device__ __forceinline__ uint32_t cvt_hi(uint32_t w) {
 
 // Persistent CTAs: CTA b takes the 32-row blocks b, b + grid, ... of the matrix and runs one cp.async pipeline over all
 // their chunks, so the weights of the next block are already in flight while the epilogue of the current one runs.
-// The 8 warps are 2 blocks of 16 rows x 4 roles; a role is a pair of column ranges (the low- and high-nibble range of
+// The warps are 2 (or 4) blocks of 16 rows x 4..8 roles; a role is a pair of column ranges (the low- and high-nibble range of
 // the same tile words) and a share of every chunk's steps. The activations of all MT tokens stay resident in shared
 // memory for the whole kernel when they fit (XRES); otherwise their chunks travel through the pipeline with the weights.
-template <int MT, int K>
+template <int MT, int K, int ROWS_ = 32>
 struct VG {
   using C = TCfg<K>;
-  static constexpr int RT = C::RT, NJ = C::NJ, ROWS = 32, TILES = ROWS / RT;
+  static constexpr int RT = C::RT, NJ = C::NJ, ROWS = ROWS_, TILES = ROWS / RT, NMB = ROWS / 16;
   static constexpr int NW = MT <= 16 ? 16 : 8;             // warps: few tokens leave little work per warp, so use more
-  static constexpr int NROLE = NW / 2, NTHR = NW * 32;
+  static constexpr int NROLE = NW / NMB, NTHR = NW * 32;        // warps = 16-row blocks x roles
   static constexpr int PG = NJ >= 2 ? NJ / 2 : 1;          // pairs of ranges
   static constexpr int SPLIT = NROLE / PG;                 // warps that share the steps of one (row block, pair)
   static constexpr int XRS = K * 2 + 32;                   // resident activations: bytes per token row
@@ -363,9 +363,9 @@ struct VG {
   static_assert(smem() <= 227 * 1024, "verify GEMM shared memory");
 };
 
-template <int MT, int K, int EPI, int HD>
-__global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
-  using V = VG<MT, K>;
+template <int MT, int K, int EPI, int HD, int ROWS_ = 32>
+__global__ void __launch_bounds__(VG<MT, K, ROWS_>::NTHR) v_gemm(const VGemmParams P) {
+  using V = VG<MT, K, ROWS_>;
   using C = TCfg<K>;
   constexpr int RT = V::RT, NT = MT / 8, STAGES = V::STAGES, NBC = V::NBC, SPW = V::SPW, ROWS = V::ROWS, NCHUNK = V::NCHUNK;
   constexpr int G = C::G;
@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(VG<MT, K>::NTHR) v_gemm(const VGemmParams P) {
   uint8_t* s_meta = reinterpret_cast<uint8_t*>(red) + V::RED;   // [MDEPTH][TILES][mbytes]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int mb = warp & 1, role = warp >> 1, pg = role % V::PG, kq = role / V::PG;
+  const int mb = warp % V::NMB, role = warp / V::NMB, pg = role % V::PG, kq = role / V::PG;
   const int ntiles = (P.rows + RT - 1) / RT, nrb = (P.rows + ROWS - 1) / ROWS;
   const int tile_b = C::NIB + mbytes;
   const int nmine = (int)blockIdx.x < nrb ? (nrb - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
