@@ -309,9 +309,12 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   c->maxchunks = c->sm_count / d.n_kv_head;
   if (c->maxchunks < 1) c->maxchunks = 1;
   if (c->maxchunks > 64) c->maxchunks = 64;
-  {  // the merging CTA gathers every other chunk's partial into shared memory next to its own
-    const int wpc_bytes = (c->rgqa * d.head_dim + 2 * c->rgqa) * 4;
-    if (c->maxchunks > kScratchBytes / wpc_bytes) c->maxchunks = kScratchBytes / wpc_bytes;
+  {  // every chunk CTA merges its share of the attention output with one tagged load per thread:
+     // chunks * (R + ceil(R * HD/2 / chunks)) loads must fit the consumer threads
+    const int pairs = c->rgqa * d.head_dim / 2;
+    const int cap = (kConsumerThreads - pairs) / (c->rgqa + 1);
+    if (c->maxchunks > cap) c->maxchunks = cap;
+    if (c->maxchunks < 1) c->maxchunks = 1;
   }
   const int QD = d.n_head * d.head_dim;
   cudaError_t e = cudaSuccess;
@@ -329,7 +332,6 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   const size_t ll_words[8] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
                               (size_t)d.ffn / 2, 2 * (size_t)c->sm_count, (size_t)d.n_kv_head * c->maxchunks * wpc};
   uint64_t** ll_ptrs[8] = {&c->h_ll, &c->q_ll, &c->k_ll, &c->v_ll, &c->ao_ll, &c->act_ll, &c->cand_ll, &c->part_ll};
-  if ((size_t)(c->maxchunks - 1) * wpc * 4 + wpc * 4 > (size_t)kScratchBytes) e = cudaErrorInvalidValue;
   for (int i = 0; i < 8; i++) {
     A(dmalloc(ll_ptrs[i], 8 * ll_words[i] + 16));
     if (e == cudaSuccess) A(cudaMemset(*ll_ptrs[i], 0, 8 * ll_words[i] + 16));

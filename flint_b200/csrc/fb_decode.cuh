@@ -238,7 +238,7 @@ struct Attn2Args {
   const uint16_t* kc;       // layer base: bf16 [max_seq, NKV, HD]
   const uint16_t* vc;
   uint64_t* part_ll;        // [NKV][maxchunks][R*HD + 2R] tagged chunk partials (acc, then m, then d per head)
-  uint32_t* ao_flags;       // [NKV] arrival flags of the attention output
+  uint32_t* ao_flags;       // [NKV * nchunks] arrival flags of the attention output, one per (kv head, chunk) CTA
   int nkv, pos, nchunks, maxchunks;
   float scale;
   uint32_t tag_in, tag_part, tag_out;
@@ -414,7 +414,6 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
     named_bar_sync(kBarConsumers, kConsumerThreads);
     // ---- merge the CTA's warps; one thread per (head, dim pair) ----
     constexpr int WPC = R * HD + 2 * R;                       // words of one chunk partial
-    float* own = reinterpret_cast<float*>(scratch + kScratchBytes) - WPC;   // chunk 0 keeps its partial here
     uint64_t* mine = a.part_ll + ((size_t)kvh * a.maxchunks + c) * WPC;
     for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
       const int r = o / HP, d = 2 * (o % HP);
@@ -432,49 +431,68 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
       const int qh = kvh * R + r;
       if (a.nchunks == 1) {
         ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
-      } else if (c != 0) {
+      } else {
         ll_store(mine + r * HD + d, __float_as_uint(A0), a.tag_part);
         ll_store(mine + r * HD + d + 1, __float_as_uint(A1), a.tag_part);
         if (d == 0) {
           ll_store(mine + R * HD + r, __float_as_uint(gm), a.tag_part);
           ll_store(mine + R * HD + R + r, __float_as_uint(Dn), a.tag_part);
         }
-      } else {
-        // chunk 0 is the merger: its own partial stays in shared memory (own[] overlays nothing that is still read)
-        own[r * HD + d] = A0; own[r * HD + d + 1] = A1;
-        if (d == 0) { own[R * HD + r] = gm; own[R * HD + R + r] = Dn; }
       }
     }
-    const bool merger = (a.nchunks > 1 && c == 0);
-    if (merger) {
-      // chunk 0 of a kv head merges: the other chunks' partials arrive as tagged words, no counter, no fence
-      named_bar_sync(kBarConsumers, kConsumerThreads);        // wacc / wm / wd are dead, own[] is written
-      uint32_t* pg = reinterpret_cast<uint32_t*>(scratch);     // [(nchunks-1)][WPC] payloads
-      const int total = (a.nchunks - 1) * WPC;
-      const uint64_t* src = a.part_ll + ((size_t)kvh * a.maxchunks + 1) * WPC;
-      constexpr int SEGW = 8 * kConsumerThreads;              // words one ll_gather<4> call can own
-      for (int off = 0; off < total; off += SEGW)
-        ll_gather<4>(src + off, min(SEGW, total - off), a.tag_part, pg + off, tid_c, kConsumerThreads, wc, layer);
+    if (a.nchunks > 1) {
+      // Every chunk CTA of the kv head merges its share of the output: dim pairs c, c + nchunks, ... From each chunk's
+      // partial it needs the 2R words (max, denominator) and its own pairs only: one 16-byte tagged load per thread,
+      // no counter, no fence, a single round trip.
+      named_bar_sync(kBarConsumers, kConsumerThreads);        // wacc / wm / wd are dead: scratch is free
+      const int npairs = R * HP;
+      const int nown = (npairs - c + a.nchunks - 1) / a.nchunks;
+      const int per = R + nown;                                // loads per source chunk
+      uint32_t* pg = reinterpret_cast<uint32_t*>(scratch);     // [nchunks][per][2] payloads
+      const int total = a.nchunks * per;                       // <= kConsumerThreads (host checks the shape)
+      if (tid_c < total) {
+        const int cc = tid_c / per, sl2 = tid_c % per;
+        int w;
+        if (sl2 < R) {
+          w = R * HD + 2 * sl2;
+        } else {
+          const int o = c + (sl2 - R) * a.nchunks;
+          w = (o / HP) * HD + 2 * (o % HP);
+        }
+        const uint64_t* src = a.part_ll + ((size_t)kvh * a.maxchunks + cc) * WPC + w;
+        for (unsigned spin = 0;; spin++) {
+          uint64_t u, v;
+          ll_load2(src, u, v);
+          if ((uint32_t)(u >> 32) == a.tag_part && (uint32_t)(v >> 32) == a.tag_part) {
+            pg[2 * tid_c] = (uint32_t)u; pg[2 * tid_c + 1] = (uint32_t)v;
+            break;
+          }
+          if (*wc.s_abort) break;
+          if (spin > 16) __nanosleep(40);
+          if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+          if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)a.tag_part, -4); break; }
+        }
+      }
       named_bar_sync(kBarConsumers, kConsumerThreads);
-      const float* pf = reinterpret_cast<const float*>(pg);
-      for (int o = tid_c; o < R * HP; o += kConsumerThreads) {
-        const int r = o / HP, d = 2 * (o % HP);
-        float gm = own[R * HD + r];
-        for (int cc = 0; cc < a.nchunks - 1; cc++) gm = fmaxf(gm, pf[cc * WPC + R * HD + r]);
-        float e = __expf(own[R * HD + r] - gm);
-        float Dn = own[R * HD + R + r] * e, A0 = own[r * HD + d] * e, A1 = own[r * HD + d + 1] * e;
-        for (int cc = 0; cc < a.nchunks - 1; cc++) {
-          e = __expf(pf[cc * WPC + R * HD + r] - gm);
-          Dn += pf[cc * WPC + R * HD + R + r] * e;
-          A0 += pf[cc * WPC + r * HD + d] * e;
-          A1 += pf[cc * WPC + r * HD + d + 1] * e;
+      if (tid_c < nown) {
+        const float* pf = reinterpret_cast<const float*>(pg);
+        const int o = c + tid_c * a.nchunks, r = o / HP, d = 2 * (o % HP);
+        // words 0..R-1 of a chunk's (max, denominator) area are the maxima, R..2R-1 the denominators
+        float gm = -1e30f;
+        for (int cc = 0; cc < a.nchunks; cc++) gm = fmaxf(gm, pf[cc * per * 2 + r]);
+        float Dn = 0.f, A0 = 0.f, A1 = 0.f;
+        for (int cc = 0; cc < a.nchunks; cc++) {
+          const float e = __expf(pf[cc * per * 2 + r] - gm);
+          Dn += pf[cc * per * 2 + R + r] * e;
+          A0 += pf[(cc * per + R + tid_c) * 2] * e;
+          A1 += pf[(cc * per + R + tid_c) * 2 + 1] * e;
         }
         const int qh = kvh * R + r;
         ll_store(a.ao_ll + (size_t)qh * HP + (d >> 1), (uint32_t)f2bf(A0 / Dn) | ((uint32_t)f2bf(A1 / Dn) << 16), a.tag_out);
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
-    if ((a.nchunks == 1 || merger) && tid_c == 0) st_relaxed_u32(a.ao_flags + kvh, a.tag_out);
+    if (tid_c == 0) st_relaxed_u32(a.ao_flags + kvh * a.nchunks + c, a.tag_out);
   }
 }
 
@@ -536,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
   static_assert(CG::RT % 4 == 0, "the SwiGLU epilogue packs rows (g, u, g', u') into one tagged word");
   const int D = P.dim, FF = P.ffn, L = P.n_layer, V = P.vocab;
   const int QKV = (P.n_head + 2 * P.n_kv) * HD;
-  const int FG = P.poll_words ? 0 : G, FKV = P.poll_words ? 0 : P.n_kv;     // arrival flags to wait for
+  const int FG = P.poll_words ? 0 : G, FKV = P.poll_words ? 0 : P.n_kv * P.nchunks;     // arrival flags to wait for
   constexpr int recD = rec_bytes_of(KDIM, HZ), recO = rec_bytes_of(KOUT, HZ), recF = rec_bytes_of(KFFN, HZ);
   const size_t strQ = (size_t)pad_rows(QKV, KDIM) * recD, strO = (size_t)pad_rows(D, KOUT) * recO,
                strG = (size_t)pad_rows(2 * FF, KDIM) * recD, strF = (size_t)pad_rows(D, KFFN) * recF;
