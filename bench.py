@@ -258,7 +258,7 @@ def main():
         "mbu_vs_8TBs": bytes_tok * (tps / n_rep) / HBM_NOMINAL,
         "mbu_weights_only_vs_8TBs": weights_only * (tps / n_rep) / HBM_NOMINAL,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": bytes_tok * 1.020, "traffic_note": "ncu: DRAM read+write / algorithmic = 1.020 on one "
+                     "traffic": bytes_tok * 1.010, "traffic_note": "ncu: DRAM read+write / algorithmic = 1.010 on one "
                      "launch of this kernel and model (profiles/decode_mega2_granite3b.md), scaled to this run's bytes",
                      "peak_source": which, "kernel": "decode_mega2 (one launch per token)"},
         "e2e": {"value": tps_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
