@@ -43,6 +43,19 @@ class WeightPtrs(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in WEIGHT_FIELDS]
 
 
+class DraftDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("dim", "n_head", "n_kv_head", "inter", "fuse", "vocab", "max_roll",
+                                              "max_tokens")] + \
+               [(n, ctypes.c_float) for n in ("rope_base", "rms_eps", "logits_scaling")]
+
+
+DRAFT_WEIGHT_FIELDS = ("merge", "n1", "n2", "q", "k", "v", "o", "gate", "up", "down", "fout", "nf", "embed")
+
+
+class DraftWeights(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in DRAFT_WEIGHT_FIELDS]
+
+
 class Status(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("code", "cuda_error", "where", "layer", "block", "expected", "seen")]
 
@@ -56,6 +69,7 @@ _PROTOS = {
                                         ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p)]),
     "fb_tp_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "fb_tp_connect": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]),
+    "fb_tp_connect_local": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int32]),
     "fb_last_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(Status)]),
     "fb_bind_weights": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(WeightPtrs), ctypes.c_void_p]),
     "fb_bind_kv": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]),
@@ -74,6 +88,19 @@ _PROTOS = {
     "fb_set_option": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64]),
     "fb_verify": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                  ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_kv_compact": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
+    "fb_sample": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_float,
+                                 ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_accept_chain": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_accept_tree": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p,
+                                      ctypes.c_void_p]),
+    "fb_draft_create": (ctypes.c_int, [ctypes.POINTER(DraftDesc), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]),
+    "fb_draft_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "fb_draft_bind": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(DraftWeights)]),
+    "fb_draft_forward": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "fb_draft_head": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_void_p]),
     "fb_kv_move": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32),
                                   ctypes.c_int32, ctypes.c_void_p]),
 }

@@ -6,10 +6,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 LIB = os.path.join(os.path.dirname(HERE), "libflintb200.so")
-SOURCES = ["fb_api.cu"]
+SOURCES = ["fb_api.cu", "fb_spec.cu"]
 HEADERS = sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))) + [os.path.join(ROOT, "include", "flint_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 
 def _stale() -> bool:
@@ -24,11 +24,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    extra = os.environ.get("FLINT_B200_NVCC_FLAGS", "").split()
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    # one object per translation unit, compiled side by side, then one link
+    procs, objs = [], []
+    for src in SOURCES:
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + f".{os.getpid()}.o")
+        objs.append(obj)
+        cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, os.path.join(HERE, src)]
+        procs.append((cmd, subprocess.Popen(cmd)))
+    for cmd, p in procs:
+        if p.wait() != 0:
+            raise subprocess.CalledProcessError(p.returncode, cmd)
     tmp = LIB + f".tmp{os.getpid()}"
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-          ["-o", tmp] + [os.path.join(HERE, s) for s in SOURCES] + ["-lcudart"]
-    subprocess.check_call(cmd)
+    subprocess.check_call([nvcc, "-shared", "-Xcompiler", "-fPIC", "-o", tmp] + objs + ["-lcudart"])
     os.replace(tmp, LIB)
+    for o in objs:
+        os.remove(o)
     return LIB
 
 

@@ -7,37 +7,12 @@
 #include <new>
 
 #include "../../include/flint_b200.h"
+#include "fb_ctx.hpp"
 #include "fb_decode.cuh"
 #include "fb_verify.cuh"
 
 using namespace fb;
 
-struct fb_ctx {
-  fb_model_desc d;
-  int device, sm_count, kernel_id, rgqa;
-  uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
-  const void *n1, *n2, *nf, *embed;
-  float* invf;
-  DevStatus* status;
-  void *kc, *vc;
-  int max_seq, maxchunks;
-  unsigned spin_limit;
-  bool weights_bound;
-  int last_cuda_error;
-  int force_chunks;
-  long long* prof;
-  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll, *part_ll;   // tagged vectors of the data-flow kernel
-  unsigned* cnt;
-  uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
-  unsigned tag_base;
-  int tp_size, tp_rank, vocab_base, ko;                             // tensor parallelism (1 GPU: tp_size 1, ko = dim)
-  uint64_t* inbox;                                                  // [2][tp][dim] partial words + [tp][2] candidates
-  uint64_t* peer_inbox[8];
-  bool peers_open[8];
-  uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
-  float* vpart;                                                     // verify attention: per-span partials
-  int max_fly, poll_words;
-};
 
 namespace {
 
@@ -53,22 +28,33 @@ struct KernelEntry {
 
 const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(512, 512, 1408, 64, 4),       // tiny test decoder
+    FB_DECODE_ENTRY(512, 512, 1536, 64, 4),       // tiny decoder whose FFN splits into whole groups over 2 ranks
+    FB_DECODE_ENTRY(512, 256, 768, 64, 4),        // ... and its 2-rank slice
     FB_DECODE_ENTRY(2560, 2560, 8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
     FB_DECODE_ENTRY(2560, 2560, 8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
     FB_DECODE_ENTRY(4096, 4096, 14336, 128, 4),   // 8B-class
     FB_DECODE_ENTRY(2560, 1280, 4096, 80, 4),     // 3B-class over 2 GPUs
     FB_DECODE_ENTRY(2560, 640, 2048, 80, 4),      // 3B-class over 4 GPUs
+    FB_DECODE_ENTRY(2560, 384, 1024, 80, 4),      // 3B-class over 8 GPUs (320 attention columns inside 3 whole groups)
     FB_DECODE_ENTRY(4096, 2048, 7168, 128, 4),    // 8B-class over 2 GPUs
     FB_DECODE_ENTRY(4096, 1024, 3584, 128, 4),    // 8B-class over 4 GPUs
     FB_DECODE_ENTRY(4096, 512, 1792, 128, 4),     // 8B-class over 8 GPUs
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
 
-int find_kernel(const fb_model_desc& d) {
+// columns of the O projection a rank reads: its heads' columns widened to whole int4 groups (a rank of the 3B-class
+// model split 8 ways owns 320 columns = 2.5 groups: it reads 384 and feeds zeros for its neighbour's 64)
+void o_window(int width, int rank, int* ko, int* off) {
+  const int start = rank * width, lo = start / 128 * 128, hi = (start + width + 127) / 128 * 128;
+  *ko = hi - lo;
+  *off = start - lo;
+}
+
+int find_kernel(const fb_model_desc& d, int ko) {
   if (d.n_kv_head <= 0 || d.n_head % d.n_kv_head) return -1;
   for (int i = 0; i < kNumDecodeKernels; i++) {
     const KernelEntry& e = kDecodeKernels[i];
-    if (e.dim == d.dim && e.ko == d.n_head * d.head_dim && e.ffn == d.ffn && e.head_dim == d.head_dim &&
+    if (e.dim == d.dim && e.ko == ko && e.ffn == d.ffn && e.head_dim == d.head_dim &&
         e.rgqa == d.n_head / d.n_kv_head && e.hz == (d.has_zeros ? 1 : 0))
       return i;
   }
@@ -107,7 +93,7 @@ int chunks_for(const fb_ctx* c, int T) {
 }
 
 // every K the stand-alone entry points (re-layout, dequantise, GEMV) are built for
-#define FB_FOR_EACH_K(X) X(512) X(640) X(1024) X(1280) X(1408) X(1792) X(2048) X(2560) X(3584) X(4096) X(7168) X(8192) X(14336)
+#define FB_FOR_EACH_K(X) X(256) X(384) X(512) X(640) X(768) X(1024) X(1280) X(1408) X(1536) X(1792) X(2048) X(2560) X(3584) X(4096) X(7168) X(8192) X(14336)
 
 template <int K>
 int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
@@ -169,12 +155,14 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
 
 template <int MT, int K, int EPI, int HD, int ROWS>
 cudaError_t launch_vgemm_r(const VGemmParams& p, int sms, cudaStream_t st) {
-  static bool configured = false;
+  static bool configured[64] = {};        // the attribute belongs to a device's copy of the function: once per device
   using V = VG<MT, K, ROWS>;
-  if (!configured) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(v_gemm<MT, K, EPI, HD, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, V::smem());
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   const int per_sm = (227 * 1024) / (V::smem() + 1024) >= 2 ? 2 : 1;      // persistent CTAs: as many as are resident
   const int nrb = (p.rows + V::ROWS - 1) / V::ROWS;
@@ -271,7 +259,11 @@ int fb_query(int device, fb_caps* out) {
   out->cooperative_launch = p.cooperativeLaunch;
   out->total_mem_bytes = (int64_t)p.totalGlobalMem;
   cudaFuncAttributes fa;
-  if (cudaFuncGetAttributes(&fa, kDecodeKernels[2].fn2) == cudaSuccess) out->regs_decode_kernel = fa.numRegs;
+  for (int i = 0; i < kNumDecodeKernels; i++)      /* registers of the 3B-class instantiation, the one the benchmark runs */
+    if (kDecodeKernels[i].dim == 2560 && kDecodeKernels[i].head_dim == 80 && kDecodeKernels[i].ko == 2560 && !kDecodeKernels[i].hz) {
+      if (cudaFuncGetAttributes(&fa, kDecodeKernels[i].fn2) == cudaSuccess) out->regs_decode_kernel = fa.numRegs;
+      break;
+    }
   return FB_OK;
 }
 
@@ -285,9 +277,12 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   *out = nullptr;
   const fb_model_desc& d = *desc;
   if (tp_size < 1 || tp_size > 8 || tp_rank < 0 || tp_rank >= tp_size) return FB_ERR_ARG;
-  if (d.n_layer <= 0 || d.vocab <= 0 || d.dim % 128 || d.ffn % 128 || (d.n_head * d.head_dim) % 128) return FB_ERR_SHAPE;
+  if (d.n_layer <= 0 || d.vocab <= 0 || d.dim % 128 || d.ffn % 128 || d.n_head <= 0 || d.head_dim <= 0) return FB_ERR_SHAPE;
   if (tp_size == 1 && d.n_head * d.head_dim != d.dim) return FB_ERR_SHAPE;
-  const int kid = find_kernel(d);
+  int ko = 0, ao_off = 0;
+  o_window(d.n_head * d.head_dim, tp_rank, &ko, &ao_off);
+  if (tp_size == 1 && ao_off) return FB_ERR_SHAPE;
+  const int kid = find_kernel(d, ko);
   if (kid < 0) return FB_ERR_SHAPE;
   DeviceGuard g(device);
   if (!g.ok) return FB_ERR_CUDA;
@@ -304,7 +299,7 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   c->rgqa = d.n_head / d.n_kv_head;
   c->spin_limit = 4000000u;
   c->max_fly = 4;
-  c->tp_size = tp_size; c->tp_rank = tp_rank; c->vocab_base = vocab_base; c->ko = d.n_head * d.head_dim;
+  c->tp_size = tp_size; c->tp_rank = tp_rank; c->vocab_base = vocab_base; c->ko = ko; c->ao_off = ao_off;
   c->tag_base = 8;
   c->maxchunks = c->sm_count / d.n_kv_head;
   if (c->maxchunks < 1) c->maxchunks = 1;
@@ -329,15 +324,13 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   }
   const size_t hp = d.head_dim / 2;
   const size_t wpc = (size_t)c->rgqa * d.head_dim + 2 * c->rgqa;
-  const size_t ll_words[8] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)QD / 2,
+  const size_t ll_words[8] = {(size_t)d.dim / 2, d.n_head * hp, d.n_kv_head * hp, d.n_kv_head * hp, (size_t)ko / 2,
                               (size_t)d.ffn / 2, 2 * (size_t)c->sm_count, (size_t)d.n_kv_head * c->maxchunks * wpc};
   uint64_t** ll_ptrs[8] = {&c->h_ll, &c->q_ll, &c->k_ll, &c->v_ll, &c->ao_ll, &c->act_ll, &c->cand_ll, &c->part_ll};
   for (int i = 0; i < 8; i++) {
     A(dmalloc(ll_ptrs[i], 8 * ll_words[i] + 16));
     if (e == cudaSuccess) A(cudaMemset(*ll_ptrs[i], 0, 8 * ll_words[i] + 16));
   }
-  A(dmalloc(&c->cnt, 256));
-  if (e == cudaSuccess) A(cudaMemset(c->cnt, 0, 256));
   {
     const size_t rowsz[5] = {(size_t)d.dim, (size_t)d.dim, (size_t)QD, (size_t)QD, (size_t)d.ffn};
     uint16_t** vp[5] = {&c->vh, &c->vxn, &c->vq, &c->vao, &c->vact};
@@ -351,7 +344,7 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
   {  // rows of the residual stream one CTA owns (whole tiles of the O and the down matrix)
-    const int uo = tile_rt(QD) > tile_rt(d.ffn) ? tile_rt(QD) : tile_rt(d.ffn);
+    const int uo = tile_rt(ko) > tile_rt(d.ffn) ? tile_rt(ko) : tile_rt(d.ffn);
     const int units = (d.dim + uo - 1) / uo;
     if (((units + c->sm_count - 1) / c->sm_count + 1) * uo > kMaxOwnRows || (2 * d.ffn) % 4) e = cudaErrorInvalidValue;
   }
@@ -376,7 +369,7 @@ int fb_ctx_destroy(fb_ctx* c) {
   for (int p = 0; p < 8; p++)
     if (c->peers_open[p] && c->peer_inbox[p]) cudaIpcCloseMemHandle(c->peer_inbox[p]);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf,
-                  c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->cnt, c->flags,
+                  c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->flags,
                   c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -414,7 +407,6 @@ int fb_last_status(fb_ctx* c, fb_status* out) {
   out->seen = s.seen;
   if (s.code != 0) {   // a launch gave up: clear the report so that the next launch starts clean
     cudaMemset(c->status, 0, sizeof(DevStatus));
-    cudaMemset(c->cnt, 0, 256);
   }
   return FB_OK;
 }
@@ -523,7 +515,7 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   struct M { uint8_t** dst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
   M ms[] = {
       {&c->w_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
-      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, QD, 0, 0, 0},
+      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, c->ko, 0, 0, 0},
       {&c->w_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
       {&c->w_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
       {&c->w_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
@@ -575,7 +567,7 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   Q.tag_base = c->tag_base; Q.spin_limit = c->spin_limit;
   Q.eps = d.rms_eps; Q.attn_scale = d.attn_scale; Q.resid = d.resid_mult; Q.emb_mult = d.emb_mult;
   Q.logits_scaling = d.logits_scaling; Q.prof = c->prof; Q.max_fly = (unsigned)c->max_fly; Q.poll_words = c->poll_words;
-  Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox;
+  Q.tp_size = c->tp_size; Q.tp_rank = c->tp_rank; Q.vocab_base = c->vocab_base; Q.inbox = c->inbox; Q.ao_off = c->ao_off;
   for (int p = 0; p < c->tp_size; p++) {
     if (!c->peer_inbox[p]) return FB_ERR_STATE;       /* fb_tp_connect has not been called */
     Q.peer_inbox[p] = c->peer_inbox[p];
@@ -656,6 +648,27 @@ int fb_tp_connect(fb_ctx* c, const void* handles, int32_t n) {
     FB_CUDA(c, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
     c->peer_inbox[p] = (uint64_t*)ptr;
     c->peers_open[p] = true;
+  }
+  return FB_OK;
+}
+
+int fb_tp_connect_local(fb_ctx* c, fb_ctx* const* ranks, int32_t n) {
+  if (!c || !ranks || n != c->tp_size) return FB_ERR_ARG;
+  DeviceGuard g(c->device);
+  for (int p = 0; p < n; p++) {
+    if (p == c->tp_rank) continue;
+    fb_ctx* o = ranks[p];
+    if (!o || o == c || o->tp_size != n || o->tp_rank != p || o->d.dim != c->d.dim) return FB_ERR_ARG;
+    if (o->device != c->device) {
+      int can = 0;
+      FB_CUDA(c, cudaDeviceCanAccessPeer(&can, c->device, o->device));
+      if (!can) return FB_ERR_STATE;
+      cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+      else if (e != cudaSuccess) return cuda_fail(c, e);
+    }
+    c->peer_inbox[p] = o->inbox;
+    c->peers_open[p] = false;                          /* not an IPC mapping: the owner frees it */
   }
   return FB_OK;
 }

@@ -1,0 +1,34 @@
+// The context object behind the C ABI's opaque `fb_ctx`, shared by the translation units of the library.
+#pragma once
+#include <stdint.h>
+
+#include "../../include/flint_b200.h"
+
+namespace fb { struct DevStatus; }
+using fb::DevStatus;
+
+struct fb_ctx {
+  fb_model_desc d;
+  int device, sm_count, kernel_id, rgqa;
+  uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
+  const void *n1, *n2, *nf, *embed;
+  float* invf;
+  DevStatus* status;
+  void *kc, *vc;
+  int max_seq, maxchunks;
+  unsigned spin_limit;
+  bool weights_bound;
+  int last_cuda_error;
+  int force_chunks;
+  long long* prof;
+  uint64_t *h_ll, *q_ll, *k_ll, *v_ll, *ao_ll, *act_ll, *cand_ll, *part_ll;   // tagged vectors of the data-flow kernel
+  uint32_t* flags;                                                  // [3][256] arrival flags: h, act, ao
+  unsigned tag_base;
+  int tp_size, tp_rank, vocab_base, ko, ao_off;                     // tensor parallelism (1 GPU: tp_size 1, ko = dim)
+  uint64_t* inbox;                                                  // [2][tp][dim] partial words + [tp][2] candidates
+  uint64_t* peer_inbox[8];
+  bool peers_open[8];
+  uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
+  float* vpart;                                                     // verify attention: per-span partials
+  int max_fly, poll_words;
+};

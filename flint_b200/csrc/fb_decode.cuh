@@ -47,6 +47,13 @@ __device__ __forceinline__ uint64_t ll_load_sys(const uint64_t* p) {
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
   return a;
 }
+__device__ __forceinline__ void ll_store2_sys(uint64_t* p, uint32_t pay0, uint32_t pay1, uint32_t tag) {
+  const uint64_t a = ((uint64_t)tag << 32) | pay0, b = ((uint64_t)tag << 32) | pay1;
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ll_load2_sys(const uint64_t* p, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
 // bounded poll of one word written by another GPU; returns the payload (0 after a failure)
 __device__ __forceinline__ uint32_t ll_poll_sys(const uint64_t* p, uint32_t tag, const WaitCtl& wc, int layer) {
   for (unsigned spin = 0;; spin++) {
@@ -520,6 +527,7 @@ struct Decode2Params {
   // tensor parallelism: this GPU holds a slice of every matrix (heads, FFN columns, vocabulary rows); the partial sums
   // of the K-sharded O and down projections are exchanged by peer stores into every rank's inbox
   int32_t tp_size, tp_rank, vocab_base;
+  int32_t ao_off;             // columns between the start of this rank's O window and its own attention output (0 or 64)
   uint64_t* inbox;            // local: [2 parities][tp_size][dim] tagged fp32 partials, then [tp_size][2] arg-max candidates
   uint64_t* peer_inbox[8];    // the same buffer of every rank (peer-mapped); own entry = inbox
 };
@@ -591,10 +599,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     auto resid_epi = [&](int row0, float c, int nvalid, uint32_t tag, int par) {
       const int r = row0 + (lane >> 3);
       if (N > 1) {
-        if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
-          ypart[r] = c;
-          for (int p = 0; p < N; p++)
-            if (p != me) ll_store_sys(P.peer_inbox[p] + ((size_t)(par * N + me)) * D + o0 + r, __float_as_uint(c), tag);
+        // lanes 0/8/16/24 hold the partial sums of rows row0..row0+3; lane j < N-1 pushes all four to one peer as two
+        // 16-byte stores, so the N-1 transfers of a tile leave the SM side by side instead of one after the other
+        const float c0 = __shfl_sync(0xffffffffu, c, 0), c1 = __shfl_sync(0xffffffffu, c, 8),
+                    c2 = __shfl_sync(0xffffffffu, c, 16), c3 = __shfl_sync(0xffffffffu, c, 24);
+        if ((lane & 7) == 0 && (lane >> 3) < nvalid) ypart[r] = c;
+        if (lane < N - 1) {
+          const int p = lane >= me ? lane + 1 : lane;
+          uint64_t* dst = P.peer_inbox[p] + ((size_t)(par * N + me)) * D + o0 + row0;     // 32-byte aligned: row0 % 4 == 0
+          if (nvalid == 4) {
+            ll_store2_sys(dst, __float_as_uint(c0), __float_as_uint(c1), tag);
+            ll_store2_sys(dst + 2, __float_as_uint(c2), __float_as_uint(c3), tag);
+          } else {
+            const float cc[4] = {c0, c1, c2, c3};
+            for (int i = 0; i < nvalid; i++) ll_store_sys(dst + i, __float_as_uint(cc[i]), tag);
+          }
         }
         return;
       }
@@ -607,19 +626,33 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       if ((lane & 15) == 0 && (lane >> 3) < nvalid)
         ll_store(P.h_ll + ((o0 + r) >> 1), (uint32_t)f2bf(hn) | ((uint32_t)f2bf(hn1) << 16), tag);
     };
-    // tensor parallel only: sum the partials of all ranks in rank order (identical on every rank), update h, publish
+    // tensor parallel only: collect the peers' partials of this CTA's rows (one 16-byte load per thread and poll round,
+    // all peers and row pairs in flight together), sum in rank order (identical on every rank), update h, publish
+    float* yin = sm.yin;                                      // [N-1][kMaxOwnRows]
     auto resid_finish = [&](uint32_t tag, int par, int layer) {
-      named_bar_sync(kBarConsumers, kConsumerThreads);
-      for (int pr = tid_c; pr < (o1 - o0) / 2; pr += kConsumerThreads) {
+      const int npair = (o1 - o0) / 2, nitem = npair * (N - 1);
+      for (int it = tid_c; it < nitem; it += kConsumerThreads) {
+        const int j = it / npair, pr = it % npair, s2 = j >= me ? j + 1 : j;
+        const uint64_t* src = P.inbox + ((size_t)(par * N + s2)) * D + o0 + 2 * pr;
+        for (unsigned spin = 0;; spin++) {
+          uint64_t u, v;
+          ll_load2_sys(src, u, v);
+          if ((uint32_t)(u >> 32) == tag && (uint32_t)(v >> 32) == tag) {
+            yin[j * kMaxOwnRows + 2 * pr] = __uint_as_float((uint32_t)u);
+            yin[j * kMaxOwnRows + 2 * pr + 1] = __uint_as_float((uint32_t)v);
+            break;
+          }
+          if (*wc.s_abort) break;
+          if ((spin & 255) == 255 && ld_volatile_s32(&wc.st->abort)) { *wc.s_abort = 1; break; }
+          if (spin >= wc.limit) { report_fail(wc, W_FLAG, layer, (int)tag, -3); break; }
+        }
+      }
+      named_bar_sync(kBarConsumers, kConsumerThreads);        // every row's own partial and every peer's are in shared memory
+      for (int pr = tid_c; pr < npair; pr += kConsumerThreads) {
         float tot0 = 0.f, tot1 = 0.f;
         for (int s2 = 0; s2 < N; s2++) {
-          if (s2 == me) {
-            tot0 += ypart[2 * pr]; tot1 += ypart[2 * pr + 1];
-          } else {
-            const uint64_t* src = P.inbox + ((size_t)(par * N + s2)) * D + o0 + 2 * pr;
-            tot0 += __uint_as_float(ll_poll_sys(src, tag, wc, layer));
-            tot1 += __uint_as_float(ll_poll_sys(src + 1, tag, wc, layer));
-          }
+          const float* src = s2 == me ? ypart : yin + (s2 > me ? s2 - 1 : s2) * kMaxOwnRows;
+          tot0 += src[2 * pr]; tot1 += src[2 * pr + 1];
         }
         const float h0 = rbf(hown[2 * pr] + tot0 * P.resid), h1 = rbf(hown[2 * pr + 1] + tot1 * P.resid);
         hown[2 * pr] = h0; hown[2 * pr + 1] = h1;
@@ -700,7 +733,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
       FB_STAMP(2);
       // ================= attention =================
       {
-        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll, kcl, vcl, P.part_ll, P.ao_flags, P.n_kv, P.pos, P.nchunks,
+        if (b == 0 && KOUT != 0) {
+          // columns of the O window that belong to a neighbouring rank (tensor parallel, 8-way split of the 3B-class
+          // shape): the O projection must see zeros there, tagged like the real attention output
+          const int used = P.n_head * HP, off = P.ao_off >> 1;
+          for (int i = tid_c; i < KOUT / 2 - used; i += kConsumerThreads)
+            ll_store(P.ao_ll + (i < off ? i : used + i), 0u, tg_att);
+        }
+        Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll + (P.ao_off >> 1), kcl, vcl, P.part_ll, P.ao_flags, P.n_kv, P.pos, P.nchunks,
                      P.maxchunks, P.attn_scale, tg_qkv, mk_tag(P.tag_base, l, PH_PART), tg_att};
         named_bar_sync(kBarConsumers, kConsumerThreads);        // scratch (the activations) is free: every warp left the GEMV
         attn2_phase<HD, R>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l);

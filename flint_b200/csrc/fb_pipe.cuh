@@ -34,6 +34,7 @@ struct Smem {
   int* tdone;          // [kStages] units finished per stage in flight
   int* bcnt;           // [kStages][2] slices finished per tile
   float4* xf;          // [kMaxGroups] per-group activation factors
+  float* yin;          // [7][kMaxOwnRows] tensor parallel: the peers' partial sums of this CTA's rows
 };
 
 __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
@@ -52,10 +53,11 @@ __device__ __forceinline__ Smem carve_smem(uint8_t* base) {
   s.qpart = reinterpret_cast<float*>(tail + 1024);
   s.tdone = reinterpret_cast<int*>(tail + 2048);
   s.bcnt = reinterpret_cast<int*>(tail + 2080);
+  s.yin = reinterpret_cast<float*>(tail + 2176);
   s.xf = reinterpret_cast<float4*>(tail + 4096);
   return s;
 }
-static_assert(kMaxGroups * 16 + 4096 <= kTailBytes && 2 * kMaxOwnRows * 4 <= 512, "tail layout");
+static_assert(kMaxGroups * 16 + 4096 <= kTailBytes && 2 * kMaxOwnRows * 4 <= 512 && 2176 + 7 * kMaxOwnRows * 4 <= 4096, "tail layout");
 
 // called by one thread before the CTA-wide barrier that opens the kernel
 __device__ __forceinline__ void pipe_init(const Smem& sm) {

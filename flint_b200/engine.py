@@ -192,6 +192,42 @@ class DecodeEngine:
         self._keepalive = (hc, depth, amask)
         return logits, feat
 
+    # ------------------------------------------------------------------ token choice and acceptance on the device
+    def sample(self, logits: torch.Tensor, temperature: float = 0.0, top_k: Optional[int] = None, seed: int = 0,
+               counter: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One token per row of `logits` (f32 [vocab] or [rows, vocab]) without a host sync: arg-max when temperature <= 0,
+        else a draw from softmax(logits / temperature) over the top_k entries (reference: engine/generate.py:37-55)."""
+        lg = logits if logits.dim() == 2 else logits.view(1, -1)
+        if lg.dtype != torch.float32 or lg.stride(-1) != 1:
+            raise ValueError("logits must be f32 with contiguous rows")
+        rows, vocab = lg.shape
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=lg.device)
+        _lib.check(self.lib.fb_sample(_ptr(lg), vocab, rows, lg.stride(0) if rows > 1 else 0, float(temperature),
+                                      int(top_k or 0), int(seed), int(counter), _ptr(out), _stream_ptr(self.device)), "fb_sample")
+        return out
+
+    def accept_chain(self, target: torch.Tensor, draft: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Device int32 [2]: accepted count and the target's next token (reference: spec_mega.py:106-113)."""
+        out = out if out is not None else torch.empty(2, dtype=torch.int32, device=self.device)
+        _lib.check(self.lib.fb_accept_chain(_ptr(target), _ptr(draft), int(draft.numel()), _ptr(out),
+                                            _stream_ptr(self.device)), "fb_accept_chain")
+        return out
+
+    def accept_tree(self, cand: torch.Tensor, parent: torch.Tensor, target: torch.Tensor,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Device int32 [2 + M]: path length (root included), the target's token at its end, the path's node indices
+        (reference: spec_tree.py:108-118)."""
+        M = int(cand.numel())
+        out = out if out is not None else torch.zeros(2 + M, dtype=torch.int32, device=self.device)
+        _lib.check(self.lib.fb_accept_tree(_ptr(cand), _ptr(parent), _ptr(target), M, _ptr(out), _stream_ptr(self.device)),
+                   "fb_accept_tree")
+        return out
+
+    def kv_compact(self, accept: torch.Tensor, pos: int):
+        """Moves the accepted path's cache rows to slots pos+1.. on the device, from accept_tree's output."""
+        _lib.check(self.lib.fb_kv_compact(self._ctx, _ptr(accept), int(pos), _stream_ptr(self.device)), "fb_kv_compact")
+
     def kv_move(self, src, dst):
         """cache[:, dst[i]] = cache[:, src[i]] in order, K and V, every layer (reference: spec_tree.py:126-128)."""
         n = len(src)

@@ -1,7 +1,9 @@
 """Tensor parallelism of the decode path over 2/4/8 GPUs of one box: host side.
 
 Megatron-style sharding of every int4 matrix: QKV by heads (rows), O by this rank's heads (columns = K), gate/up by
-FFN rows, down by FFN columns (K), LM head by vocabulary rows; norms and the embedding table are replicated. The two
+FFN rows, down by FFN columns (K), LM head by vocabulary rows; norms and the embedding table are replicated. Where a
+rank's attention width is not a multiple of the int4 group (the 3B-class model over 8 ranks: 320 columns), its O slice
+is widened to the enclosing group boundaries and the kernel feeds zeros for the neighbour's columns (`o_window`). The two
 K-sharded projections leave partial sums that the kernel exchanges itself (peer stores into every rank's inbox,
 tagged words, summed in rank order so every rank holds bit-identical residuals); this module only slices the packed
 tensors, creates one engine per process and passes the IPC handles of the inboxes around once, through
@@ -21,13 +23,46 @@ def _rows(t: torch.Tensor, a: int, b: int) -> torch.Tensor:
     return t[..., a:b, :]
 
 
+def o_window(cfg: ModelArgs, rank: int, size: int):
+    """Columns of the O projection rank `rank` reads: its heads' columns widened to whole int4 groups.
+
+    Returns (lo, hi, off): the rank holds columns [lo, hi) of every O row and its own attention output starts `off`
+    columns into that window; the kernel feeds zeros for the columns of the window that belong to a neighbour, so no
+    weight is re-quantised and every rank's dequantised values stay bit-exact. For shapes whose per-rank width is a
+    multiple of 128 the window is exactly the rank's columns (off = 0)."""
+    w = (cfg.n_head // size) * cfg.head_dim
+    start = rank * w
+    lo = start // GROUP * GROUP
+    hi = (start + w + GROUP - 1) // GROUP * GROUP
+    return lo, hi, start - lo
+
+
+def can_shard(cfg: ModelArgs, size: int) -> bool:
+    nh, nkv, f, v = cfg.n_head, cfg.n_local_heads, cfg.ffn_padded, cfg.vocab_size
+    if size == 1:
+        return True
+    if nh % size or nkv % size or (f // GROUP) % size or v % size:
+        return False
+    widths = {o_window(cfg, r, size)[1] - o_window(cfg, r, size)[0] for r in range(size)}
+    return len(widths) == 1                                    # one kernel shape for every rank
+
+
+def max_tp(cfg: ModelArgs, world: int) -> int:
+    """Largest tensor-parallel degree <= world (a power-of-two divisor of it) this model splits into."""
+    tp = world
+    while tp > 1 and (world % tp or not can_shard(cfg, tp)):
+        tp //= 2
+    return max(tp, 1)
+
+
 def shard_packed(P: Dict[str, torch.Tensor], cfg: ModelArgs, rank: int, size: int) -> Dict[str, torch.Tensor]:
     """This rank's slice of a packed model (the dict `pack_model` / `synth_packed` return)."""
     hd, nh, nkv, f, v = cfg.head_dim, cfg.n_head, cfg.n_local_heads, cfg.ffn_padded, cfg.vocab_size
-    if nh % size or nkv % size or (f // GROUP) % size or v % size or ((nh // size) * hd) % GROUP:
+    if not can_shard(cfg, size):
         raise ValueError(f"model does not shard over {size} ranks with whole int4 groups")
     nhl, nkvl, fl, vl = nh // size, nkv // size, f // size, v // size
     qd, kvd = nh * hd, nkv * hd
+    lo, hi, _ = o_window(cfg, rank, size)
     out: Dict[str, torch.Tensor] = {}
     for suf in ("q", "s", "z"):
         if f"qkv_{suf}" not in P:
@@ -37,8 +72,7 @@ def shard_packed(P: Dict[str, torch.Tensor], cfg: ModelArgs, rank: int, size: in
         out[f"qkv_{suf}"] = torch.cat([_rows(t, rank * nhl * hd, (rank + 1) * nhl * hd),
                                        _rows(t, qd + rank * nkvl * hd, qd + (rank + 1) * nkvl * hd),
                                        _rows(t, qd + kvd + rank * nkvl * hd, qd + kvd + (rank + 1) * nkvl * hd)], -2).contiguous()
-        ko = nhl * hd
-        out[f"o_{suf}"] = P[f"o_{suf}"][..., rank * ko // per:(rank + 1) * ko // per].contiguous()
+        out[f"o_{suf}"] = P[f"o_{suf}"][..., lo // per:hi // per].contiguous()
         t = P[f"gu_{suf}"]
         out[f"gu_{suf}"] = torch.cat([_rows(t, rank * fl, (rank + 1) * fl), _rows(t, f + rank * fl, f + (rank + 1) * fl)],
                                      -2).contiguous()

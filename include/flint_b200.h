@@ -82,11 +82,15 @@ int fb_ctx_destroy(fb_ctx* ctx);
  * them before the first fb_decode. The partial sums of the K-sharded O and down projections and the arg-max
  * candidates then travel by peer stores over NVLink inside the kernel; no NCCL launch is involved.
  *   fb_tp_export : 64-byte cudaIpcMemHandle_t of this rank's inbox
- *   fb_tp_connect: handles = n * 64 bytes, entry p = rank p's handle (the own entry is ignored) */
+ *   fb_tp_connect: handles = n * 64 bytes, entry p = rank p's handle (the own entry is ignored)
+ *   fb_tp_connect_local: the single-process form (one host process that drives several GPUs, or several ranks of a
+ *                  test on one GPU): ranks[p] = rank p's context of THIS process; peer access is enabled between the
+ *                  devices, no IPC handle is involved. Every rank's context must outlive the others' launches. */
 int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int32_t tp_size, int32_t vocab_base,
                      fb_ctx** out);
 int fb_tp_export(fb_ctx* ctx, void* handle_out64);
 int fb_tp_connect(fb_ctx* ctx, const void* handles, int32_t n);
+int fb_tp_connect_local(fb_ctx* ctx, fb_ctx* const* ranks, int32_t n);
 int fb_last_status(fb_ctx* ctx, fb_status* out);
 
 /* Re-lays the caller's int4 tensors out into the context's streaming layout (one pass on the GPU, once).
@@ -124,11 +128,68 @@ int fb_verify(fb_ctx* ctx, const int32_t* d_tokens, const void* d_h, const int32
  * src/dst are HOST arrays. Replaces `kc[:, dst] = kc[:, src]` (reference: spec_tree.py:126-128). */
 int fb_kv_move(fb_ctx* ctx, const int32_t* src, const int32_t* dst, int32_t n, void* stream);
 
+/* On-device KV compaction after a tree acceptance: the device-side form of fb_kv_move. d_accept is fb_accept_tree's
+ * output (device int32: [0] = nodes on the accepted path, [2 + i] = node index of path step i); cache row pos + i
+ * receives row pos + path[i] for i = 1 .. len-1, K and V, every layer. No host copy of the path is needed. */
+int fb_kv_compact(fb_ctx* ctx, const int32_t* d_accept, int32_t pos, void* stream);
+
+/* Token choice on the device, no host sync (replaces the host-side pick() / sample(), reference: chat.py:76-81,
+ * engine/generate.py:37-55). One token per row of d_logits (f32, `vocab` entries, rows `row_stride` elements apart; a
+ * stride of 0 draws every row from the same vector).
+ *   temperature <= 0 : arg-max, first index of the maximum
+ *   temperature  > 0 : a sample of softmax(logits / temperature) restricted, when 0 < top_k < vocab, to the entries
+ *                      >= the top_k-th largest (ties kept, as the reference's masking does)
+ *   seed, counter    : row r uses the random stream (seed, counter + r): equal arguments give equal tokens; advance
+ *                      `counter` by `rows` per call */
+int fb_sample(const float* d_logits, int32_t vocab, int32_t rows, int64_t row_stride, float temperature, int32_t top_k,
+              uint64_t seed, uint64_t counter, int32_t* d_out, void* stream);
+
+/* Acceptance walks on the device (replace the host loops, reference: spec_mega.py:106-113, spec_tree.py:108-118).
+ *   fb_accept_chain: d_target int32[k+1] = the target's greedy token at every candidate position, d_draft int32[k];
+ *                    d_out[0] = accepted count a (longest agreeing prefix), d_out[1] = d_target[a]
+ *   fb_accept_tree : d_cand / d_parent / d_target int32[m] (node 0 = root, parent[0] = -1, parents before children);
+ *                    d_out int32[2 + m]: [0] = nodes on the accepted path incl. the root, [1] = the target's token at
+ *                    its last node, [2 + i] = node index of path step i */
+int fb_accept_chain(const int32_t* d_target, const int32_t* d_draft, int32_t k, int32_t* d_out, void* stream);
+int fb_accept_tree(const int32_t* d_cand, const int32_t* d_parent, const int32_t* d_target, int32_t m, int32_t* d_out,
+                   void* stream);
+
+/* EAGLE draft head inside the library: one decoder block over [target feature ; token embedding] with bf16 weights in
+ * torch.nn.Linear layout, the computation of the reference's DraftHead.forward (reference: train/draft_model.py:24-64)
+ * and of its token head (reference: spec_mega.py:43-44), rounding to bf16 where bf16 PyTorch modules round.
+ * fuse * dim is the width of the (fused) feature; n_kv_head == n_head is the reference's multi-head form.
+ *   fb_draft_forward: T rows. d_feat bf16 [T, fuse*dim]; the token embedding of row t is d_emb[t] (bf16 [T, dim]) or,
+ *                     when d_emb is NULL, row d_tokens[t] of the bound embedding table (a negative id = zeros), read on
+ *                     the device; d_positions int32[T] rotation positions; d_slots int32[T] = cache slot of every row
+ *                     (its k/v are written there and row t attends slots 0..d_slots[t]) or NULL (slot t: plain causal
+ *                     attention over the T rows); d_out bf16 [T, fuse*dim] = predicted next features
+ *   fb_draft_head   : n <= 16 feature rows -> the top_b <= 16 tokens of each (d_tokens int32 [n, top_b], best first) and
+ *                     optionally their logits (d_scores f32 [n, top_b]); logits are rounded to bf16 as the reference's
+ *                     bf16 head computes them */
+typedef struct fb_draft_desc {
+  int32_t dim, n_head, n_kv_head, inter, fuse, vocab;
+  int32_t max_roll;        /* cache slots (window + rollout depth) */
+  int32_t max_tokens;      /* most rows one fb_draft_forward call takes */
+  float rope_base, rms_eps, logits_scaling;
+} fb_draft_desc;
+typedef struct fb_draft_weights {
+  const void *merge, *n1, *n2, *q, *k, *v, *o, *gate, *up, *down, *fout;   /* the draft head's own tensors */
+  const void *nf, *embed;                                                  /* the target's final norm and embedding table */
+} fb_draft_weights;
+typedef struct fb_draft fb_draft;
+int fb_draft_create(const fb_draft_desc* desc, int device, fb_draft** out);
+int fb_draft_destroy(fb_draft* draft);
+int fb_draft_bind(fb_draft* draft, const fb_draft_weights* w);
+int fb_draft_forward(fb_draft* draft, const void* d_feat, const void* d_emb, const int32_t* d_tokens,
+                     const int32_t* d_positions, const int32_t* d_slots, int32_t T, void* d_out, void* stream);
+int fb_draft_head(fb_draft* draft, const void* d_feat_rows, int32_t n, int32_t top_b, int32_t* d_tokens, float* d_scores,
+                  void* stream);
+
 /* Stand-alone slices of the same path, on the streaming layout (unit-test granularity; they replace the
  * reference's GEMV family, reference: kernels/int4_gemv.cu:384-424).
  *   fb_stream_bytes : bytes of the streaming layout for one [rows, k] matrix
  *   fb_repack       : caller layout -> streaming layout (order: 0 plain, 1 RoPE pair interleave with head_dim,
- *                     2 gate/up interleave)
+ *                     2 gate/up interleave: stream rows (2i, 2i+1) hold source rows (i, i+order_arg))
  *   fb_dequant      : streaming layout -> f32 [rows, k] in ORIGINAL row order: (nib-8)*s+z, bit for bit
  *   fb_gemv         : y f32 [rows] (original row order) = W x, x bf16 [k]; d_status is a zeroed 32-byte device
  *                     buffer (int32[8]) whose first word becomes FB_ERR_TIMEOUT if a bounded wait ran out */

@@ -3,6 +3,9 @@ checkout, into oracle/_ref/ (git-ignored). Nothing is copied into this repositor
 
     python -m oracle.build_ref [/path/to/reference]
 
+Without an argument the checkout is taken from $FLINT_REFERENCE, else from a folder named `reference` beside this
+repository.
+
 The two files need nothing but nvcc and the PyTorch extension headers (reference: chat.py:62-63, spec_mega.py:29-31
 build them the same way, with -O3 --use_fast_math). The resulting pybind11 modules are used by the GPU tests as a
 second checker at the reference's native head shape (40 query / 8 kv heads of 64) and by nothing else.
@@ -16,7 +19,7 @@ TARGETS = {"flint_ref_decode": "kernels/megakernel_decode.cu", "flint_ref_verify
 
 
 def build(ref: str = None, verbose: bool = False):
-    ref = ref or os.environ.get("FLINT_REFERENCE", "/root/reference")
+    ref = ref or os.environ.get("FLINT_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     if not os.path.isdir(ref):
         raise FileNotFoundError(f"reference checkout not found at {ref}")
     os.makedirs(OUT, exist_ok=True)

@@ -28,6 +28,9 @@
  * into oracle/_ref, the reference megakernel itself at its native head shape.
  */
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -228,6 +231,18 @@ void fo_dequant(const uint32_t *q, const uint16_t *s, const uint16_t *z, int row
       const float v = nib * sc;
       out[(size_t)r * k + c] = z ? v + bf2f(z[(size_t)r * groups + c / 128]) : v;
     }
+}
+
+/* Launchers export OMP_NUM_THREADS=1 to their children (torch.distributed.run does): the timed CPU baseline sets the
+ * thread count itself. Returns the count in force. */
+int fo_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
 }
 
 int fo_argmax(const float *v, int n) { /* first index of the maximum (torch.argmax tie rule) */

@@ -62,6 +62,13 @@ def lib():
     return _lib
 
 
+def set_threads(n: int = 0) -> int:
+    """OpenMP threads of the oracle (0 = leave as is); returns the count in force. Process launchers often export
+    OMP_NUM_THREADS=1, which would turn the timed CPU baseline into a one-core run."""
+    lib().fo_set_threads.restype = ctypes.c_int
+    return int(lib().fo_set_threads(ctypes.c_int(int(n))))
+
+
 def _np(t) -> np.ndarray:
     """torch tensor (bf16 viewed as int16) or ndarray -> C-contiguous ndarray sharing or copying the bits."""
     if isinstance(t, np.ndarray):

@@ -36,6 +36,8 @@ def main():
     model = Transformer.from_name(a.config).load_synthetic(seed=0)
     cfg: ModelArgs = model.config
     draft = seeded_draft(cfg.dim, cfg.n_head, cfg.intermediate_size, seed=1, rope_base=cfg.rope_base, device="cuda")
+    draft.bind_target(model.packed["embed"], model.packed["nf"], cfg.logits_scaling)
+    draft.setup_cache(32 + 8)
     if not a.tree:
         prompt = torch.randint(0, cfg.vocab_size, (32,), generator=torch.Generator().manual_seed(1234), dtype=torch.int32)
         t0 = time.perf_counter()
@@ -53,8 +55,8 @@ def main():
     am = torch.from_numpy(tree_mask(parent)).cuda()
     dp = torch.tensor(depth, dtype=torch.int32, device="cuda")
     toks = torch.randint(0, cfg.vocab_size, (a.nodes,), device="cuda", dtype=torch.int32)
-    feat = torch.randn(1, 32, cfg.dim, device="cuda").bfloat16()
-    emb = torch.randn(1, 32, cfg.dim, device="cuda").bfloat16()
+    feat = torch.randn(32, cfg.dim, device="cuda").bfloat16()
+    wtok = torch.full((32,), -1, dtype=torch.int32, device="cuda")
 
     def timed(fn, n=5):
         fn()
@@ -66,8 +68,16 @@ def main():
         return (time.perf_counter() - t0) / n
 
     t_ver = timed(lambda: eng.verify(toks, a.cache, dp, am))
-    pos32 = torch.arange(32, device="cuda")
-    rollout = lambda: [draft(feat, emb, pos32) for _ in range(5)]                                    # depth-5 rollout
+    pos32 = torch.arange(32, dtype=torch.int32, device="cuda")
+    steps = [torch.tensor([32 + i], dtype=torch.int32, device="cuda") for i in range(4)]
+
+    def rollout():                                   # window prime + 4 single steps = a depth-5 chain, all on the device
+        fp = draft(feat, None, pos32, input_pos=pos32, tokens=wtok)
+        f = fp[31:32]
+        t = draft.head(f).view(1)
+        for i in range(4):
+            f = draft(f, None, steps[i], input_pos=steps[i], tokens=t)[0:1]
+            t = draft.head(f).view(1)
     t_draft_eager = timed(rollout)
     g = torch.cuda.CUDAGraph()                       # the reference replays its draft from a CUDA graph too
     with torch.cuda.graph(g):

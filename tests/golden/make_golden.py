@@ -34,7 +34,9 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLINT_REFERENCE", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLINT_REFERENCE")
+    if not ref or not os.path.isdir(ref):
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference   (or set FLINT_REFERENCE)")
     sys.path.insert(0, ref)
     sys.path.insert(0, os.path.join(ref, "engine"))
     sys.path.insert(0, os.path.join(ref, "train"))

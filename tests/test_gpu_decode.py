@@ -141,19 +141,50 @@ def test_determinism_bitwise():
 
 
 def test_wait_runs_out_reports_timeout_and_context_survives():
-    """A spin limit of 1 makes some bounded wait give up: the launch must end, report FB_ERR_TIMEOUT and the
-    next launch with a sane limit must work."""
+    """A wait that nothing satisfies: two tensor-parallel ranks live in this process on this GPU, only rank 0 launches.
+    Rank 0's own phases complete, then it polls its inbox for rank 1's partial sums, which never arrive: the bounded
+    wait runs out, the launch ENDS, the host reads FB_ERR_TIMEOUT with the place it gave up, and the GPU stays usable:
+    a fresh single-GPU context decodes correctly afterwards."""
+    import ctypes
+    from flint_b200 import _lib
+    from flint_b200.tp import shard_packed
+    cfg = ModelArgs(block_size=32, vocab_size=1024, n_layer=2, n_head=8, n_local_heads=2, dim=512, intermediate_size=1536)
+    P = packing.synth_packed(cfg, 0)
+    one = DecodeEngine(cfg, _to_cuda(P), max_seq=32)
+    ref = one.decode(5, 0).clone()
+    one.check()
+    ranks = [DecodeEngine(cfg, _to_cuda(shard_packed(P, cfg, r, 2)), max_seq=32, tp_rank=r, tp_size=2) for r in (0, 1)]
+    arr = (ctypes.c_void_p * 2)(ranks[0]._ctx, ranks[1]._ctx)
+    for e in ranks:
+        _lib.check(e.lib.fb_tp_connect_local(e._ctx, arr, 2), "fb_tp_connect_local")
+    ranks[0].set_option(0, 20000)              # far above any wait of a healthy launch, milliseconds for the dead one
+    ranks[0].decode(5, 0)
+    st = ranks[0].status()
+    assert st["code"] == _lib.FB_ERR_TIMEOUT, st
+    assert st["where"] == 5 and st["layer"] == 0, st       # a tagged-word wait in the first layer's exchange
+    for e in ranks:
+        e.close()
+    again = one.decode(5, 0).clone()
+    one.check()
+    assert torch.equal(ref, again)
+    fresh = DecodeEngine(cfg, _to_cuda(P), max_seq=32)
+    assert torch.equal(ref, fresh.decode(5, 0))
+    fresh.check()
+
+
+def test_spin_limit_zero_gives_up_at_once():
+    """With a limit of 0 every wait that is not already satisfied gives up: the launch still ends and reports
+    FB_ERR_TIMEOUT or, if every wait happened to be satisfied, nothing; either way the next launch is clean."""
     cfg = ModelArgs.from_name("tiny")
     W = _to_cuda(packing.synth_packed(cfg, 0))
     e = DecodeEngine(cfg, W, max_seq=32)
     ref = e.decode(5, 0).clone()
     e.check()
-    e.set_option(0, 1)
+    e.set_option(0, 0)
     e.decode(5, 0)
     st = e.status()
+    assert st["code"] in (0, 5), st
     e.set_option(0, 4000000)
-    if st["code"] != 0:
-        assert st["code"] == 5
     again = e.decode(5, 0).clone()
     e.check()
     assert torch.equal(ref, again)
@@ -250,3 +281,74 @@ def test_granite3b_class_full_depth_vs_oracle():
         agree += int(int(eng.next_token.item()) == O.argmax_first(ref))
     assert worst_rel < 0.1, worst_rel
     assert agree == len(toks)
+
+
+def test_llama8b_class_shape_two_layers_vs_oracle():
+    """The 8B-class shape on ONE GPU (d 4096, 32/8 heads of 128, FFN 14336 = tiles of 2 rows, vocab 128256, untied LM
+    head, RoPE base 500000) at a depth of 2 layers against the oracle: the kernel instantiation the tensor-parallel
+    configuration is built from."""
+    cfg = ModelArgs.from_name("llama-8b-class")
+    cfg.n_layer = 2
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    orc = O.OracleModel(cfg, P, 64)
+    eng = DecodeEngine(cfg, W, max_seq=64)
+    worst, agree = 0.0, 0
+    toks = [17, 120000, 123, 4567, 9, 31000]
+    for pos, t in enumerate(toks):
+        ref = orc.decode(t, pos)
+        got = eng.decode(t, pos).cpu().numpy()
+        eng.check()
+        worst = max(worst, float(np.abs(got - ref).max()) / logit_tol(ref))
+        tok = int(eng.next_token.item())
+        agree += int(tok == O.argmax_first(ref) or ref[tok] >= ref.max() - logit_tol(ref))
+    assert worst < 1.0, worst
+    assert agree == len(toks)
+
+
+def test_granite3b_class_256_greedy_steps_agree_with_oracle():
+    """The agreement gate at the configuration it is stated for: all 40 layers, 128-token prompt, 256 greedy steps,
+    teacher-forced on the oracle's tokens.
+
+    The seeded N(0, 0.02) model has nearly flat logits and is chaotic under bf16 rounding at this depth: ONE bf16 ulp
+    flipped in ONE input element moves the oracle's OWN logits by up to 0.17 (tests/test_packer_oracle.py measures it at
+    the tiny scale). A step whose two best logits are closer than that is decided by rounding noise in any
+    implementation, the oracle included. So the gate is: on the steps the oracle itself decides (top-2 margin above
+    twice that sensitivity) >= 99 % of the device's picks equal the oracle's, and EVERY pick, decided step or not, lies
+    within three sensitivities of the oracle's best logit."""
+    SENS = 0.17
+    cfg = ModelArgs.from_name("granite-3b-class")
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    n_prompt, steps = 128, 256
+    orc = O.OracleModel(cfg, P, n_prompt + steps + 1)
+    eng = DecodeEngine(cfg, W, max_seq=n_prompt + steps + 1)
+    seq = torch.randint(0, cfg.vocab_size, (n_prompt,), generator=torch.Generator().manual_seed(1234)).tolist()
+    picks = torch.zeros(n_prompt + steps, dtype=torch.int32, device="cuda")
+    refs = []
+    for pos in range(n_prompt + steps - 1):
+        eng.decode(seq[pos], pos, next_token=picks[pos:pos + 1], want_logits=False)
+        ref = orc.decode(seq[pos], pos)
+        if pos >= n_prompt - 1:
+            best = O.argmax_first(ref)
+            seq.append(best)
+            refs.append(ref)
+    eng.check()
+    got = picks[n_prompt - 1:n_prompt + steps - 1].tolist()
+    assert len(got) == len(refs) == steps
+    decided = agree_decided = agree_all = 0
+    worst_gap = 0.0
+    for tok, ref in zip(got, refs):
+        top2 = np.partition(ref, -2)[-2:]
+        margin = float(top2[1] - top2[0])
+        same = int(tok == O.argmax_first(ref))
+        agree_all += same
+        worst_gap = max(worst_gap, float(ref.max() - ref[tok]))
+        if margin > 2 * SENS:
+            decided += 1
+            agree_decided += same
+    print(f"greedy agreement: {agree_all}/{steps} of all steps, {agree_decided}/{decided} of the decided steps, "
+          f"worst gap of a pick to the oracle's best logit {worst_gap:.3f}")
+    assert worst_gap <= 3 * SENS, worst_gap
+    assert agree_decided >= 0.99 * decided, (agree_decided, decided)
+    assert decided >= steps // 8, decided          # the gate must bite on a real share of the steps

@@ -52,7 +52,7 @@ def _worker(rank, world, port, name, n_layer, steps, ret):
 
 
 @pytest.mark.parametrize("name,world", [("granite-3b-class", 2), ("llama-8b-class", 2), ("llama-8b-class", 4),
-                                        ("llama-8b-class", 8), ("granite-3b-class", 4)])
+                                        ("llama-8b-class", 8), ("granite-3b-class", 4), ("granite-3b-class", 8)])
 def test_tp_matches_single_gpu(name, world):
     """TP-N logits against TP-1 on the same seeded 2-layer model (full-size matrices): only the fp32 summation order of
     the two K-sharded projections differs, so rel-L2 stays at the bf16-flip level and the greedy tokens agree."""
@@ -67,3 +67,56 @@ def test_tp_matches_single_gpu(name, world):
     mp.spawn(_worker, args=(world, port, name, 2, steps, ret), nprocs=world, join=True)
     assert ret["rel"] < 0.02, dict(ret)
     assert ret["agree"] >= steps - 1, dict(ret)
+
+
+def _worker_peer_missing(rank, world, port, ret):
+    """Rank 1 skips one step (between steps, nothing of its own in flight); rank 0 launches it with a short spin limit.
+    The two ranks then rebuild their contexts and decode together again."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from flint_b200 import packing
+    from flint_b200.config import ModelArgs
+    from flint_b200.engine import DecodeEngine
+    from flint_b200.tp import make_tp_engine
+    cfg = ModelArgs.from_name("granite-3b-class")
+    cfg.n_layer = 2
+    dev = torch.device(f"cuda:{rank}")
+    W = packing.synth_packed(cfg, 0, device=str(dev))
+    eng = make_tp_engine(cfg, W, max_seq=64, device=dev)
+    nxt = torch.zeros(1, dtype=torch.int32, device=dev)
+    eng.decode(17, 0, next_token=nxt, want_logits=False)       # a healthy step on both ranks
+    assert eng.status()["code"] == 0
+    dist.barrier()
+    if rank == 0:
+        eng.set_option(0, 20000)
+        eng.decode(5, 1, want_logits=False)                   # the peer never launches this step
+        st = eng.status()
+        ret["code"], ret["where"] = st["code"], st["where"]
+    dist.barrier()                                            # rank 1 learns of the failed step on the host
+    eng.close()
+    eng = make_tp_engine(cfg, W, max_seq=64, device=dev)
+    lg = torch.zeros(cfg.vocab_size, dtype=torch.float32, device=dev)
+    eng.decode(17, 0, logits=lg, next_token=nxt)
+    assert eng.status()["code"] == 0
+    if rank == 0:
+        one = DecodeEngine(cfg, W, max_seq=64)
+        one.decode(17, 0)
+        one.check()
+        ret["token_after"] = int(nxt.item())
+        ret["token_single"] = int(one.next_token.item())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_peer_that_never_arrives_times_out_and_ranks_recover():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker_peer_missing, args=(2, port, ret), nprocs=2, join=True)
+    assert ret["code"] == 5 and ret["where"] == 5, dict(ret)      # FB_ERR_TIMEOUT in a tagged-word wait
+    assert ret["token_after"] == ret["token_single"], dict(ret)

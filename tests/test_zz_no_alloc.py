@@ -1,4 +1,4 @@
-"""GPU: the allocation-free GEMV entry point (fb_gemv_static) against the ordinary one (fb_repack + fb_gemv).
+"""GPU: the allocation-free GEMV entry point (fb_gemv_static) against the ordinary one (fb_repack + fb_gemv) and the CPU oracle.
 
 Some hosts of this library may not allocate device memory once they are running: a server that has handed all of HBM to
 its own arena, or code inside a stream capture. For them the library carries the GEMV's scratch (the streaming-layout
@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from flint_b200 import _lib, packing
+from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +60,9 @@ def test_static_scratch_gemv_matches_ordinary_entry_point_twice():
         scale = float(want.abs().max()) + 1e-6
         assert float((y - want).abs().max()) / scale < 2e-5       # the bound the GEMV tests use; same kernels: equal
         assert torch.equal(y, want)
+        # and on its own feet: the CPU oracle's GEMV on the caller-layout tensors (fp32 summation order differs)
+        ref = O.c_gemv(q.cpu(), s.cpu(), None if z is None else z.cpu(), x.cpu())[0]
+        assert float(np.abs(y.cpu().numpy() - ref).max()) / (float(np.abs(ref).max()) + 1e-6) < 2e-5
 
 
 def test_static_scratch_rejects_oversized_matrix():
