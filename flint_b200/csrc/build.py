@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-LIB = os.path.join(os.path.dirname(HERE), "libflintb200.so")
+LIB = os.environ.get("FLINT_B200_BUILD_OUT") or os.path.join(os.path.dirname(HERE), "libflintb200.so")
 SOURCES = ["fb_api.cu", "fb_spec.cu"]
 HEADERS = sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))) + [os.path.join(ROOT, "include", "flint_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -38,7 +38,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.wait() != 0:
             raise subprocess.CalledProcessError(p.returncode, cmd)
     tmp = LIB + f".tmp{os.getpid()}"
-    subprocess.check_call([nvcc, "-shared", "-Xcompiler", "-fPIC", "-o", tmp] + objs + ["-lcudart"])
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-o", tmp] + objs + ["-lcudart"])
     os.replace(tmp, LIB)
     for o in objs:
         os.remove(o)

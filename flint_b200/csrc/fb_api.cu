@@ -10,6 +10,7 @@
 #include "fb_ctx.hpp"
 #include "fb_decode.cuh"
 #include "fb_verify.cuh"
+#include "fb_vtc.cuh"
 
 using namespace fb;
 
@@ -31,6 +32,7 @@ const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(512, 512, 1536, 64, 4),       // tiny decoder whose FFN splits into whole groups over 2 ranks
     FB_DECODE_ENTRY(512, 256, 768, 64, 4),        // ... and its 2-rank slice
     FB_DECODE_ENTRY(2560, 2560, 8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
+#ifndef FB_KERNELS_MINIMAL                        // (a build for kernel experiments keeps only the shapes above)
     FB_DECODE_ENTRY(2560, 2560, 8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
     FB_DECODE_ENTRY(4096, 4096, 14336, 128, 4),   // 8B-class
     FB_DECODE_ENTRY(2560, 1280, 4096, 80, 4),     // 3B-class over 2 GPUs
@@ -39,6 +41,7 @@ const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(4096, 2048, 7168, 128, 4),    // 8B-class over 2 GPUs
     FB_DECODE_ENTRY(4096, 1024, 3584, 128, 4),    // 8B-class over 4 GPUs
     FB_DECODE_ENTRY(4096, 512, 1792, 128, 4),     // 8B-class over 8 GPUs
+#endif
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
 
@@ -212,6 +215,44 @@ cudaError_t launch_vgemm_mt(const VGemmParams& p, int mt, int k, int hd, int sms
   }
   return cudaErrorInvalidValue;
 }
+constexpr int kTcMaxItems = 256;      // split-K work items whose partial sums the context can hold
+
+// K splits of one verify GEMM: enough (row block, split) items to occupy the GPU, whole groups per split, at most 4
+// partials to add, at most kTcMaxGroups groups per item
+int tc_splits(int rows, int k, int sms) {
+  const int rb = (rows + kTcRowBlock - 1) / kTcRowBlock, G = k / 128;
+  int ns = 1;
+  while (ns < 4 && rb * ns < sms * 3 / 4 && G / (ns * 2) >= 2 && rb * ns * 2 <= kTcMaxItems) ns *= 2;
+  while ((G + ns - 1) / ns > kTcMaxGroups && ns < 64) ns *= 2;
+  return ns;
+}
+
+template <int MT, int EPI>
+cudaError_t launch_vtc_mt(VtcParams& p, int sms, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(v_gemm_tc<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, VtcSmem<MT>::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  p.nsplit = tc_splits(p.rows, p.K, sms);
+  const int items = ((p.rows + kTcRowBlock - 1) / kTcRowBlock) * p.nsplit;
+  if (p.K % 128 || (p.K / 128 + p.nsplit - 1) / p.nsplit > kTcMaxGroups || (p.nsplit > 1 && items > kTcMaxItems))
+    return cudaErrorInvalidValue;
+  return launch_pdl(v_gemm_tc<MT, EPI>, dim3(items < sms ? items : sms), dim3(kTcThreads), (size_t)VtcSmem<MT>::TOTAL, st, p);
+}
+template <int EPI>
+cudaError_t launch_vtc(VtcParams& p, int mt, int sms, cudaStream_t st) {
+  switch (mt) {
+    case 16: return launch_vtc_mt<16, EPI>(p, sms, st);
+    case 32: return launch_vtc_mt<32, EPI>(p, sms, st);
+    case 64: return launch_vtc_mt<64, EPI>(p, sms, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_vnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D, int M, float eps,
                          cudaStream_t st) {
   if (D % 16 || D > 8 * 256 * 2) return cudaErrorInvalidValue;
@@ -221,7 +262,7 @@ cudaError_t launch_vnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, u
 constexpr int kVSpans = 32;       // most spans of positions a kv head's attention is cut into
 
 cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc, const uint16_t* vc, const uint8_t* amask,
-                         uint16_t* ao, int pos, int M, cudaStream_t st) {
+                         uint16_t* ao, int pos, int M, int natural, cudaStream_t st) {
   const fb_model_desc& d = c->d;
   const int T = pos + M;
   int S = (T + 63) / 64;
@@ -234,7 +275,7 @@ cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc,
                                d.n_head, d.n_kv_head, pos, M, d.attn_scale, span);                                      \
     if (e != cudaSuccess) return e;                                                                                     \
     return launch_pdl(v_attn_merge<HD_, R_>, dim3(M, d.n_kv_head), dim3(256), 0, st, (const float*)c->vpart, ao, d.n_head, \
-                      d.n_kv_head, M, S);                                                                               \
+                      d.n_kv_head, M, S, natural);                                                                      \
   }
   FB_VATTN(64, 4) FB_VATTN(80, 4) FB_VATTN(64, 5) FB_VATTN(128, 4)
 #undef FB_VATTN
@@ -340,6 +381,10 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
     }
   }
   A(dmalloc(&c->vpart, (size_t)d.n_kv_head * 32 * 64 * c->rgqa * (d.head_dim + 2) * 4));
+  A(dmalloc(&c->vsplit, (size_t)kTcMaxItems * 64 * 128 * 4));
+  A(dmalloc(&c->vcount, 4096 * 4));
+  if (e == cudaSuccess) A(cudaMemset(c->vcount, 0, 4096 * 4));
+  A(cudaMalloc(&c->vrope, (size_t)64 * (d.head_dim / 2) * 8));
   A(dmalloc(&c->flags, 3 * 256 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
@@ -370,7 +415,8 @@ int fb_ctx_destroy(fb_ctx* c) {
     if (c->peers_open[p] && c->peer_inbox[p]) cudaIpcCloseMemHandle(c->peer_inbox[p]);
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf,
                   c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->flags,
-                  c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox};
+                  c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox,
+                  c->t_qkv, c->t_o, c->t_gu, c->t_d, c->t_lm, c->vsplit, c->vcount, c->vrope};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -382,6 +428,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
+  if (what == 7) { c->verify_path = value != 0; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -512,19 +559,27 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int L = d.n_layer, D = d.dim, FF = d.ffn, HD = d.head_dim;
   const int QKV = (d.n_head + 2 * d.n_kv_head) * HD, QD = d.n_head * HD;
-  struct M { uint8_t** dst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
+  struct M { uint8_t** dst; uint8_t** tdst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
   M ms[] = {
-      {&c->w_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
-      {&c->w_o, w->o_q, w->o_s, w->o_z, L, D, c->ko, 0, 0, 0},
-      {&c->w_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
-      {&c->w_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
-      {&c->w_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
+      {&c->w_qkv, &c->t_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
+      {&c->w_o, &c->t_o, w->o_q, w->o_s, w->o_z, L, D, c->ko, 0, 0, 0},
+      {&c->w_gu, &c->t_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
+      {&c->w_d, &c->t_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
+      {&c->w_lm, &c->t_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
   };
   for (M& m : ms) {
     const size_t bytes = (size_t)m.layers * pad_rows(m.rows, m.k) * rec_bytes_of(m.k, hz);
     if (*m.dst) { cudaFree(*m.dst); *m.dst = nullptr; }
     FB_CUDA(c, dmalloc(m.dst, bytes + 16));
     FB_CUDA(c, launch_repack(m.q, m.s, hz ? m.z : nullptr, m.layers, m.rows, m.k, m.order, m.arg, m.orows, *m.dst, st));
+    if (*m.tdst) { cudaFree(*m.tdst); *m.tdst = nullptr; }
+    if (c->tp_size == 1) {     // the verify path's own copy, in the layout the tcgen05 GEMM streams
+      const int nrb = (m.rows + kTcRowBlock - 1) / kTcRowBlock;
+      FB_CUDA(c, dmalloc(m.tdst, (size_t)m.layers * tc_matrix_bytes(m.rows, m.k, hz) + 16));
+      tc_repack<<<dim3(nrb, m.layers), 256, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s, hz ? (const uint16_t*)m.z : nullptr,
+                                                     m.rows, m.k, m.order, m.arg, m.orows, *m.tdst);
+      FB_CUDA(c, cudaGetLastError());
+    }
   }
   c->n1 = w->n1; c->n2 = w->n2; c->nf = w->nf; c->embed = w->embed;
   c->weights_bound = true;
@@ -597,6 +652,41 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
                strG = (size_t)pad_rows(2 * FF, D) * rec_bytes_of(D, hz), strF = (size_t)pad_rows(D, FF) * rec_bytes_of(FF, hz);
   FB_CUDA(c, launch_pdl(v_embed, dim3(M), dim3(256), 0, st, d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh,
                         D, d.vocab, d.emb_mult, &c->status->code));
+  if (c->verify_path == 0) {
+    // ---- tcgen05 path: natural-order activations, the matrices in the TC layout ----
+    const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),
+                 tF = tc_matrix_bytes(D, FF, hz);
+    FB_CUDA(c, launch_pdl(v_rope_table, dim3(M), dim3(64), 0, st, d_depth, (const float*)c->invf, (int)pos, HD / 2, (float2*)c->vrope));
+    VtcParams t;
+    memset(&t, 0, sizeof(t));
+    t.M = M; t.has_zeros = hz; t.part = c->vsplit; t.counters = c->vcount; t.status = c->status; t.spin_limit = c->spin_limit;
+    t.rope = (const float2*)c->vrope; t.n_head = d.n_head; t.nkv = d.n_kv_head; t.pos = pos; t.head_dim = HD;
+    t.resid = d.resid_mult; t.logits_scaling = d.logits_scaling;
+    for (int l = 0; l < d.n_layer; l++) {
+      uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
+      uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
+      FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, nullptr, c->vxn, D, M, d.rms_eps, st));
+      t.w = c->t_qkv + l * tQ; t.x = c->vxn; t.rows = QKV; t.K = D; t.q = c->vq; t.kc = kcl; t.vc = vcl;
+      FB_CUDA(c, launch_vtc<EPI_QKV>(t, MT, c->sm_count, st));
+      FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, 1, st));
+      t.w = c->t_o + l * tO; t.x = c->vao; t.rows = D; t.K = QD; t.h = c->vh; t.out_ld = D;
+      FB_CUDA(c, launch_vtc<EPI_RESID>(t, MT, c->sm_count, st));
+      FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, nullptr, c->vxn, D, M, d.rms_eps, st));
+      t.w = c->t_gu + l * tG; t.x = c->vxn; t.rows = 2 * FF; t.K = D; t.act = c->vact; t.out_ld = FF;
+      FB_CUDA(c, launch_vtc<EPI_SWIGLU>(t, MT, c->sm_count, st));
+      t.w = c->t_d + l * tF; t.x = c->vact; t.rows = D; t.K = FF; t.out_ld = D;
+      FB_CUDA(c, launch_vtc<EPI_RESID>(t, MT, c->sm_count, st));
+    }
+    // the feature goes to the caller in natural order; the LM head reads the same rows
+    uint16_t* feat = d_feat ? (uint16_t*)d_feat : c->vxn;
+    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, nullptr, feat, D, M, d.rms_eps, st));
+    if (d_logits) {
+      t.w = c->t_lm; t.x = feat; t.rows = d.vocab; t.K = D; t.logits = d_logits; t.out_ld = d.vocab;
+      FB_CUDA(c, launch_vtc<EPI_LOGITS>(t, MT, c->sm_count, st));
+    }
+    FB_CUDA(c, cudaGetLastError());
+    return FB_OK;
+  }
   VGemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = M; p.has_zeros = hz; p.depth = d_depth; p.invf = c->invf; p.n_head = d.n_head; p.nkv = d.n_kv_head; p.pos = pos;
@@ -608,7 +698,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
     p.q = c->vq; p.kc = kcl; p.vc = vcl;
     FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, c->sm_count, st));
-    FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, st));
+    FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, 0, st));
     p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
     FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, c->sm_count, st));
     FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));

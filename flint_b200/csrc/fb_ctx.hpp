@@ -30,5 +30,10 @@ struct fb_ctx {
   bool peers_open[8];
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   float* vpart;                                                     // verify attention: per-span partials
+  uint8_t *t_qkv, *t_o, *t_gu, *t_d, *t_lm;                          // verify: the matrices in the tensor-core (TC) layout
+  float* vsplit;                                                    // verify: split-K partial sums
+  unsigned* vcount;                                                 // verify: arrivals per (row block, row quadrant)
+  void* vrope;                                                      // verify: (cos, sin) per (token, rotation pair)
+  int verify_path;                                                  // 0: tcgen05 GEMMs, 1: warp-level MMA GEMMs
   int max_fly, poll_words;
 };

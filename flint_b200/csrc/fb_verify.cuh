@@ -91,9 +91,11 @@ __global__ void __launch_bounds__(256) v_rmsnorm(const uint16_t* h, const uint16
       for (int e = 0; e < 4; e++)
         o[e] = (uint32_t)f2bf(bflo(p[e]) * r * bflo(q[e])) | ((uint32_t)f2bf(bfhi(p[e]) * r * bfhi(q[e])) << 16);
       // elements 8i .. 8i+7 are half (i & 1) of a 16-block: pair e goes to 32-bit slot 2e + half of the block
-      uint32_t* dst = reinterpret_cast<uint32_t*>(xn_t + (size_t)m * D + (size_t)(i >> 1) * 16);
+      if (xn_t) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(xn_t + (size_t)m * D + (size_t)(i >> 1) * 16);
 #pragma unroll
-      for (int e = 0; e < 4; e++) dst[2 * e + (i & 1)] = o[e];
+        for (int e = 0; e < 4; e++) dst[2 * e + (i & 1)] = o[e];
+      }
       if (xn_nat) reinterpret_cast<uint4*>(xn_nat + (size_t)m * D)[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
@@ -258,9 +260,10 @@ __global__ void __launch_bounds__(128) v_attn_mma(const uint16_t* q, const uint1
   }
 }
 
-// one CTA per (token, kv head): combine the spans' partials, write bf16 in B order (S <= 32 spans)
+// one CTA per (token, kv head): combine the spans' partials, write bf16 in B order or natural order (S <= 32 spans)
 template <int HD, int R>
-__global__ void __launch_bounds__(256) v_attn_merge(const float* part, uint16_t* ao_t, int n_head, int nkv, int M, int S) {
+__global__ void __launch_bounds__(256) v_attn_merge(const float* part, uint16_t* ao_t, int n_head, int nkv, int M, int S,
+                                                    int natural) {
   constexpr int PW = HD + 2, MAXS = 32;
   const int m = blockIdx.x, kvh = blockIdx.y, rows = M * R, QD = n_head * HD;
   pdl_trigger();
@@ -286,7 +289,8 @@ __global__ void __launch_bounds__(256) v_attn_merge(const float* part, uint16_t*
       Dn = fmaf(pl[s2], e, Dn);
       A = fmaf(pa[s2], e, A);
     }
-    ao_t[(size_t)m * QD + k16_pos((kvh * R + r) * HD + d)] = f2bf(A / Dn);
+    const int col = (kvh * R + r) * HD + d;
+    ao_t[(size_t)m * QD + (natural ? col : k16_pos(col))] = f2bf(A / Dn);
   }
 }
 
