@@ -227,13 +227,13 @@ int tc_splits(int rows, int k, int sms) {
   return ns;
 }
 
-template <int MT, int EPI>
-cudaError_t launch_vtc_mt(VtcParams& p, int sms, cudaStream_t st) {
+template <int MT, int EPI, bool HZ>
+cudaError_t launch_vtc_hz(VtcParams& p, int sms, cudaStream_t st) {
   static bool configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(v_gemm_tc<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, VtcSmem<MT>::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(v_gemm_tc<MT, EPI, HZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, VtcSmem<MT, HZ>::TOTAL);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -241,7 +241,11 @@ cudaError_t launch_vtc_mt(VtcParams& p, int sms, cudaStream_t st) {
   const int items = ((p.rows + kTcRowBlock - 1) / kTcRowBlock) * p.nsplit;
   if (p.K % 128 || (p.K / 128 + p.nsplit - 1) / p.nsplit > kTcMaxGroups || (p.nsplit > 1 && items > kTcMaxItems))
     return cudaErrorInvalidValue;
-  return launch_pdl(v_gemm_tc<MT, EPI>, dim3(items < sms ? items : sms), dim3(kTcThreads), (size_t)VtcSmem<MT>::TOTAL, st, p);
+  return launch_pdl(v_gemm_tc<MT, EPI, HZ>, dim3(items < sms ? items : sms), dim3(kTcThreads), (size_t)VtcSmem<MT, HZ>::TOTAL, st, p);
+}
+template <int MT, int EPI>
+cudaError_t launch_vtc_mt(VtcParams& p, int sms, cudaStream_t st) {
+  return p.has_zeros ? launch_vtc_hz<MT, EPI, true>(p, sms, st) : launch_vtc_hz<MT, EPI, false>(p, sms, st);
 }
 template <int EPI>
 cudaError_t launch_vtc(VtcParams& p, int mt, int sms, cudaStream_t st) {

@@ -1,11 +1,13 @@
 // int4 x bf16 GEMM of the M-token verify path on the 5th-generation tensor cores (tcgen05): every weight row is read
 // once and multiplied with all MT <= 64 candidate tokens.
 //
-// D[128 weight rows][MT tokens] (fp32, in TENSOR MEMORY) = A[128][64] * B[MT][64]^T per 64-column chunk, issued by one
-// thread as four tcgen05.mma (K = 16 each). A is the chunk's weights dequantised to bf16 (nib - 8) / 64 — exact — and
-// written by 128 threads into shared memory in the K-major 128-byte-swizzle layout the MMA reads; B is the tokens'
-// activations, copied into the same layout by cp.async. A group of 128 columns (two chunks) shares one bf16 scale per
-// row, so every group accumulates into its own TMEM accumulator (two, used alternately); four epilogue warps read a
+// D[128 weight rows][MT tokens] (fp32, in TENSOR MEMORY) = A[128][128] * B[MT][128]^T per group of 128 columns, issued by
+// one thread as eight tcgen05.mma (K = 16 each). A is the chunk's weights dequantised to bf16 (nib - 8) / 64 — exact — by 128
+// threads, thread = weight row = TMEM lane, and stored with tcgen05.st straight into tensor memory (a ring of four
+// 64-column stages): routing A through shared memory would cost 8 bytes of shared-memory traffic per int4 byte and cap
+// the kernel well below the HBM rate. B is the tokens' activations, copied by cp.async into shared memory in the K-major
+// 128-byte-swizzle layout the MMA reads. A group of 128 columns shares one bf16 scale per
+// row, so every group accumulates into its own TMEM accumulator (a ring of them); four epilogue warps read a
 // finished group with tcgen05.ld and fold it into per-thread fp32 sums with the row's scale: the arithmetic is the
 // reference's sum (nib - 8) * s * x with fp32 accumulation (reference: kernels/verify_mega.cu:18-75), only the order of
 // summation differs. The asymmetric layout's zero points ride the same chunks as a second MMA with A = z (exact in bf16)
@@ -26,8 +28,7 @@
 
 namespace fb {
 
-constexpr int kTcRaw = 8;         // raw int4 chunks in flight (4 KB each)
-constexpr int kTcStages = 4;      // dequantised A / activation B stages
+constexpr int kTcStages = 4;      // operand stages: A (dequantised group, 64 TMEM columns) and B (activations, shared memory)
 constexpr int kTcThreads = 14 * 32;
 constexpr int kTcRowBlock = 128;
 
@@ -140,20 +141,43 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&v)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr));
 }
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+        "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // shared-memory plan (bytes): raw ring, A stages (+ zero-point A stages), B stages, scales (2 items), barriers
 constexpr int kTcMaxGroups = 32;  // groups of one work item (the host raises the K split until this holds)
-template <int MT>
+// shared-memory plan (bytes). The raw ring is what keeps HBM busy: 12..14 groups of 8 KB in flight per SM; a stage of
+// activations is the group's two 64-column tiles.
+template <int MT, bool HZ>
 struct VtcSmem {
+  static constexpr int NRAW = HZ ? 12 : 14;                        // raw int4 groups in flight (8 KB each)
+  static constexpr int BSTAGE = MT * 256;                          // two [MT rows x 128 bytes] swizzled tiles
   static constexpr int RAW = 0;
-  static constexpr int A = RAW + kTcRaw * 4096;
-  static constexpr int AZ = A + kTcStages * 16384;                 // asymmetric layout only: A = z per row, per group parity
-  static constexpr int B = AZ + 2 * 16384;
-  static constexpr int SC = B + kTcStages * MT * 128;
-  static constexpr int SC_BYTES = kTcMaxGroups * 256 * 2;          // scales, then zeros
-  static constexpr int BAR = SC + 2 * SC_BYTES;
-  static constexpr int TOTAL = BAR + 512 + 1024;                   // + slack to align the base to 1024 bytes
+  static constexpr int B = RAW + NRAW * 8192;
+  static constexpr int SC = B + kTcStages * BSTAGE;
+  static constexpr int SC_BYTES = kTcMaxGroups * 256 * (HZ ? 2 : 1);   // scales, then zeros
+  static constexpr int EPI = SC + 2 * SC_BYTES;                    // the item's sums, fp32 [MT][128 rows]
+  static constexpr int BAR = EPI + MT * 512;
+  static constexpr int TOTAL = BAR + 1024 + 1024;                  // barriers + slack to align the base to 1024 bytes
+  static_assert(TOTAL <= 227 * 1024, "verify GEMM shared memory");
+  // tensor memory columns: group accumulators, zero-point accumulator, A stages (64 columns = 128 bf16 per row), A_z
+  // (8 columns = one k16 step of the row's zero point, the same for every step of the group)
+  static constexpr int NACC = HZ ? 2 : 4;
+  static constexpr int T_ACCZ = NACC * MT, T_A = T_ACCZ + (HZ ? MT : 0), T_AZ = T_A + kTcStages * 64;
+  static_assert(T_AZ + (HZ ? kTcStages * 8 : 0) <= 512, "tensor memory columns");
 };
 
 // work items of this CTA in order; every role walks the same sequence
@@ -174,29 +198,35 @@ struct TcWalk {
   __device__ __forceinline__ void next() { item += step; set(); }
 };
 
-template <int MT, int EPI>
+__device__ __forceinline__ void tc_st8(uint32_t taddr, uint32_t z) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(z) : "memory");
+}
+
+template <int MT, int EPI, bool HZ>
 __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
-  using S = VtcSmem<MT>;
+  using S = VtcSmem<MT, HZ>;
+  constexpr int NRAW = S::NRAW, NS = kTcStages, NACC = S::NACC;
   extern __shared__ __align__(1024) uint8_t tsm_raw[];
   // the swizzle pattern is a function of the absolute shared-memory address: tiles must start on 1024-byte boundaries
   uint8_t* tsm = tsm_raw + ((1024u - (smem_u32(tsm_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tsm + S::BAR);
-  uint64_t *raw_full = bars, *raw_empty = bars + kTcRaw, *ab_full = bars + 2 * kTcRaw, *ab_empty = ab_full + kTcStages,
-           *acc_full = ab_empty + kTcStages, *acc_empty = acc_full + 2, *sc_full = acc_empty + 2, *sc_empty = sc_full + 2;
+  uint64_t *raw_full = bars, *raw_empty = bars + NRAW, *a_full = bars + 2 * NRAW, *b_full = a_full + NS, *s_empty = b_full + NS,
+           *acc_full = s_empty + NS, *acc_empty = acc_full + NACC, *sc_full = acc_empty + NACC, *sc_empty = sc_full + 2;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sc_empty + 2);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool hz = P.has_zeros != 0;
+  constexpr bool hz = HZ;
   const int K = P.K, G = K / 128;
   const size_t blk_bytes = tc_block_bytes(K, hz);
   if (tid == 0) {
-    for (int i = 0; i < kTcRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
-    for (int i = 0; i < kTcStages; i++) { mbar_init(&ab_full[i], 8); mbar_init(&ab_empty[i], 1); }
-    for (int i = 0; i < 2; i++) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 4); }
+    for (int i = 0; i < NRAW; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
+    for (int i = 0; i < NS; i++) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 4); mbar_init(&s_empty[i], 1); }
+    for (int i = 0; i < NACC; i++) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 4); }
     *s_abort = 0;
     mbar_fence_init();
   }
-  constexpr int TCOLS = 256;                                  // two group accumulators + the zero-point accumulator
+  constexpr int TCOLS = 512;
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TCOLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
@@ -209,9 +239,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
   pdl_trigger();
 
   if (warp == 0) {
-    // ---------------- producer: raw int4 chunks and the item's scales (weights do not depend on the previous kernel)
+    // ---------------- producer: raw int4 groups and the item's scales (weights do not depend on the previous kernel)
     if (lane == 0) {
-      uint32_t it = 0, ii = 0;
+      uint32_t gi = 0, ii = 0;
       for (TcWalk w(P.rows, K, P.nsplit); w.valid(); w.next(), ii++) {
         const uint8_t* blk = P.w + (size_t)w.rb * blk_bytes;
         const int b = ii & 1, ng = w.g1 - w.g0;
@@ -219,137 +249,132 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
         mbar_expect_tx(&sc_full[b], (uint32_t)ng * 256 * (hz ? 2 : 1));
         bulk_g2s(tsm + S::SC + b * S::SC_BYTES, blk + (size_t)(K / 64) * 4096 + (size_t)w.g0 * 256, ng * 256, &sc_full[b]);
         if (hz)
-          bulk_g2s(tsm + S::SC + b * S::SC_BYTES + kTcMaxGroups * 256, blk + (size_t)(K / 64) * 4096 + (size_t)(G + w.g0) * 256, ng * 256,
-                   &sc_full[b]);
+          bulk_g2s(tsm + S::SC + b * S::SC_BYTES + kTcMaxGroups * 256, blk + (size_t)(K / 64) * 4096 + (size_t)(G + w.g0) * 256,
+                   ng * 256, &sc_full[b]);
         bool ok = true;
-        for (int c = 2 * w.g0; c < 2 * w.g1 && ok; c++, it++) {
-          const int s = it % kTcRaw;
-          ok = mbar_wait(&raw_empty[s], ((it / kTcRaw) & 1) ^ 1, wc, W_EMPTY, 2);
+        for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+          const int s = gi % NRAW;
+          ok = mbar_wait(&raw_empty[s], ((gi / NRAW) & 1) ^ 1, wc, W_EMPTY, 2);
           if (!ok) break;
-          mbar_expect_tx(&raw_full[s], 4096);
-          bulk_g2s(tsm + S::RAW + s * 4096, blk + (size_t)c * 4096, 4096, &raw_full[s]);
+          mbar_expect_tx(&raw_full[s], 8192);
+          bulk_g2s(tsm + S::RAW + s * 8192, blk + (size_t)g * 8192, 8192, &raw_full[s]);
         }
         if (!ok) break;
       }
       // every copy issued must have landed before the CTA may exit: the consumers wait for all of them in a clean run;
       // after a failure, wait here (bounded)
       if (*s_abort) {
-        for (int k = 0; k < kTcRaw && k < (int)it; k++) {
-          const uint32_t j = it - 1 - k;
+        for (int k = 0; k < NRAW && k < (int)gi; k++) {
+          const uint32_t j = gi - 1 - k;
           for (unsigned i = 0; i < wc.limit; i++) {
-            if (mbar_try(&raw_full[j % kTcRaw], (j / kTcRaw) & 1)) break;
+            if (mbar_try(&raw_full[j % NRAW], (j / NRAW) & 1)) break;
             if ((i & 1023) == 1023) __nanosleep(64);
           }
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issue: one thread
+    // ---------------- MMA issue: one thread, eight MMAs per group, two commits
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((128u >> 4) << 24);
-      uint32_t it = 0, gi = 0;
+      uint32_t gi = 0;
       bool ok = true;
       for (TcWalk w(P.rows, K, P.nsplit); w.valid() && ok; w.next()) {
         for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
-          const int a = gi & 1;
-          ok = mbar_wait(&acc_empty[a], ((gi >> 1) & 1) ^ 1, wc, W_EMPTY, 3);
-          for (int half = 0; half < 2 && ok; half++, it++) {
-            const int s = it % kTcStages;
-            ok = mbar_wait(&ab_full[s], (it / kTcStages) & 1, wc, W_FULL, 4);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t sa = smem_u32(tsm + S::A + s * 16384), sb = smem_u32(tsm + S::B + s * MT * 128);
-            const uint32_t sz = smem_u32(tsm + S::AZ + (gi & 1) * 16384);
+          const int a = gi % NACC, s = gi % NS;
+          ok = mbar_wait(&acc_empty[a], ((gi / NACC) & 1) ^ 1, wc, W_EMPTY, 3) && mbar_wait(&a_full[s], (gi / NS) & 1, wc, W_FULL, 4) &&
+               mbar_wait(&b_full[s], (gi / NS) & 1, wc, W_FULL, 4);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t ta = tmem + S::T_A + s * 64, tz = tmem + S::T_AZ + s * 8;
+          const uint32_t sb = smem_u32(tsm + S::B + s * S::BSTAGE);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-              tc_mma(tmem + a * MT, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (half | k) ? 1u : 0u);
-              if (hz) tc_mma(tmem + 2 * MT, tc_desc(sz + k * 32), tc_desc(sb + k * 32), idesc, (g > w.g0 || half || k) ? 1u : 0u);
-            }
-            tc_commit(&ab_empty[s]);
+          for (int k = 0; k < 8; k++) {
+            const uint64_t db = tc_desc(sb + (k >> 2) * (MT * 128) + (k & 3) * 32);
+            tc_mma_ts(tmem + a * MT, ta + k * 8, db, idesc, k ? 1u : 0u);
+            if (hz) tc_mma_ts(tmem + S::T_ACCZ, tz, db, idesc, (g > w.g0 || k) ? 1u : 0u);
           }
-          if (ok) tc_commit(&acc_full[a]);
+          tc_commit(&s_empty[s]);
+          tc_commit(&acc_full[a]);
         }
       }
     }
   } else if (warp < 6) {
-    // ---------------- dequantise: thread = row of the block; 8 words -> 8 swizzled 16-byte pieces per chunk
-    const int row = (warp - 2) * 32 + lane;
-    const uint32_t rsw = (uint32_t)(row >> 3) * 1024 + (uint32_t)(row & 7) * 128, rx = (uint32_t)(row & 7);
-    uint32_t it = 0, gi = 0, ii = 0;
+    // ---------------- dequantise: thread = row of the block = TMEM lane; 16 words -> 64 packed bf16 pairs per group
+    const int quad = warp & 3, row = quad * 32 + lane;
+    const uint32_t tl = tmem + ((uint32_t)(quad * 32) << 16);
+    uint32_t gi = 0, ii = 0;
     bool ok = true;
     for (TcWalk w(P.rows, K, P.nsplit); w.valid() && ok; w.next(), ii++) {
+      if (hz) ok = mbar_wait(&sc_full[ii & 1], (ii >> 1) & 1, wc, W_FULL, 7);
       for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
-        for (int half = 0; half < 2 && ok; half++, it++) {
-          const int sr = it % kTcRaw, s = it % kTcStages;
-          ok = mbar_wait(&raw_full[sr], (it / kTcRaw) & 1, wc, W_FULL, 5) &&
-               mbar_wait(&ab_empty[s], ((it / kTcStages) & 1) ^ 1, wc, W_EMPTY, 6);
-          if (!ok) break;
-          const uint32_t raw = smem_u32(tsm + S::RAW + sr * 4096) + (uint32_t)row * 4, dst = smem_u32(tsm + S::A + s * 16384) + rsw;
-          uint32_t wv[8];
+        const int sr = gi % NRAW, s = gi % NS;
+        ok = mbar_wait(&raw_full[sr], (gi / NRAW) & 1, wc, W_FULL, 5) && mbar_wait(&s_empty[s], ((gi / NS) & 1) ^ 1, wc, W_EMPTY, 6);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t raw = smem_u32(tsm + S::RAW + sr * 8192) + (uint32_t)row * 4;
 #pragma unroll
-          for (int q8 = 0; q8 < 8; q8++) wv[q8] = lds32(raw + q8 * 512);
+        for (int c = 0; c < 2; c++) {
+          uint32_t v[32];
 #pragma unroll
-          for (int q8 = 0; q8 < 8; q8++)
-            sts128(dst + (((uint32_t)q8 ^ rx) << 4), tc_cvt_lo(wv[q8]), tc_cvt_hi(wv[q8]), tc_cvt_lo(wv[q8] >> 8), tc_cvt_hi(wv[q8] >> 8));
-          if (hz && half == 0) {
-            // the group's zero point of this row, replicated over a 64-column tile: A_z = z. The tile is shared by the
-            // group's two chunks and reused every second group: its last readers are the MMAs of chunks it-4 and it-3,
-            // so the stage of chunk it+1 (= it-3's) must be free too; then the scales must have landed
-            ok = mbar_wait(&ab_empty[(it + 1) % kTcStages], (((it + 1) / kTcStages) & 1) ^ 1, wc, W_EMPTY, 6) &&
-                 mbar_wait(&sc_full[ii & 1], (ii >> 1) & 1, wc, W_FULL, 7);
-            if (!ok) break;
-            const uint16_t z = reinterpret_cast<const uint16_t*>(tsm + S::SC + (ii & 1) * S::SC_BYTES + kTcMaxGroups * 256)[(g - w.g0) * 128 + row];
-            const uint32_t zz = (uint32_t)z | ((uint32_t)z << 16), dz = smem_u32(tsm + S::AZ + (gi & 1) * 16384) + rsw;
-#pragma unroll
-            for (int q8 = 0; q8 < 8; q8++) sts128(dz + ((uint32_t)q8 << 4), zz, zz, zz, zz);
+          for (int q8 = 0; q8 < 8; q8++) {
+            const uint32_t wv = lds32(raw + c * 4096 + q8 * 512);
+            v[4 * q8] = tc_cvt_lo(wv); v[4 * q8 + 1] = tc_cvt_hi(wv); v[4 * q8 + 2] = tc_cvt_lo(wv >> 8); v[4 * q8 + 3] = tc_cvt_hi(wv >> 8);
           }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) { mbar_arrive(&raw_empty[sr]); mbar_arrive(&ab_full[s]); }
+          tc_st32(tl + S::T_A + s * 64 + c * 32, v);
         }
+        if (hz) {
+          // the group's zero point of this row as one k16 step: A_z = z for every column
+          const uint16_t z = reinterpret_cast<const uint16_t*>(tsm + S::SC + (ii & 1) * S::SC_BYTES + kTcMaxGroups * 256)[(g - w.g0) * 128 + row];
+          tc_st8(tl + S::T_AZ + s * 8, (uint32_t)z | ((uint32_t)z << 16));
+        }
+        tc_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&raw_empty[sr]); mbar_arrive(&a_full[s]); }
       }
     }
   } else if (warp < 10) {
-    // ---------------- activations: cp.async pieces into the swizzled B stages, three chunks ahead
+    // ---------------- activations: cp.async pieces into the swizzled B stages, three groups ahead
     pdl_wait();                                                  // the activations are the previous kernel's output
     const int lt = (warp - 6) * 32 + lane;
-    constexpr int PIECES = MT * 8, PPT = (PIECES + 127) / 128, AHEAD = kTcStages - 1;
-    auto issue = [&](int chunk, int s) {
-      uint8_t* dst = tsm + S::B + s * MT * 128;
+    constexpr int PIECES = MT * 16, PPT = (PIECES + 127) / 128, AHEAD = NS - 1;
+    auto issue = [&](int g, int s) {
+      uint8_t* dst = tsm + S::B + s * S::BSTAGE;
 #pragma unroll
       for (int k = 0; k < PPT; k++) {
         const int i = lt + k * 128;
         if (i < PIECES) {
-          const int m = i >> 3, c = i & 7;
-          uint8_t* d = dst + (m >> 3) * 1024 + (m & 7) * 128 + ((c ^ (m & 7)) << 4);
-          if (m < P.M) cp_async16(d, P.x + (size_t)m * K + chunk * 64 + c * 8);
+          const int c = i & 7, m = (i >> 3) % MT, tile = i / (8 * MT);
+          uint8_t* d = dst + tile * (MT * 128) + (m >> 3) * 1024 + (m & 7) * 128 + ((c ^ (m & 7)) << 4);
+          if (m < P.M) cp_async16(d, P.x + (size_t)m * K + g * 128 + tile * 64 + c * 8);
           else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
       }
     };
-    // the chunk sequence of this CTA, walked twice: once for issuing (ahead), once for completing
+    // the group sequence of this CTA, walked twice: once for issuing (ahead), once for completing
     TcWalk wi(P.rows, K, P.nsplit);
-    int ci = wi.valid() ? 2 * wi.g0 : 0;
-    uint32_t iti = 0;
+    int gn = wi.valid() ? wi.g0 : 0;
+    uint32_t gii = 0;
     bool ok = true;
     auto issue_next = [&]() {
       if (wi.valid() && ok) {
-        const int s = iti % kTcStages;
-        ok = mbar_wait(&ab_empty[s], ((iti / kTcStages) & 1) ^ 1, wc, W_EMPTY, 8);
-        if (ok) issue(ci, s);
-        iti++;
-        if (++ci >= 2 * wi.g1) { wi.next(); ci = wi.valid() ? 2 * wi.g0 : 0; }
+        const int s = gii % NS;
+        ok = mbar_wait(&s_empty[s], ((gii / NS) & 1) ^ 1, wc, W_EMPTY, 8);
+        if (ok) issue(gn, s);
+        gii++;
+        if (++gn >= wi.g1) { wi.next(); gn = wi.valid() ? wi.g0 : 0; }
       }
       cp_async_commit();
     };
     for (int j = 0; j < AHEAD; j++) issue_next();
-    uint32_t it = 0;
+    uint32_t gi = 0;
     for (TcWalk w(P.rows, K, P.nsplit); w.valid() && ok; w.next()) {
-      for (int c = 2 * w.g0; c < 2 * w.g1 && ok; c++, it++) {
+      for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
         cp_async_wait<AHEAD - 1>();
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ab_full[it % kTcStages]);
+        if (lane == 0) mbar_arrive(&b_full[gi % NS]);
         issue_next();
       }
     }
@@ -369,24 +394,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
       ok = mbar_wait(&sc_full[b], (ii >> 1) & 1, wc, W_FULL, 9);
       const uint16_t* scs = reinterpret_cast<const uint16_t*>(tsm + S::SC + b * S::SC_BYTES);
       for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
-        const int a = gi & 1;
-        ok = mbar_wait(&acc_full[a], (gi >> 1) & 1, wc, W_FULL, 10);
+        const int a = gi % NACC;
+        ok = mbar_wait(&acc_full[a], (gi / NACC) & 1, wc, W_FULL, 10);
         if (!ok) break;
         tc_fence_after();
         const float s64 = bf2f(scs[(g - w.g0) * 128 + row]) * 64.0f;
+        constexpr int HALF = MT >= 32 ? 32 : MT;                // columns per batch of loads: one wait per batch
 #pragma unroll
-        for (int c8 = 0; c8 < MT / 8; c8++) {
-          uint32_t v[8];
-          tc_ld8(tlane + a * MT + c8 * 8, v);
+        for (int h0 = 0; h0 < MT; h0 += HALF) {
+          uint32_t v[HALF / 8][8];
+#pragma unroll
+          for (int c8 = 0; c8 < HALF / 8; c8++) tc_ld8(tlane + a * MT + h0 + c8 * 8, v[c8]);
           tc_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 8; e++) y[c8 * 8 + e] = fmaf(s64, __uint_as_float(v[e]), y[c8 * 8 + e]);
+          for (int c8 = 0; c8 < HALF / 8; c8++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) y[h0 + c8 * 8 + e] = fmaf(s64, __uint_as_float(v[c8][e]), y[h0 + c8 * 8 + e]);
         }
         if (hz && g == w.g1 - 1) {                               // the item's zero-point sums: sum_g z_g * sum_k x_k
 #pragma unroll
           for (int c8 = 0; c8 < MT / 8; c8++) {
             uint32_t v[8];
-            tc_ld8(tlane + 2 * MT + c8 * 8, v);
+            tc_ld8(tlane + S::T_ACCZ + c8 * 8, v);
             tc_ld_wait();
 #pragma unroll
             for (int e = 0; e < 8; e++) y[c8 * 8 + e] += __uint_as_float(v[e]);
@@ -423,57 +452,75 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
           for (int t = 0; t < MT; t++) y[t] += __ldcg(src + t * 128 + row);
         }
       }
-      // ---- epilogue proper: stream row `srow` of the matrix, token t -> y[t] ----
+      // ---- epilogue proper. The sums go through shared memory ([token][row], a warp touches only its own 32 rows) so
+      // that the per-token work is a compact loop (unrolled over 64 tokens it is tens of KB of straight-line code that
+      // runs once per item: one instruction-cache miss after the other). Tokens go in batches of 8 whose global loads
+      // are all issued before the first dependent store.
+      float* ys = reinterpret_cast<float*>(tsm + S::EPI);
+      __syncwarp();
+#pragma unroll
+      for (int t = 0; t < MT; t++) ys[t * 128 + row] = y[t];
+      __syncwarp();
       const int srow = w.rb * 128 + row;
       if (EPI == EPI_RESID) {
+        if (srow < P.rows)
+          for (int t0 = 0; t0 < P.M; t0 += 8) {
+            uint16_t hv[8];
 #pragma unroll
-        for (int t = 0; t < MT; t++)
-          if (srow < P.rows && t < P.M) {
-            uint16_t* hp = P.h + (size_t)t * P.out_ld + srow;
-            *hp = f2bf(bf2f(*hp) + y[t] * P.resid);
+            for (int e = 0; e < 8; e++) hv[e] = t0 + e < P.M ? P.h[(size_t)(t0 + e) * P.out_ld + srow] : (uint16_t)0;
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+              if (t0 + e < P.M) P.h[(size_t)(t0 + e) * P.out_ld + srow] = f2bf(bf2f(hv[e]) + ys[(t0 + e) * 128 + row] * P.resid);
           }
       } else if (EPI == EPI_LOGITS) {
-#pragma unroll
-        for (int t = 0; t < MT; t++)
-          if (srow < P.rows && t < P.M) P.logits[(size_t)t * P.out_ld + srow] = y[t] / P.logits_scaling;
+        if (srow < P.rows)
+#pragma unroll 4
+          for (int t = 0; t < P.M; t++) P.logits[(size_t)t * P.out_ld + srow] = ys[t * 128 + row] / P.logits_scaling;
       } else if (EPI == EPI_SWIGLU) {
-        // stream rows (2i, 2i+1) = (gate_i, up_i): neighbouring lanes
-#pragma unroll
-        for (int t = 0; t < MT; t++) {
-          const float u = __shfl_xor_sync(0xffffffffu, y[t], 1);
-          if (!(lane & 1) && srow < P.rows && t < P.M) {
-            const float gg = rbf(y[t]), uu = rbf(u);
+        // stream rows (2i, 2i+1) = (gate_i, up_i): the even row's thread writes act_i
+        if (!(lane & 1) && srow < P.rows)
+#pragma unroll 4
+          for (int t = 0; t < P.M; t++) {
+            const float gg = rbf(ys[t * 128 + row]), uu = rbf(ys[t * 128 + row + 1]);
             P.act[(size_t)t * P.out_ld + (srow >> 1)] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
           }
-        }
       } else {
         // QKV: stream rows (2p, 2p+1) of a q / k head are dims (p, p + HD/2); v rows keep their order
         const int HD = P.head_dim, HP = HD >> 1, QD = P.n_head * HD;
-        const int head = srow / HD, within = srow % HD;
+        const int head = srow / HD, within = srow % HD, i = within >> 1;
+        if (!(lane & 1) && srow < P.rows) {
+          if (head < P.n_head + P.nkv) {
+            for (int t0 = 0; t0 < P.M; t0 += 8) {
+              float2 cs[8];
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-          const float o = __shfl_xor_sync(0xffffffffu, y[t], 1);
-          if (!(lane & 1) && srow < P.rows && t < P.M) {
-            if (head < P.n_head + P.nkv) {
-              const int i = within >> 1;
-              const float x0 = rbf(y[t]), x1 = rbf(o);
-              const float2 cs = __ldg(P.rope + (size_t)t * HP + i);
-              const uint16_t y0 = f2bf(x0 * cs.x - x1 * cs.y), y1 = f2bf(x1 * cs.x + x0 * cs.y);
-              if (head < P.n_head) {
-                P.q[(size_t)t * QD + head * HD + i] = y0;
-                P.q[(size_t)t * QD + head * HD + i + HP] = y1;
-              } else {
-                uint16_t* kr = P.kc + ((size_t)(P.pos + t) * P.nkv + (head - P.n_head)) * HD;
-                kr[i] = y0;
-                kr[i + HP] = y1;
+              for (int e = 0; e < 8; e++) cs[e] = t0 + e < P.M ? __ldg(P.rope + (size_t)(t0 + e) * HP + i) : make_float2(1.f, 0.f);
+#pragma unroll
+              for (int e = 0; e < 8; e++) {
+                const int t = t0 + e;
+                if (t < P.M) {
+                  const float x0 = rbf(ys[t * 128 + row]), x1 = rbf(ys[t * 128 + row + 1]);
+                  const uint16_t y0 = f2bf(x0 * cs[e].x - x1 * cs[e].y), y1 = f2bf(x1 * cs[e].x + x0 * cs[e].y);
+                  if (head < P.n_head) {
+                    P.q[(size_t)t * QD + head * HD + i] = y0;
+                    P.q[(size_t)t * QD + head * HD + i + HP] = y1;
+                  } else {
+                    uint16_t* kr = P.kc + ((size_t)(P.pos + t) * P.nkv + (head - P.n_head)) * HD;
+                    kr[i] = y0;
+                    kr[i + HP] = y1;
+                  }
+                }
               }
-            } else {
+            }
+          } else {
+#pragma unroll 4
+            for (int t = 0; t < P.M; t++) {
               uint16_t* vr = P.vc + ((size_t)(P.pos + t) * P.nkv + (head - P.n_head - P.nkv)) * HD;
-              *reinterpret_cast<uint32_t*>(vr + within) = (uint32_t)f2bf(y[t]) | ((uint32_t)f2bf(o) << 16);
+              *reinterpret_cast<uint32_t*>(vr + within) = (uint32_t)f2bf(ys[t * 128 + row]) | ((uint32_t)f2bf(ys[t * 128 + row + 1]) << 16);
             }
           }
         }
       }
+      __syncwarp();                                              // the staging rows are rewritten by the next item
     }
   }
   tc_fence_before();
