@@ -269,13 +269,18 @@ cudaError_t launch_vattn(const fb_ctx* c, const uint16_t* q, const uint16_t* kc,
                          uint16_t* ao, int pos, int M, int natural, cudaStream_t st) {
   const fb_model_desc& d = c->d;
   const int T = pos + M;
+  // a CTA takes 64 query rows (four 16-row tiles); spans of positions are sized so that about two CTAs per SM exist
+  const int mgroups = (M * c->rgqa + 63) / 64;
+  int smax = (2 * c->sm_count) / (d.n_kv_head * mgroups);
+  if (smax < 1) smax = 1;
+  if (smax > kVSpans) smax = kVSpans;
   int S = (T + 63) / 64;
-  if (S > kVSpans) S = kVSpans;
+  if (S > smax) S = smax;
   const int span = ((T + S - 1) / S + 63) / 64 * 64;
   S = (T + span - 1) / span;
 #define FB_VATTN(HD_, R_)                                                                                               \
   if (d.head_dim == HD_ && c->rgqa == R_) {                                                                             \
-    cudaError_t e = launch_pdl(v_attn_mma<HD_, R_>, dim3(d.n_kv_head, S), dim3(128), 0, st, q, kc, vc, amask, c->vpart,  \
+    cudaError_t e = launch_pdl(v_attn_mma<HD_, R_>, dim3(d.n_kv_head, S, mgroups), dim3(128), 0, st, q, kc, vc, amask, c->vpart,  \
                                d.n_head, d.n_kv_head, pos, M, d.attn_scale, span);                                      \
     if (e != cudaSuccess) return e;                                                                                     \
     return launch_pdl(v_attn_merge<HD_, R_>, dim3(M, d.n_kv_head), dim3(256), 0, st, (const float*)c->vpart, ao, d.n_head, \
@@ -432,7 +437,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
-  if (what == 7) { c->verify_path = value != 0; return FB_OK; }
+  if (what == 7) { if (value < 0 || value > 2) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -656,7 +661,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
                strG = (size_t)pad_rows(2 * FF, D) * rec_bytes_of(D, hz), strF = (size_t)pad_rows(D, FF) * rec_bytes_of(FF, hz);
   FB_CUDA(c, launch_pdl(v_embed, dim3(M), dim3(256), 0, st, d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh,
                         D, d.vocab, d.emb_mult, &c->status->code));
-  if (c->verify_path == 0) {
+  if (c->verify_path == 2 || (c->verify_path == 0 && M > 32)) {
     // ---- tcgen05 path: natural-order activations, the matrices in the TC layout ----
     const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),
                  tF = tc_matrix_bytes(D, FF, hz);

@@ -292,7 +292,11 @@ __device__ __forceinline__ void tile_dot(const uint8_t* tile, int slice, const X
 #pragma unroll
   for (int i = 0; i < 4; i++) xb[i] = lds64(xa[i]);
   const bool odd0 = (NB % 2 == 0) ? false : (b0 & 1);           // the slice starts in the middle of a round
+#ifdef FB_DOT_UNROLL2
+#pragma unroll 2
+#else
 #pragma unroll
+#endif
   for (int bi = 0; bi < NB; bi++) {
     uint4 wn;
     uint2 xn[4];

@@ -34,6 +34,6 @@ struct fb_ctx {
   float* vsplit;                                                    // verify: split-K partial sums
   unsigned* vcount;                                                 // verify: arrivals per (row block, row quadrant)
   void* vrope;                                                      // verify: (cos, sin) per (token, rotation pair)
-  int verify_path;                                                  // 0: tcgen05 GEMMs, 1: warp-level MMA GEMMs
+  int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs, 2: tcgen05 GEMMs
   int max_fly, poll_words;
 };

@@ -118,8 +118,9 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
 
-// Tree-masked attention of all M candidate tokens on the tensor pipe. One CTA per (kv head, span of cached positions):
-// the M * R query rows that share the kv head (row = token * R + head in group) are the M dimension of the MMAs, 64
+// Tree-masked attention of all M candidate tokens on the tensor pipe. One CTA per (kv head, span of cached positions,
+// group of 64 query rows): the M * R query rows that share the kv head (row = token * R + head in group; a warp owns 16
+// of them, blockIdx.z selects the CTA's four 16-row tiles) are the M dimension of the MMAs, 64
 // positions at a time the N dimension of Q K^T and the K dimension of P V. Query m sees every cached position
 // t < pos and, among the M new slots pos..pos+M-1, those with amask[m][t - pos] != 0. Probabilities enter P V as a
 // sum of two bf16 values (p = hi + lo), which keeps their fp32 precision to ~2^-17. Every span writes, per query row,
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(128) v_attn_mma(const uint16_t* q, const uint1
   pdl_wait();
   const int t_begin = sp * span, t_end = min(T, t_begin + span);
   const int ntile = (rows + 15) / 16;
-  for (int mt0 = 0; mt0 < ntile; mt0 += 4) {
-    const int mt = mt0 + warp;
+  {
+    const int mt = (int)blockIdx.z * 4 + warp;
     const bool live = mt < ntile;
     const int r_lo = min(mt * 16 + g, rows - 1), r_hi = min(mt * 16 + g + 8, rows - 1);
     const int m_lo = r_lo / R, m_hi = r_hi / R;

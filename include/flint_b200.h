@@ -228,8 +228,9 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
  *           builds (reference: kernels/megakernel_decode.cu:15-24)
  *   what 4: bulk weight copies one CTA keeps in flight at once (1..4, default 4)
  *   what 5: 1 = consumers poll the tagged activation words directly; 0 = they wait for the producers' arrival flags first
- *   what 7: GEMMs of fb_verify: 0 = tcgen05 tensor-core kernels with accumulators in tensor memory (default),
- *           1 = the warp-level mma.sync kernels (kept as a second implementation to compare against) */
+ *   what 7: GEMMs of fb_verify: 0 = chosen by tree size (default: more than 32 tokens, where the contraction is
+ *           tensor-bound, run the tcgen05 kernels with accumulators in tensor memory; smaller trees, HBM- and
+ *           latency-bound, run the warp-level mma.sync kernels), 1 = always warp-level, 2 = always tcgen05 */
 int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
 
 #ifdef __cplusplus

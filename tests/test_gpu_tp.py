@@ -118,5 +118,6 @@ def test_tp_peer_that_never_arrives_times_out_and_ranks_recover():
     s.close()
     ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_worker_peer_missing, args=(2, port, ret), nprocs=2, join=True)
-    assert ret["code"] == 5 and ret["where"] == 5, dict(ret)      # FB_ERR_TIMEOUT in a tagged-word wait
+    # FB_ERR_TIMEOUT; the first wait to run out is the peer-word poll (5) or, behind it, a stage wait of the weight ring (2, 3, 6)
+    assert ret["code"] == 5 and ret["where"] in (2, 3, 5, 6), dict(ret)
     assert ret["token_after"] == ret["token_single"], dict(ret)

@@ -34,12 +34,16 @@ def _prefix(orc, eng, toks):
         eng.decode(t, p, want_logits=False)
 
 
+@pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("asym", [False, True])
-@pytest.mark.parametrize("M", [1, 5, 16, 26])
-def test_tiny_chain_verify_vs_oracle(M, asym):
+@pytest.mark.parametrize("M", [1, 5, 16, 26, 40])
+def test_tiny_chain_verify_vs_oracle(M, asym, path):
+    """Both GEMM implementations of the verify path (1 = warp-level mma.sync, 2 = tcgen05 with accumulators in tensor
+    memory) at every padded token count (16 / 32 / 64), symmetric and asymmetric weights."""
     cfg = ModelArgs.from_name("tiny")
     P = packing.synth_packed(cfg, 0, asym=asym)
     orc, eng = O.OracleModel(cfg, P, 128), DecodeEngine(cfg, _cuda(P), max_seq=128)
+    eng.set_option(7, path)
     _prefix(orc, eng, [3, 1, 4, 1, 5, 9, 2])
     toks = torch.randint(0, cfg.vocab_size, (M,), generator=torch.Generator().manual_seed(M)).tolist()
     ref_lg, ref_ft = orc.verify(toks, 7)
@@ -169,8 +173,9 @@ def _verify_rows_ok(lg, ref_lg, bound=0.02):
     assert _argmax_ok(lg, ref_lg)
 
 
+@pytest.mark.parametrize("path", [1, 2])
 @pytest.mark.parametrize("M", [16, 26, 64])
-def test_granite3b_shape_verify_over_1024_token_cache(M):
+def test_granite3b_shape_verify_over_1024_token_cache(M, path):
     """The benchmark's verify configuration: static trees of 16 / 26 / 64 nodes over a cache of 1024 positions (seeded
     N(0, 1) keys and values), so the attention runs over many spans of positions and the span merge is checked."""
     from flint_b200.tree import static_tree
@@ -180,6 +185,7 @@ def test_granite3b_shape_verify_over_1024_token_cache(M):
     P = {k: v.cpu() for k, v in W.items()}
     T0 = 1024
     orc, eng = O.OracleModel(cfg, P, T0 + 64), DecodeEngine(cfg, W, max_seq=T0 + 64)
+    eng.set_option(7, path)
     _prefill_random(orc, eng, cfg, T0)
     parent, depth = static_tree(M)
     amask = O.tree_mask(parent)
