@@ -96,6 +96,10 @@ transformer_configs = {
     # Tiny CPU-runnable decoder: 4 layers, d 512, 8 q / 2 kv heads, hd 64, SwiGLU 1376, vocab 4096, tied.
     "tiny": dict(block_size=256, vocab_size=4096, n_layer=4, n_head=8, n_local_heads=2, dim=512,
                  intermediate_size=1376, rope_base=10000),
+    # Small decoder with heads of 80 whose 2-rank split owns 320 attention columns = 2.5 int4 groups: the same O-window
+    # situation as the 3B-class model over 8 ranks, testable on 2 GPUs.
+    "tiny-window": dict(block_size=256, vocab_size=512, n_layer=2, n_head=8, n_local_heads=2, dim=640,
+                        intermediate_size=1024, rope_base=10000),
     # 3B-class Granite-shaped dense decoder (the headline single-GPU config).
     "granite-3b-class": dict(block_size=4096, vocab_size=49160, n_layer=40, n_head=32, n_local_heads=8, dim=2560,
                              intermediate_size=8192, rope_base=10000),

@@ -31,6 +31,8 @@ const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(512, 512, 1408, 64, 4),       // tiny test decoder
     FB_DECODE_ENTRY(512, 512, 1536, 64, 4),       // tiny decoder whose FFN splits into whole groups over 2 ranks
     FB_DECODE_ENTRY(512, 256, 768, 64, 4),        // ... and its 2-rank slice
+    FB_DECODE_ENTRY(640, 640, 1024, 80, 4),       // small decoder with heads of 80 ...
+    FB_DECODE_ENTRY(640, 384, 512, 80, 4),        // ... whose 2-rank slice reads a widened O window (320 columns in 3 groups)
     FB_DECODE_ENTRY(2560, 2560, 8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
 #ifndef FB_KERNELS_MINIMAL                        // (a build for kernel experiments keeps only the shapes above)
     FB_DECODE_ENTRY(2560, 2560, 8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
@@ -257,6 +259,38 @@ cudaError_t launch_vtc(VtcParams& p, int mt, int sms, cudaStream_t st) {
   return cudaErrorInvalidValue;
 }
 
+template <int MT, bool HZ>
+cudaError_t launch_vchain_hz(VchainParams& p, int sms, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(v_chain_tc<MT, HZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, VtcSmem<MT, HZ>::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  for (int i = 0; i < p.nph; i++) {
+    VtcPhase& f = p.ph[i];
+    f.nsplit = tc_splits(f.rows, f.K, sms);
+    const int items = ((f.rows + kTcRowBlock - 1) / kTcRowBlock) * f.nsplit;
+    if (f.K % 128 || (f.K / 128 + f.nsplit - 1) / f.nsplit > kTcMaxGroups || (f.nsplit > 1 && items > kTcMaxItems) ||
+        (f.rows + kTcRowBlock - 1) / kTcRowBlock * 4 > 4096)
+      return cudaErrorInvalidValue;
+  }
+  void* args[] = {&p};
+  // every CTA must be resident: the loaders of a phase wait for the epilogue warps of the whole grid
+  return cudaLaunchCooperativeKernel((const void*)v_chain_tc<MT, HZ>, dim3(sms), dim3(kTcThreads), args,
+                                     (size_t)VtcSmem<MT, HZ>::TOTAL, st);
+}
+cudaError_t launch_vchain(VchainParams& p, int mt, bool hz, int sms, cudaStream_t st) {
+  switch (mt) {
+    case 16: return hz ? launch_vchain_hz<16, true>(p, sms, st) : launch_vchain_hz<16, false>(p, sms, st);
+    case 32: return hz ? launch_vchain_hz<32, true>(p, sms, st) : launch_vchain_hz<32, false>(p, sms, st);
+    case 64: return hz ? launch_vchain_hz<64, true>(p, sms, st) : launch_vchain_hz<64, false>(p, sms, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_vnorm(const uint16_t* h, const uint16_t* w, uint16_t* xn_t, uint16_t* xn_nat, int D, int M, float eps,
                          cudaStream_t st) {
   if (D % 16 || D > 8 * 256 * 2) return cudaErrorInvalidValue;
@@ -394,6 +428,8 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   A(dmalloc(&c->vcount, 4096 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->vcount, 0, 4096 * 4));
   A(cudaMalloc(&c->vrope, (size_t)64 * (d.head_dim / 2) * 8));
+  A(dmalloc(&c->vssq, (size_t)2 * 256 * 64 * 4));
+  A(dmalloc(&c->vgbar, (size_t)(d.n_layer + 2) * 4 * 4));
   A(dmalloc(&c->flags, 3 * 256 * 4));
   if (e == cudaSuccess) A(cudaMemset(c->flags, 0, 3 * 256 * 4));
   if (c->sm_count > 256) e = cudaErrorInvalidValue;
@@ -425,7 +461,7 @@ int fb_ctx_destroy(fb_ctx* c) {
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf,
                   c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->flags,
                   c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox,
-                  c->t_qkv, c->t_o, c->t_gu, c->t_d, c->t_lm, c->vsplit, c->vcount, c->vrope};
+                  c->t_qkv, c->t_o, c->t_gu, c->t_d, c->t_lm, c->vsplit, c->vcount, c->vrope, c->vssq, c->vgbar};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -437,7 +473,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
-  if (what == 7) { if (value < 0 || value > 2) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
+  if (what == 7) { if (value < 0 || value > 3) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -661,6 +697,66 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
                strG = (size_t)pad_rows(2 * FF, D) * rec_bytes_of(D, hz), strF = (size_t)pad_rows(D, FF) * rec_bytes_of(FF, hz);
   FB_CUDA(c, launch_pdl(v_embed, dim3(M), dim3(256), 0, st, d_tokens, (const uint16_t*)c->embed, (const uint16_t*)d_h, c->vh,
                         D, d.vocab, d.emb_mult, &c->status->code));
+  if (c->verify_path == 3) {
+    // ---- tcgen05 GEMM chains: per layer one launch covers O -> gate/up -> down -> the next layer's QKV (or the LM head)
+    const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),
+                 tF = tc_matrix_bytes(D, FF, hz);
+    const int L = d.n_layer, nssq = (D + kTcRowBlock - 1) / kTcRowBlock * 4;
+    float *ssqA = c->vssq, *ssqB = c->vssq + 256 * 64;
+    if (nssq > 256) return FB_ERR_SHAPE;
+    FB_CUDA(c, cudaMemsetAsync(c->vgbar, 0, (size_t)(L + 2) * 16, st));
+    FB_CUDA(c, launch_pdl(v_rope_table, dim3(M), dim3(64), 0, st, d_depth, (const float*)c->invf, (int)pos, HD / 2, (float2*)c->vrope));
+    VchainParams t;
+    memset(&t, 0, sizeof(t));
+    t.M = M; t.part = c->vsplit; t.counters = c->vcount; t.status = c->status; t.spin_limit = c->spin_limit;
+    t.rope = (const float2*)c->vrope; t.n_head = d.n_head; t.nkv = d.n_kv_head; t.pos = pos; t.head_dim = HD; t.dim = D;
+    t.resid = d.resid_mult; t.logits_scaling = d.logits_scaling; t.eps = d.rms_eps;
+    auto kcl = [&](int l) { return (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD; };
+    auto vcl = [&](int l) { return (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD; };
+    auto qkv_phase = [&](int l, bool normed) {
+      VtcPhase f;
+      memset(&f, 0, sizeof(f));
+      f.w = c->t_qkv + l * tQ; f.rows = QKV; f.K = D; f.epi = EPI_QKV; f.q = c->vq; f.kc = kcl(l); f.vc = vcl(l);
+      if (normed) { f.x = c->vh; f.norm_w = (const uint16_t*)c->n1 + (size_t)l * D; f.ssq_in = ssqB; f.n_ssq = nssq; }
+      else f.x = c->vxn;
+      return f;
+    };
+    // layer 0's QKV reads the embeddings through the stand-alone norm kernel
+    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1, nullptr, c->vxn, D, M, d.rms_eps, st));
+    t.nph = 1; t.ph[0] = qkv_phase(0, false); t.gbar = c->vgbar;
+    FB_CUDA(c, launch_vchain(t, MT, hz, c->sm_count, st));
+    for (int l = 0; l < L; l++) {
+      FB_CUDA(c, launch_vattn(c, c->vq, kcl(l), vcl(l), d_amask, c->vao, pos, M, 1, st));
+      VtcPhase f;
+      memset(&f, 0, sizeof(f));
+      f.w = c->t_o + l * tO; f.x = c->vao; f.rows = D; f.K = QD; f.epi = EPI_RESID; f.h = c->vh; f.out_ld = D; f.ssq_out = ssqA;
+      t.ph[0] = f;
+      memset(&f, 0, sizeof(f));
+      f.w = c->t_gu + l * tG; f.x = c->vh; f.norm_w = (const uint16_t*)c->n2 + (size_t)l * D; f.ssq_in = ssqA; f.n_ssq = nssq;
+      f.rows = 2 * FF; f.K = D; f.epi = EPI_SWIGLU; f.act = c->vact; f.out_ld = FF;
+      t.ph[1] = f;
+      memset(&f, 0, sizeof(f));
+      f.w = c->t_d + l * tF; f.x = c->vact; f.rows = D; f.K = FF; f.epi = EPI_RESID; f.h = c->vh; f.out_ld = D; f.ssq_out = ssqB;
+      t.ph[2] = f;
+      t.nph = 3;
+      if (l + 1 < L) {
+        t.ph[3] = qkv_phase(l + 1, true);
+        t.nph = 4;
+      } else if (d_logits) {
+        memset(&f, 0, sizeof(f));
+        f.w = c->t_lm; f.x = c->vh; f.norm_w = (const uint16_t*)c->nf; f.ssq_in = ssqB; f.n_ssq = nssq; f.xn_out = (uint16_t*)d_feat;
+        f.rows = d.vocab; f.K = D; f.epi = EPI_LOGITS; f.logits = d_logits; f.out_ld = d.vocab;
+        t.ph[3] = f;
+        t.nph = 4;
+      }
+      t.gbar = c->vgbar + 4 * (l + 1);
+      FB_CUDA(c, launch_vchain(t, MT, hz, c->sm_count, st));
+    }
+    if (!d_logits && d_feat)
+      FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, nullptr, (uint16_t*)d_feat, D, M, d.rms_eps, st));
+    FB_CUDA(c, cudaGetLastError());
+    return FB_OK;
+  }
   if (c->verify_path == 2 || (c->verify_path == 0 && M > 32)) {
     // ---- tcgen05 path: natural-order activations, the matrices in the TC layout ----
     const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),

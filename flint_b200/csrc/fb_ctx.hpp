@@ -33,7 +33,9 @@ struct fb_ctx {
   uint8_t *t_qkv, *t_o, *t_gu, *t_d, *t_lm;                          // verify: the matrices in the tensor-core (TC) layout
   float* vsplit;                                                    // verify: split-K partial sums
   unsigned* vcount;                                                 // verify: arrivals per (row block, row quadrant)
+  float* vssq;                                                      // verify chain: partial sums of squares, 2 x [256][64]
+  unsigned* vgbar;                                                  // verify chain: grid arrival counters per launch and phase
   void* vrope;                                                      // verify: (cos, sin) per (token, rotation pair)
-  int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs, 2: tcgen05 GEMMs
+  int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs, 2: tcgen05 GEMMs, 3: tcgen05 GEMM chains
   int max_fly, poll_words;
 };

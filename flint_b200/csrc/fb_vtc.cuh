@@ -171,7 +171,7 @@ struct VtcSmem {
   static constexpr int SC_BYTES = kTcMaxGroups * 256 * (HZ ? 2 : 1);   // scales, then zeros
   static constexpr int EPI = SC + 2 * SC_BYTES;                    // the item's sums, fp32 [MT][128 rows]
   static constexpr int BAR = EPI + MT * 512;
-  static constexpr int TOTAL = BAR + 1024 + 1024;                  // barriers + slack to align the base to 1024 bytes
+  static constexpr int TOTAL = BAR + 2048 + 1024;                  // barriers, 1/rms per phase and token + slack to align the base
   static_assert(TOTAL <= 227 * 1024, "verify GEMM shared memory");
   // tensor memory columns: group accumulators, zero-point accumulator, A stages (64 columns = 128 bf16 per row), A_z
   // (8 columns = one k16 step of the row's zero point, the same for every step of the group)
@@ -521,6 +521,436 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_gemm_tc(const VtcParams P) {
         }
       }
       __syncwarp();                                              // the staging rows are rewritten by the next item
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCOLS));
+}
+
+
+// ------------------------------------------------------------------------------------------------ GEMM chain
+// Up to four of the GEMMs above in ONE launch (O projection -> gate/up -> down -> next layer's QKV, or the LM head at
+// the end): the warp roles and their rings simply keep running from one GEMM ("phase") into the next, so the weights of
+// the next phase are already streaming — and partly dequantised in tensor memory — while the current one drains, and the
+// per-launch ramp of a short pipeline is paid once per four GEMMs. Only the activation loaders need the other CTAs: they
+// wait (bounded) on a grid-wide arrival counter that every epilogue warp bumps when its last item of the previous phase is
+// in global memory. RMSNorm does not get a phase of its own: the epilogue that updates the residual rows also leaves, per
+// 32-row warp, the sums of squares of the rows it wrote; the next phase's loaders reduce them in a fixed order to 1/rms per
+// token and normalise the activation tiles in place, in shared memory, after their cp.async has landed:
+// bf16((float(h) * r) * float(w)), the rounding of the reference's rmsnorm (reference: kernels/verify_mega.cu:78-104).
+struct VtcPhase {
+  const uint8_t* w;          // TC layout
+  const uint16_t* x;         // bf16 [M][K]: activations, or (norm_w set) the residual stream to be normalised on the fly
+  const uint16_t* norm_w;    // bf16 [K] RMSNorm weights or nullptr
+  const float* ssq_in;       // [n_ssq][64]: partial sums of squares per token, written by the previous residual phase
+  float* ssq_out;            // RESID: [row blocks * 4][64] or nullptr
+  uint16_t* xn_out;          // norm_w set: CTA 0 also writes the normalised rows here (the feature output) or nullptr
+  uint16_t* h;               // RESID
+  uint16_t* q;               // QKV
+  uint16_t *kc, *vc;         // QKV
+  uint16_t* act;             // SWIGLU
+  float* logits;             // LOGITS
+  int rows, K, nsplit, epi, n_ssq, out_ld;
+};
+struct VchainParams {
+  VtcPhase ph[4];
+  int nph, M;
+  float* part;
+  unsigned* counters;
+  unsigned* gbar;            // [4] arrivals of the epilogue warps per phase, zero at launch
+  DevStatus* status;
+  unsigned spin_limit;
+  const float2* rope;
+  int n_head, nkv, pos, head_dim, dim;
+  float resid, logits_scaling, eps;
+};
+
+template <int MT, bool HZ>
+__global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P) {
+  using S = VtcSmem<MT, HZ>;
+  constexpr int NRAW = S::NRAW, NS = kTcStages, NACC = S::NACC;
+  extern __shared__ __align__(1024) uint8_t tsm_raw[];
+  uint8_t* tsm = tsm_raw + ((1024u - (smem_u32(tsm_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tsm + S::BAR);
+  uint64_t *raw_full = bars, *raw_empty = bars + NRAW, *a_full = bars + 2 * NRAW, *b_full = a_full + NS, *s_empty = b_full + NS,
+           *acc_full = s_empty + NS, *acc_empty = acc_full + NACC, *sc_full = acc_empty + NACC, *sc_empty = sc_full + 2;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sc_empty + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  float* s_rinv = reinterpret_cast<float*>(tsm + S::BAR + 1024);    // [4 phases][64] 1/rms per token
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr bool hz = HZ;
+  if (tid == 0) {
+    for (int i = 0; i < NRAW; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }
+    for (int i = 0; i < NS; i++) { mbar_init(&a_full[i], 4); mbar_init(&b_full[i], 4); mbar_init(&s_empty[i], 1); }
+    for (int i = 0; i < NACC; i++) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 4); }
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  constexpr int TCOLS = 512;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(TCOLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  WaitCtl wc{P.status, s_abort, P.spin_limit};
+  const unsigned arrivals = 4u * gridDim.x;                           // epilogue warps of the whole grid
+
+  if (warp == 0) {
+    // ---------------- producer: runs ahead through the phases, bounded only by the raw ring
+    if (lane == 0) {
+      uint32_t gi = 0, ii = 0;
+      bool ok = true;
+      for (int ph = 0; ph < P.nph && ok; ph++) {
+        const VtcPhase& F = P.ph[ph];
+        const int K = F.K, G = K / 128;
+        const size_t blk_bytes = tc_block_bytes(K, hz);
+        for (TcWalk w(F.rows, K, F.nsplit); w.valid() && ok; w.next(), ii++) {
+          const uint8_t* blk = F.w + (size_t)w.rb * blk_bytes;
+          const int b = ii & 1, ng = w.g1 - w.g0;
+          ok = mbar_wait(&sc_empty[b], ((ii >> 1) & 1) ^ 1, wc, W_EMPTY, 1);
+          if (!ok) break;
+          mbar_expect_tx(&sc_full[b], (uint32_t)ng * 256 * (hz ? 2 : 1));
+          bulk_g2s(tsm + S::SC + b * S::SC_BYTES, blk + (size_t)(K / 64) * 4096 + (size_t)w.g0 * 256, ng * 256, &sc_full[b]);
+          if (hz)
+            bulk_g2s(tsm + S::SC + b * S::SC_BYTES + kTcMaxGroups * 256, blk + (size_t)(K / 64) * 4096 + (size_t)(G + w.g0) * 256,
+                     ng * 256, &sc_full[b]);
+          for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+            const int s = gi % NRAW;
+            ok = mbar_wait(&raw_empty[s], ((gi / NRAW) & 1) ^ 1, wc, W_EMPTY, 2);
+            if (!ok) break;
+            mbar_expect_tx(&raw_full[s], 8192);
+            bulk_g2s(tsm + S::RAW + s * 8192, blk + (size_t)g * 8192, 8192, &raw_full[s]);
+          }
+        }
+      }
+      if (*s_abort) {                                            // after a failure: wait (bounded) for the copies in flight
+        for (int k = 0; k < NRAW && k < (int)gi; k++) {
+          const uint32_t j = gi - 1 - k;
+          for (unsigned i = 0; i < wc.limit; i++) {
+            if (mbar_try(&raw_full[j % NRAW], (j / NRAW) & 1)) break;
+            if ((i & 1023) == 1023) __nanosleep(64);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MT >> 3) << 17) | ((128u >> 4) << 24);
+      uint32_t gi = 0;
+      bool ok = true;
+      for (int ph = 0; ph < P.nph && ok; ph++) {
+        const VtcPhase& F = P.ph[ph];
+        for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next()) {
+          for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+            const int a = gi % NACC, s = gi % NS;
+            ok = mbar_wait(&acc_empty[a], ((gi / NACC) & 1) ^ 1, wc, W_EMPTY, 3) && mbar_wait(&a_full[s], (gi / NS) & 1, wc, W_FULL, 4) &&
+                 mbar_wait(&b_full[s], (gi / NS) & 1, wc, W_FULL, 4);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t ta = tmem + S::T_A + s * 64, tz = tmem + S::T_AZ + s * 8;
+            const uint32_t sb = smem_u32(tsm + S::B + s * S::BSTAGE);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+              const uint64_t db = tc_desc(sb + (k >> 2) * (MT * 128) + (k & 3) * 32);
+              tc_mma_ts(tmem + a * MT, ta + k * 8, db, idesc, k ? 1u : 0u);
+              if (hz) tc_mma_ts(tmem + S::T_ACCZ, tz, db, idesc, (g > w.g0 || k) ? 1u : 0u);
+            }
+            tc_commit(&s_empty[s]);
+            tc_commit(&acc_full[a]);
+          }
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- dequantise into tensor memory
+    const int quad = warp & 3, row = quad * 32 + lane;
+    const uint32_t tl = tmem + ((uint32_t)(quad * 32) << 16);
+    uint32_t gi = 0, ii = 0;
+    bool ok = true;
+    for (int ph = 0; ph < P.nph && ok; ph++) {
+      const VtcPhase& F = P.ph[ph];
+      for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next(), ii++) {
+        if (hz) ok = mbar_wait(&sc_full[ii & 1], (ii >> 1) & 1, wc, W_FULL, 7);
+        for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+          const int sr = gi % NRAW, s = gi % NS;
+          ok = mbar_wait(&raw_full[sr], (gi / NRAW) & 1, wc, W_FULL, 5) && mbar_wait(&s_empty[s], ((gi / NS) & 1) ^ 1, wc, W_EMPTY, 6);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t raw = smem_u32(tsm + S::RAW + sr * 8192) + (uint32_t)row * 4;
+#pragma unroll
+          for (int c = 0; c < 2; c++) {
+            uint32_t v[32];
+#pragma unroll
+            for (int q8 = 0; q8 < 8; q8++) {
+              const uint32_t wv = lds32(raw + c * 4096 + q8 * 512);
+              v[4 * q8] = tc_cvt_lo(wv); v[4 * q8 + 1] = tc_cvt_hi(wv); v[4 * q8 + 2] = tc_cvt_lo(wv >> 8); v[4 * q8 + 3] = tc_cvt_hi(wv >> 8);
+            }
+            tc_st32(tl + S::T_A + s * 64 + c * 32, v);
+          }
+          if (hz) {
+            const uint16_t z = reinterpret_cast<const uint16_t*>(tsm + S::SC + (ii & 1) * S::SC_BYTES + kTcMaxGroups * 256)[(g - w.g0) * 128 + row];
+            tc_st8(tl + S::T_AZ + s * 8, (uint32_t)z | ((uint32_t)z << 16));
+          }
+          tc_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(&raw_empty[sr]); mbar_arrive(&a_full[s]); }
+        }
+      }
+    }
+  } else if (warp < 10) {
+    // ---------------- activations, phase by phase. A phase's activations exist only once every epilogue warp of the grid
+    // has finished the previous phase, so the cp.async pipeline (three groups ahead) restarts at every phase boundary:
+    // wait for the grid-wide arrival counter (bounded), prepare 1/rms, prime, then stream.
+    const int lt = (warp - 6) * 32 + lane;
+    constexpr int PIECES = MT * 16, PPT = (PIECES + 127) / 128, AHEAD = NS - 1;
+    bool ok = true;
+    uint32_t gi = 0;                                             // groups of this CTA so far, all phases (stage = gi % NS)
+    for (int ph = 0; ph < P.nph && ok; ph++) {
+      const VtcPhase& F = P.ph[ph];
+      if (ph > 0) {                                              // every epilogue warp of the grid has finished phase ph-1
+        if (lane == 0) {
+          bool seen = false;
+          for (unsigned i = 0; i < wc.limit; i++) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.gbar + (ph - 1)) : "memory");
+            if (v >= arrivals) { seen = true; break; }
+            if ((i & 15) == 15 && (*wc.s_abort || ld_volatile_s32(&wc.st->abort))) { *wc.s_abort = 1; break; }
+          }
+          if (!seen && *wc.s_abort == 0) report_fail(wc, W_FLAG, ph, (int)arrivals, -5);
+        }
+        __syncwarp();
+        if (*wc.s_abort) { ok = false; break; }
+      }
+      float* rinv = s_rinv + ph * 64;
+      if (F.norm_w) {                                            // 1/rms per token from the partial sums, in a fixed order
+        for (int m = lane; m < P.M; m += 32) {                   // (each loader warp writes the same values)
+          float ss = 0.f;
+          for (int i = 0; i < F.n_ssq; i++) ss += __ldcg(F.ssq_in + (size_t)i * 64 + m);
+          rinv[m] = 1.0f / sqrtf(ss / (float)P.dim + P.eps);
+        }
+        __syncwarp();
+      }
+      TcWalk wi(F.rows, F.K, F.nsplit);                          // issue-side cursor of this phase
+      int gn = wi.valid() ? wi.g0 : 0;
+      uint32_t gii = gi;
+      auto issue_next = [&]() {
+        if (ok && wi.valid()) {
+          const int s = gii % NS;
+          ok = mbar_wait(&s_empty[s], ((gii / NS) & 1) ^ 1, wc, W_EMPTY, 8);
+          if (ok) {
+            uint8_t* dst = tsm + S::B + s * S::BSTAGE;
+#pragma unroll
+            for (int k = 0; k < PPT; k++) {
+              const int i = lt + k * 128;
+              if (i < PIECES) {
+                const int c = i & 7, m = (i >> 3) % MT, tile = i / (8 * MT);
+                uint8_t* d = dst + tile * (MT * 128) + (m >> 3) * 1024 + (m & 7) * 128 + ((c ^ (m & 7)) << 4);
+                if (m < P.M) cp_async16(d, F.x + (size_t)m * F.K + gn * 128 + tile * 64 + c * 8);
+                else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+              }
+            }
+          }
+          gii++;
+          if (++gn >= wi.g1) { wi.next(); gn = wi.valid() ? wi.g0 : 0; }
+        }
+        cp_async_commit();
+      };
+      for (int j = 0; j < AHEAD; j++) issue_next();
+      bool first_item = true;
+      for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next(), first_item = false) {
+        for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+          cp_async_wait<AHEAD - 1>();
+          if (F.norm_w) {
+            // normalise this thread's own pieces in place: bf16((float(h) * r) * float(w))
+            uint8_t* dst = tsm + S::B + (gi % NS) * S::BSTAGE;
+#pragma unroll
+            for (int k = 0; k < PPT; k++) {
+              const int i = lt + k * 128;
+              if (i < PIECES) {
+                const int c = i & 7, m = (i >> 3) % MT, tile = i / (8 * MT);
+                if (m < P.M) {
+                  uint4* d = reinterpret_cast<uint4*>(dst + tile * (MT * 128) + (m >> 3) * 1024 + (m & 7) * 128 + ((c ^ (m & 7)) << 4));
+                  const int col = g * 128 + tile * 64 + c * 8;
+                  const uint4 hv = *d, wv = __ldg(reinterpret_cast<const uint4*>(F.norm_w + col));
+                  const float r = rinv[m];
+                  const uint32_t hh[4] = {hv.x, hv.y, hv.z, hv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                  uint32_t o[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++)
+                    o[e] = (uint32_t)f2bf(bflo(hh[e]) * r * bflo(ww[e])) | ((uint32_t)f2bf(bfhi(hh[e]) * r * bfhi(ww[e])) << 16);
+                  const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+                  *d = ov;
+                  if (F.xn_out && blockIdx.x == 0 && first_item) *reinterpret_cast<uint4*>(F.xn_out + (size_t)m * F.K + col) = ov;
+                }
+              }
+            }
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&b_full[gi % NS]);
+          issue_next();
+        }
+      }
+      cp_async_wait<0>();
+    }
+  } else {
+    // ---------------- epilogue
+    const int quad = warp & 3, row = quad * 32 + lane;
+    const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
+    uint32_t gi = 0, ii = 0;
+    bool ok = true;
+    for (int ph = 0; ph < P.nph && ok; ph++) {
+      const VtcPhase& F = P.ph[ph];
+      for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next(), ii++) {
+        float y[MT];
+#pragma unroll
+        for (int t = 0; t < MT; t++) y[t] = 0.f;
+        const int b = ii & 1;
+        ok = mbar_wait(&sc_full[b], (ii >> 1) & 1, wc, W_FULL, 9);
+        const uint16_t* scs = reinterpret_cast<const uint16_t*>(tsm + S::SC + b * S::SC_BYTES);
+        for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
+          const int a = gi % NACC;
+          ok = mbar_wait(&acc_full[a], (gi / NACC) & 1, wc, W_FULL, 10);
+          if (!ok) break;
+          tc_fence_after();
+          const float s64 = bf2f(scs[(g - w.g0) * 128 + row]) * 64.0f;
+          constexpr int HALF = MT >= 32 ? 32 : MT;
+#pragma unroll
+          for (int h0 = 0; h0 < MT; h0 += HALF) {
+            uint32_t v[HALF / 8][8];
+#pragma unroll
+            for (int c8 = 0; c8 < HALF / 8; c8++) tc_ld8(tlane + a * MT + h0 + c8 * 8, v[c8]);
+            tc_ld_wait();
+#pragma unroll
+            for (int c8 = 0; c8 < HALF / 8; c8++)
+#pragma unroll
+              for (int e = 0; e < 8; e++) y[h0 + c8 * 8 + e] = fmaf(s64, __uint_as_float(v[c8][e]), y[h0 + c8 * 8 + e]);
+          }
+          if (hz && g == w.g1 - 1) {
+#pragma unroll
+            for (int c8 = 0; c8 < MT / 8; c8++) {
+              uint32_t v[8];
+              tc_ld8(tlane + S::T_ACCZ + c8 * 8, v);
+              tc_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 8; e++) y[c8 * 8 + e] += __uint_as_float(v[e]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[a]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sc_empty[b]);
+        if (!ok) break;
+        if (F.nsplit > 1) {
+          float* mine = P.part + (size_t)w.item * MT * 128;
+#pragma unroll
+          for (int t = 0; t < MT; t++) mine[t * 128 + row] = y[t];
+          __threadfence();
+          __syncwarp();
+          unsigned old = 0;
+          if (lane == 0) {
+            old = atomicAdd(P.counters + w.rb * 4 + quad, 1u);
+            if (old == (unsigned)F.nsplit - 1u) P.counters[w.rb * 4 + quad] = 0u;
+          }
+          old = __shfl_sync(0xffffffffu, old, 0);
+          if (old != (unsigned)F.nsplit - 1u) continue;
+          __threadfence();
+#pragma unroll
+          for (int t = 0; t < MT; t++) y[t] = 0.f;
+          for (int sp = 0; sp < F.nsplit; sp++) {
+            const float* src = P.part + (size_t)(w.rb * F.nsplit + sp) * MT * 128;
+#pragma unroll
+            for (int t = 0; t < MT; t++) y[t] += __ldcg(src + t * 128 + row);
+          }
+        }
+        float* ys = reinterpret_cast<float*>(tsm + S::EPI);
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < MT; t++) ys[t * 128 + row] = y[t];
+        __syncwarp();
+        const int srow = w.rb * 128 + row;
+        const bool live = srow < F.rows;
+        if (F.epi == EPI_RESID) {
+          for (int t0 = 0; t0 < P.M; t0 += 8) {
+            uint16_t hv[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) hv[e] = (live && t0 + e < P.M) ? F.h[(size_t)(t0 + e) * F.out_ld + srow] : (uint16_t)0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+              const int t = t0 + e;                               // warp-uniform
+              if (t < P.M) {
+                const float hn = live ? rbf(bf2f(hv[e]) + ys[t * 128 + row] * P.resid) : 0.f;
+                if (live) F.h[(size_t)t * F.out_ld + srow] = f2bf(hn);
+                if (F.ssq_out) {                                  // the 32 rows' share of sum(h^2) of token t
+                  float sq = hn * hn;
+#pragma unroll
+                  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                  if (lane == 0) F.ssq_out[(size_t)(w.rb * 4 + quad) * 64 + t] = sq;
+                }
+              }
+            }
+          }
+        } else if (F.epi == EPI_LOGITS) {
+          if (live)
+#pragma unroll 4
+            for (int t = 0; t < P.M; t++) F.logits[(size_t)t * F.out_ld + srow] = ys[t * 128 + row] / P.logits_scaling;
+        } else if (F.epi == EPI_SWIGLU) {
+          if (!(lane & 1) && live)
+#pragma unroll 4
+            for (int t = 0; t < P.M; t++) {
+              const float gg = rbf(ys[t * 128 + row]), uu = rbf(ys[t * 128 + row + 1]);
+              F.act[(size_t)t * F.out_ld + (srow >> 1)] = f2bf((gg / (1.0f + __expf(-gg))) * uu);
+            }
+        } else {
+          const int HD = P.head_dim, HP = HD >> 1, QD = P.n_head * HD;
+          const int head = srow / HD, within = srow % HD, i = within >> 1;
+          if (!(lane & 1) && live) {
+            if (head < P.n_head + P.nkv) {
+              for (int t0 = 0; t0 < P.M; t0 += 8) {
+                float2 cs[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) cs[e] = t0 + e < P.M ? __ldg(P.rope + (size_t)(t0 + e) * HP + i) : make_float2(1.f, 0.f);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                  const int t = t0 + e;
+                  if (t < P.M) {
+                    const float x0 = rbf(ys[t * 128 + row]), x1 = rbf(ys[t * 128 + row + 1]);
+                    const uint16_t y0 = f2bf(x0 * cs[e].x - x1 * cs[e].y), y1 = f2bf(x1 * cs[e].x + x0 * cs[e].y);
+                    if (head < P.n_head) {
+                      F.q[(size_t)t * QD + head * HD + i] = y0;
+                      F.q[(size_t)t * QD + head * HD + i + HP] = y1;
+                    } else {
+                      uint16_t* kr = F.kc + ((size_t)(P.pos + t) * P.nkv + (head - P.n_head)) * HD;
+                      kr[i] = y0;
+                      kr[i + HP] = y1;
+                    }
+                  }
+                }
+              }
+            } else {
+#pragma unroll 4
+              for (int t = 0; t < P.M; t++) {
+                uint16_t* vr = F.vc + ((size_t)(P.pos + t) * P.nkv + (head - P.n_head - P.nkv)) * HD;
+                *reinterpret_cast<uint32_t*>(vr + within) = (uint32_t)f2bf(ys[t * 128 + row]) | ((uint32_t)f2bf(ys[t * 128 + row + 1]) << 16);
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
+      // this warp's results of the phase are in global memory: tell the grid (the loaders of the next phase wait for it)
+      __threadfence();
+      __syncwarp();
+      if (lane == 0 && ph + 1 < P.nph) atomicAdd(P.gbar + ph, 1u);
     }
   }
   tc_fence_before();

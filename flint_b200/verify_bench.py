@@ -24,10 +24,12 @@ def main():
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--path", type=int, default=0, help="GEMM implementation (fb_set_option 7): 0 by tree size, 1 warp-level, 2 tcgen05, 3 tcgen05 chains")
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
     W = packing.synth_packed(cfg, 0, device="cuda")
     eng = DecodeEngine(cfg, W, max_seq=a.prompt_len + 128)
+    eng.set_option(7, a.path)
     eng.kc[:, :a.prompt_len].normal_()
     eng.vc[:, :a.prompt_len].normal_()
     bt = cfg.bytes_per_token(a.prompt_len)

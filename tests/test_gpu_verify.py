@@ -34,7 +34,7 @@ def _prefix(orc, eng, toks):
         eng.decode(t, p, want_logits=False)
 
 
-@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("path", [1, 2, 3])
 @pytest.mark.parametrize("asym", [False, True])
 @pytest.mark.parametrize("M", [1, 5, 16, 26, 40])
 def test_tiny_chain_verify_vs_oracle(M, asym, path):
@@ -173,7 +173,7 @@ def _verify_rows_ok(lg, ref_lg, bound=0.02):
     assert _argmax_ok(lg, ref_lg)
 
 
-@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("path", [1, 2, 3])
 @pytest.mark.parametrize("M", [16, 26, 64])
 def test_granite3b_shape_verify_over_1024_token_cache(M, path):
     """The benchmark's verify configuration: static trees of 16 / 26 / 64 nodes over a cache of 1024 positions (seeded

@@ -70,3 +70,27 @@ def test_shard_rejects_split_groups():
     cfg = ModelArgs.from_name("tiny")                 # FFN 1408 = 11 groups: no even split
     with pytest.raises(ValueError):
         shard_packed(packing.synth_packed(cfg, 0), cfg, 0, 2)
+
+
+def test_o_window_widens_to_whole_groups_and_partials_add_up():
+    """A rank whose attention width is not a multiple of the int4 group (320 columns: the 3B-class model over 8 ranks, or
+    the small `tiny-window` model over 2) reads its columns widened to the enclosing groups and feeds zeros for the
+    neighbour's: the ranks' partial sums still add up to the full product, with the original weights."""
+    from flint_b200.tp import can_shard, max_tp, o_window
+    big = ModelArgs.from_name("granite-3b-class")
+    assert max_tp(big, 8) == 8 and [o_window(big, r, 8) for r in (0, 1, 7)] == [(0, 384, 0), (256, 640, 64), (2176, 2560, 64)]
+    assert all(o_window(big, r, 4) == (640 * r, 640 * r + 640, 0) for r in range(4))
+    cfg = ModelArgs.from_name("tiny-window")
+    assert can_shard(cfg, 2) and [o_window(cfg, r, 2) for r in (0, 1)] == [(0, 384, 0), (256, 640, 64)]
+    P = packing.synth_packed(cfg, 0)
+    ao = torch.randn(cfg.dim, generator=torch.Generator().manual_seed(3)).bfloat16()
+    full = O.c_gemv(P["o_q"][0], P["o_s"][0], None, ao)[0]
+    tot = np.zeros_like(full)
+    for r in range(2):
+        S = shard_packed(P, cfg, r, 2)
+        lo, hi, off = o_window(cfg, r, 2)
+        assert S["o_q"].shape[-1] * 8 == hi - lo == 384
+        x = torch.zeros(hi - lo, dtype=torch.bfloat16)
+        x[off:off + 320] = ao[320 * r:320 * r + 320]          # the rank's own attention output; zeros elsewhere
+        tot += O.c_gemv(S["o_q"][0], S["o_s"][0], None, x)[0]
+    assert np.abs(tot - full).max() < 1e-4 * (np.abs(full).max() + 1)
