@@ -750,6 +750,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
         t.nph = 4;
       }
       t.gbar = c->vgbar + 4 * (l + 1);
+      t.dbg = (c->prof && l == 1) ? c->prof : nullptr;
       FB_CUDA(c, launch_vchain(t, MT, hz, c->sm_count, st));
     }
     if (!d_logits && d_feat)

@@ -545,7 +545,7 @@ struct VtcPhase {
   const uint16_t* norm_w;    // bf16 [K] RMSNorm weights or nullptr
   const float* ssq_in;       // [n_ssq][64]: partial sums of squares per token, written by the previous residual phase
   float* ssq_out;            // RESID: [row blocks * 4][64] or nullptr
-  uint16_t* xn_out;          // norm_w set: CTA 0 also writes the normalised rows here (the feature output) or nullptr
+  uint16_t* xn_out;          // norm_w set: the items of row block 0 also write the normalised rows here (feature output) or nullptr
   uint16_t* h;               // RESID
   uint16_t* q;               // QKV
   uint16_t *kc, *vc;         // QKV
@@ -564,6 +564,7 @@ struct VchainParams {
   const float2* rope;
   int n_head, nkv, pos, head_dim, dim;
   float resid, logits_scaling, eps;
+  long long* dbg;            // optional: %globaltimer stamps of CTA 0, 16 per phase
 };
 
 template <int MT, bool HZ>
@@ -598,7 +599,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
   WaitCtl wc{P.status, s_abort, P.spin_limit};
-  const unsigned arrivals = 4u * gridDim.x;                           // epilogue warps of the whole grid
+#define CH_STAMP(ph, i) do { if (P.dbg && blockIdx.x == 0 && lane == 0) P.dbg[(ph) * 16 + (i)] = (long long)globaltimer_ns(); } while (0)
+  const unsigned arrivals = gridDim.x;                                // one arrival per CTA and phase
+  volatile int* s_epi = reinterpret_cast<volatile int*>(tsm + S::BAR + 960);      // [0..4) epilogue warps done per phase, [4..8) phase released, [8..12) loader warps done with their slice of the norm sums
+  if (tid < 12) s_epi[tid] = 0;
+  __syncthreads();
 
   if (warp == 0) {
     // ---------------- producer: runs ahead through the phases, bounded only by the raw ring
@@ -714,29 +719,70 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
     uint32_t gi = 0;                                             // groups of this CTA so far, all phases (stage = gi % NS)
     for (int ph = 0; ph < P.nph && ok; ph++) {
       const VtcPhase& F = P.ph[ph];
-      if (ph > 0) {                                              // every epilogue warp of the grid has finished phase ph-1
+      if (ph > 0) {                                              // every CTA of the grid has finished phase ph-1
+        // one lane of the CTA polls the global counter (with a pause: 148 pollers on one line must not starve the
+        // arrivals), the other loader warps watch a shared-memory flag
         if (lane == 0) {
           bool seen = false;
           for (unsigned i = 0; i < wc.limit; i++) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.gbar + (ph - 1)) : "memory");
-            if (v >= arrivals) { seen = true; break; }
+            if (warp == 6) {
+              unsigned v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(P.gbar + (ph - 1)) : "memory");
+              if (v >= arrivals) { s_epi[4 + ph] = 1; seen = true; break; }
+              __nanosleep(200);
+            } else if (s_epi[4 + ph]) { seen = true; break; }
             if ((i & 15) == 15 && (*wc.s_abort || ld_volatile_s32(&wc.st->abort))) { *wc.s_abort = 1; break; }
           }
           if (!seen && *wc.s_abort == 0) report_fail(wc, W_FLAG, ph, (int)arrivals, -5);
+          __threadfence();
         }
         __syncwarp();
         if (*wc.s_abort) { ok = false; break; }
       }
+      if (warp == 6) CH_STAMP(ph, 0);
       float* rinv = s_rinv + ph * 64;
-      if (F.norm_w) {                                            // 1/rms per token from the partial sums, in a fixed order
-        for (int m = lane; m < P.M; m += 32) {                   // (each loader warp writes the same values)
+      if (F.norm_w) {
+        // 1/rms per token from the partial sums, in a fixed order. The partials are independent L2 loads: the 128 loader
+        // threads split them (thread = token x slice of the partials, many loads in flight each), meet in shared memory
+        // (the epilogue staging area is idle between phases) and every warp adds the slices in slice order.
+        constexpr int NSL = 128 / MT;
+        float* sl = reinterpret_cast<float*>(tsm + S::EPI);
+        const int m0 = lt % MT, slice = lt / MT, per = (F.n_ssq + NSL - 1) / NSL;
+        if (m0 < P.M) {
+          const int i0 = slice * per, i1 = min(F.n_ssq, i0 + per);
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+          int i = i0;
+          for (; i + 4 <= i1; i += 4) {
+            const float v0 = __ldcg(F.ssq_in + (size_t)i * 64 + m0), v1 = __ldcg(F.ssq_in + (size_t)(i + 1) * 64 + m0),
+                        v2 = __ldcg(F.ssq_in + (size_t)(i + 2) * 64 + m0), v3 = __ldcg(F.ssq_in + (size_t)(i + 3) * 64 + m0);
+            a0 += v0; a1 += v1; a2 += v2; a3 += v3;
+          }
+          for (; i < i1; i++) a0 += __ldcg(F.ssq_in + (size_t)i * 64 + m0);
+          sl[slice * 64 + m0] = (a0 + a1) + (a2 + a3);
+        }
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) {
+          atomicAdd(const_cast<int*>(s_epi + 8 + ph), 1);
+          bool seen = false;
+          for (unsigned i = 0; i < wc.limit; i++) {
+            if (s_epi[8 + ph] >= 4) { seen = true; break; }
+            if ((i & 63) == 63 && *wc.s_abort) break;
+          }
+          if (!seen && *wc.s_abort == 0) report_fail(wc, W_FLAG, ph, 4, -6);
+        }
+        __syncwarp();
+        if (*wc.s_abort) { ok = false; break; }
+        __threadfence_block();
+        for (int m = lane; m < P.M; m += 32) {
           float ss = 0.f;
-          for (int i = 0; i < F.n_ssq; i++) ss += __ldcg(F.ssq_in + (size_t)i * 64 + m);
+#pragma unroll
+          for (int q = 0; q < NSL; q++) ss += sl[q * 64 + m];
           rinv[m] = 1.0f / sqrtf(ss / (float)P.dim + P.eps);
         }
         __syncwarp();
       }
+      if (warp == 6) CH_STAMP(ph, 1);
       TcWalk wi(F.rows, F.K, F.nsplit);                          // issue-side cursor of this phase
       int gn = wi.valid() ? wi.g0 : 0;
       uint32_t gii = gi;
@@ -763,8 +809,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
         cp_async_commit();
       };
       for (int j = 0; j < AHEAD; j++) issue_next();
-      bool first_item = true;
-      for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next(), first_item = false) {
+      for (TcWalk w(F.rows, F.K, F.nsplit); w.valid() && ok; w.next()) {
         for (int g = w.g0; g < w.g1 && ok; g++, gi++) {
           cp_async_wait<AHEAD - 1>();
           if (F.norm_w) {
@@ -787,7 +832,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
                     o[e] = (uint32_t)f2bf(bflo(hh[e]) * r * bflo(ww[e])) | ((uint32_t)f2bf(bfhi(hh[e]) * r * bfhi(ww[e])) << 16);
                   const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
                   *d = ov;
-                  if (F.xn_out && blockIdx.x == 0 && first_item) *reinterpret_cast<uint4*>(F.xn_out + (size_t)m * F.K + col) = ov;
+                  if (F.xn_out && w.rb == 0) *reinterpret_cast<uint4*>(F.xn_out + (size_t)m * F.K + col) = ov;
                 }
               }
             }
@@ -795,10 +840,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&b_full[gi % NS]);
+          if (warp == 6 && g == w.g0) CH_STAMP(ph, 2);
           issue_next();
         }
       }
       cp_async_wait<0>();
+      if (warp == 6) CH_STAMP(ph, 3);
     }
   } else {
     // ---------------- epilogue
@@ -850,6 +897,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
         __syncwarp();
         if (lane == 0) mbar_arrive(&sc_empty[b]);
         if (!ok) break;
+        if (warp == 10) CH_STAMP(ph, 4);
         if (F.nsplit > 1) {
           float* mine = P.part + (size_t)w.item * MT * 128;
 #pragma unroll
@@ -872,6 +920,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
             for (int t = 0; t < MT; t++) y[t] += __ldcg(src + t * 128 + row);
           }
         }
+        if (warp == 10) CH_STAMP(ph, 5);
         float* ys = reinterpret_cast<float*>(tsm + S::EPI);
         __syncwarp();
 #pragma unroll
@@ -947,10 +996,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) v_chain_tc(const VchainParams P
         }
         __syncwarp();
       }
+      if (warp == 10) CH_STAMP(ph, 6);
       // this warp's results of the phase are in global memory: tell the grid (the loaders of the next phase wait for it)
       __threadfence();
       __syncwarp();
-      if (lane == 0 && ph + 1 < P.nph) atomicAdd(P.gbar + ph, 1u);
+      if (lane == 0 && ph + 1 < P.nph) {                         // the CTA's last epilogue warp arrives for the CTA
+        if (atomicAdd(const_cast<int*>(s_epi + ph), 1) == 3) {
+          __threadfence();
+          atomicAdd(P.gbar + ph, 1u);
+        }
+      }
+      if (warp == 10) CH_STAMP(ph, 7);
     }
   }
   tc_fence_before();
