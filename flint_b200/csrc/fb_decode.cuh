@@ -15,6 +15,9 @@
 #ifndef FB_ATTN_BATCH
 #define FB_ATTN_BATCH 2      // K/V positions a lane group loads before it uses any of them
 #endif
+#ifndef FB_ATTN_PFD
+#define FB_ATTN_PFD 2        // rounds ahead of its loads that a warp asks L2 for its K/V rows
+#endif
 
 namespace fb {
 
@@ -115,18 +118,40 @@ __device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
   (void)old;
 }
 // all consumer threads call; warp 0 polls flags[0..n) until each equals tag
+#ifndef FB_FLAG_SETS
+#define FB_FLAG_SETS 1       // poll rounds kept in flight (staggered): a posted flag is seen after ~RTT/2 + RTT/(2 sets)
+#endif
 __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
                                            int layer) {
   if (cw == 0) {
-    for (unsigned spin = 0;; spin++) {
-      // all loads of a round are issued before any is compared (n <= 256: at most 8 per lane)
-      uint32_t v[8];
+    constexpr int NS = FB_FLAG_SETS;
+    uint32_t v[NS][8];
+    // all loads of a round are issued before any is compared (n <= 256: at most 8 per lane)
+    auto issue = [&](uint32_t (&d)[8]) {
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
+      for (int j = 0; j < 8; j++) d[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
+    };
+    auto all_set = [&](const uint32_t (&d)[8]) {
       bool ok = true;
 #pragma unroll
-      for (int j = 0; j < 8; j++) ok = ok && (v[j] == tag);
-      if (__all_sync(0xffffffffu, ok)) break;
+      for (int j = 0; j < 8; j++) ok = ok && (d[j] == tag);
+      return __all_sync(0xffffffffu, ok) != 0;
+    };
+#pragma unroll
+    for (int s = 0; s < NS; s++) {
+      if (s) __nanosleep(700 / NS);
+      issue(v[s]);
+    }
+    bool done = false;
+    for (unsigned spin = 0; !done; spin++) {
+#pragma unroll
+      for (int s = 0; s < NS; s++) {
+        if (!done) {
+          if (all_set(v[s])) done = true;
+          else issue(v[s]);
+        }
+      }
+      if (done) break;
       int stop = 0;
       if (lane == 0) {
         if (*wc.s_abort) stop = 1;
@@ -342,7 +367,7 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
       if (sl < (HD * 2 + 63) / 64) {
 #pragma unroll
         for (int j = 0; j < BATCH; j++) {
-          const int tp = tb + (2 * BATCH + j) * stride + seg;
+          const int tp = tb + (FB_ATTN_PFD * BATCH + j) * stride + seg;
           if (tp < t1) {
             const size_t off = ((size_t)tp * a.nkv + kvh) * HD;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.kc + off) + sl * 64));
