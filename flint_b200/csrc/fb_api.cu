@@ -10,6 +10,7 @@
 #include "fb_ctx.hpp"
 #include "fb_decode.cuh"
 #include "fb_verify.cuh"
+#include "fb_vsub.cuh"
 #include "fb_vtc.cuh"
 
 using namespace fb;
@@ -229,6 +230,29 @@ int tc_splits(int rows, int k, int sms) {
   return ns;
 }
 
+template <int NT, int EPI>
+cudaError_t launch_vsub_nt(const VsubParams& p, int sms, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(v_gemm_sub<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kVsSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  return launch_pdl(v_gemm_sub<NT, EPI>, dim3(sms), dim3(kVsThreads), (size_t)p.plan.bar_off + 512, st, p);
+}
+template <int EPI>
+cudaError_t launch_vsub(const VsubParams& p, int sms, cudaStream_t st) {
+  switch ((p.M + 7) / 8) {
+    case 1: return launch_vsub_nt<1, EPI>(p, sms, st);
+    case 2: return launch_vsub_nt<2, EPI>(p, sms, st);
+    case 3: return launch_vsub_nt<3, EPI>(p, sms, st);
+    case 4: return launch_vsub_nt<4, EPI>(p, sms, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
 template <int MT, int EPI, bool HZ>
 cudaError_t launch_vtc_hz(VtcParams& p, int sms, cudaStream_t st) {
   static bool configured[64] = {};
@@ -425,8 +449,8 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
   }
   A(dmalloc(&c->vpart, (size_t)d.n_kv_head * 32 * 64 * c->rgqa * (d.head_dim + 2) * 4));
   A(dmalloc(&c->vsplit, (size_t)kTcMaxItems * 64 * 128 * 4));
-  A(dmalloc(&c->vcount, 4096 * 4));
-  if (e == cudaSuccess) A(cudaMemset(c->vcount, 0, 4096 * 4));
+  A(dmalloc(&c->vcount, kVsCounters * 4));
+  if (e == cudaSuccess) A(cudaMemset(c->vcount, 0, kVsCounters * 4));
   A(cudaMalloc(&c->vrope, (size_t)64 * (d.head_dim / 2) * 8));
   A(dmalloc(&c->vssq, (size_t)2 * 256 * 64 * 4));
   A(dmalloc(&c->vgbar, (size_t)(d.n_layer + 2) * 4 * 4));
@@ -461,7 +485,7 @@ int fb_ctx_destroy(fb_ctx* c) {
   void* ptrs[] = {c->w_qkv, c->w_o, c->w_gu, c->w_d, c->w_lm, c->invf,
                   c->status, c->h_ll, c->q_ll, c->k_ll, c->v_ll, c->ao_ll, c->act_ll, c->cand_ll, c->flags,
                   c->part_ll, c->vh, c->vxn, c->vq, c->vao, c->vact, c->vpart, c->inbox,
-                  c->t_qkv, c->t_o, c->t_gu, c->t_d, c->t_lm, c->vsplit, c->vcount, c->vrope, c->vssq, c->vgbar};
+                  c->t_qkv, c->t_o, c->t_gu, c->t_d, c->t_lm, c->s_qkv, c->s_o, c->s_gu, c->s_d, c->s_lm, c->vsplit, c->vcount, c->vrope, c->vssq, c->vgbar};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete c;
@@ -473,7 +497,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
-  if (what == 7) { if (value < 0 || value > 3) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
+  if (what == 7) { if (value < 0 || value > 5) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -604,13 +628,13 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int L = d.n_layer, D = d.dim, FF = d.ffn, HD = d.head_dim;
   const int QKV = (d.n_head + 2 * d.n_kv_head) * HD, QD = d.n_head * HD;
-  struct M { uint8_t** dst; uint8_t** tdst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
+  struct M { uint8_t** dst; uint8_t** tdst; uint8_t** sdst; const void *q, *s, *z; int layers, rows, k, order, arg, orows; };
   M ms[] = {
-      {&c->w_qkv, &c->t_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
-      {&c->w_o, &c->t_o, w->o_q, w->o_s, w->o_z, L, D, c->ko, 0, 0, 0},
-      {&c->w_gu, &c->t_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
-      {&c->w_d, &c->t_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
-      {&c->w_lm, &c->t_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
+      {&c->w_qkv, &c->t_qkv, &c->s_qkv, w->qkv_q, w->qkv_s, w->qkv_z, L, QKV, D, 1, HD, (d.n_head + d.n_kv_head) * HD},
+      {&c->w_o, &c->t_o, &c->s_o, w->o_q, w->o_s, w->o_z, L, D, c->ko, 0, 0, 0},
+      {&c->w_gu, &c->t_gu, &c->s_gu, w->gu_q, w->gu_s, w->gu_z, L, 2 * FF, D, 2, FF, 0},
+      {&c->w_d, &c->t_d, &c->s_d, w->d_q, w->d_s, w->d_z, L, D, FF, 0, 0, 0},
+      {&c->w_lm, &c->t_lm, &c->s_lm, w->lm_q, w->lm_s, w->lm_z, 1, d.vocab, D, 0, 0, 0},
   };
   for (M& m : ms) {
     const size_t bytes = (size_t)m.layers * pad_rows(m.rows, m.k) * rec_bytes_of(m.k, hz);
@@ -623,6 +647,17 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
       FB_CUDA(c, dmalloc(m.tdst, (size_t)m.layers * tc_matrix_bytes(m.rows, m.k, hz) + 16));
       tc_repack<<<dim3(nrb, m.layers), 256, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s, hz ? (const uint16_t*)m.z : nullptr,
                                                      m.rows, m.k, m.order, m.arg, m.orows, *m.tdst);
+      FB_CUDA(c, cudaGetLastError());
+    }
+    if (*m.sdst) { cudaFree(*m.sdst); *m.sdst = nullptr; }
+    const int tiles32 = (m.rows + 31) / 32;
+    const VsPlan vp = vs_plan(m.k, 1, tiles32);
+    if (c->tp_size == 1 && !hz && vp.ok &&
+        (size_t)tiles32 * vp.nkc * 8 * 512 <= (size_t)kTcMaxItems * 64 * 128 * 4) {   // K-split partials fit the shared buffer
+      // the small-tree verify GEMM's copy (symmetric layout only; other shapes keep the bf16 warp-level kernel)
+      FB_CUDA(c, dmalloc(m.sdst, (size_t)m.layers * vs_matrix_bytes(m.rows, m.k) + 16));
+      vs_repack<<<dim3(tiles32, m.layers), 256, 0, st>>>((const uint32_t*)m.q, (const uint16_t*)m.s, m.rows, m.k, vp.ug, m.order,
+                                                         m.arg, m.orows, *m.sdst);
       FB_CUDA(c, cudaGetLastError());
     }
   }
@@ -797,27 +832,79 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   memset(&p, 0, sizeof(p));
   p.M = M; p.has_zeros = hz; p.depth = d_depth; p.invf = c->invf; p.n_head = d.n_head; p.nkv = d.n_kv_head; p.pos = pos;
   p.resid = d.resid_mult; p.logits_scaling = d.logits_scaling;
+  // small trees: every GEMM whose matrix has an R32 copy runs on the subnormal-operand kernel; same activation buffers
+  const bool use_sub = (c->verify_path == 4 || c->verify_path == 5) && M <= kVsMaxTokens && !hz;
+  const bool fuse_norm = c->verify_path != 5;            // 5: the same kernels with the separate RMSNorm launches (diagnostic)
+  VsubParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.M = M; sp.part = c->vsplit; sp.counters = (int*)c->vcount; sp.status = c->status; sp.spin_limit = c->spin_limit;
+  sp.rope = (const float2*)c->vrope; sp.n_head = d.n_head; sp.nkv = d.n_kv_head; sp.pos = pos; sp.head_dim = HD;
+  sp.resid = d.resid_mult; sp.logits_scaling = d.logits_scaling;
+  if (use_sub && c->s_qkv)
+    FB_CUDA(c, launch_pdl(v_rope_table, dim3(M), dim3(64), 0, st, d_depth, (const float*)c->invf, (int)pos, HD / 2, (float2*)c->vrope));
+  int nsub = 0;
+  auto sub = [&](const uint8_t* sw, size_t layer, int rows, int K) -> bool {
+    if (!use_sub || !sw) return false;
+    sp.plan = vs_plan(K, M, (rows + 31) / 32);
+    if (!sp.plan.ok) return false;
+    sp.w = sw + layer * vs_matrix_bytes(rows, K); sp.rows = rows; sp.K = K;
+    sp.dbg = (c->prof && layer == 1) ? c->prof + 8 * (nsub++ & 7) : nullptr;   // stamps of the second layer's GEMMs
+    return true;
+  };
   for (int l = 0; l < d.n_layer; l++) {
     uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
     uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
-    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
-    p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
-    p.q = c->vq; p.kc = kcl; p.vc = vcl;
-    FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, c->sm_count, st));
+    const bool sq = sub(c->s_qkv, l, QKV, D);
+    const bool fuse1 = sq && fuse_norm && sp.plan.nkc == 1;          // the GEMM normalises the residual rows while it stages them
+    if (!fuse1) FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+    if (sq) {
+      sp.x_t = fuse1 ? c->vh : c->vxn; sp.norm_w = fuse1 ? (const uint16_t*)c->n1 + (size_t)l * D : nullptr; sp.eps = d.rms_eps;
+      sp.q = c->vq; sp.kc = kcl; sp.vc = vcl;
+      FB_CUDA(c, launch_vsub<EPI_QKV>(sp, c->sm_count, st));
+      sp.norm_w = nullptr;
+    } else {
+      p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
+      p.q = c->vq; p.kc = kcl; p.vc = vcl;
+      FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, c->sm_count, st));
+    }
     FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, 0, st));
-    p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, c->sm_count, st));
-    FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
-    p.w = c->w_gu + l * strG; p.x_t = c->vxn; p.rows = 2 * FF; p.act_t = c->vact;
-    p.out_ld = FF;
-    FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, c->sm_count, st));
-    p.w = c->w_d + l * strF; p.x_t = c->vact; p.rows = D; p.out_ld = D;
-    FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, FF, HD, c->sm_count, st));
+    if (sub(c->s_o, l, D, QD)) {
+      sp.x_t = c->vao; sp.h = c->vh; sp.out_ld = D;
+      FB_CUDA(c, launch_vsub<EPI_RESID>(sp, c->sm_count, st));
+    } else {
+      p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
+      FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, c->sm_count, st));
+    }
+    const bool sg = sub(c->s_gu, l, 2 * FF, D);
+    const bool fuse2 = sg && fuse_norm && sp.plan.nkc == 1;
+    if (!fuse2) FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+    if (sg) {
+      sp.x_t = fuse2 ? c->vh : c->vxn; sp.norm_w = fuse2 ? (const uint16_t*)c->n2 + (size_t)l * D : nullptr; sp.eps = d.rms_eps;
+      sp.act_t = c->vact; sp.out_ld = FF;
+      FB_CUDA(c, launch_vsub<EPI_SWIGLU>(sp, c->sm_count, st));
+      sp.norm_w = nullptr;
+    } else {
+      p.w = c->w_gu + l * strG; p.x_t = c->vxn; p.rows = 2 * FF; p.act_t = c->vact;
+      p.out_ld = FF;
+      FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, c->sm_count, st));
+    }
+    if (sub(c->s_d, l, D, FF)) {
+      sp.x_t = c->vact; sp.h = c->vh; sp.out_ld = D;
+      FB_CUDA(c, launch_vsub<EPI_RESID>(sp, c->sm_count, st));
+    } else {
+      p.w = c->w_d + l * strF; p.x_t = c->vact; p.rows = D; p.h = c->vh; p.out_ld = D;
+      FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, FF, HD, c->sm_count, st));
+    }
   }
   FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, M, d.rms_eps, st));
   if (d_logits) {
-    p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.logits = d_logits; p.out_ld = d.vocab;
-    FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, D, HD, c->sm_count, st));
+    if (sub(c->s_lm, 0, d.vocab, D)) {
+      sp.x_t = c->vxn; sp.logits = d_logits; sp.out_ld = d.vocab;
+      FB_CUDA(c, launch_vsub<EPI_LOGITS>(sp, c->sm_count, st));
+    } else {
+      p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.logits = d_logits; p.out_ld = d.vocab;
+      FB_CUDA(c, launch_vgemm_mt<EPI_LOGITS>(p, MT, D, HD, c->sm_count, st));
+    }
   }
   FB_CUDA(c, cudaGetLastError());
   return FB_OK;

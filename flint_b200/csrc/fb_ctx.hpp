@@ -31,11 +31,12 @@ struct fb_ctx {
   uint16_t *vh, *vxn, *vq, *vao, *vact;                             // verify activations, 64 token rows each
   float* vpart;                                                     // verify attention: per-span partials
   uint8_t *t_qkv, *t_o, *t_gu, *t_d, *t_lm;                          // verify: the matrices in the tensor-core (TC) layout
+  uint8_t *s_qkv, *s_o, *s_gu, *s_d, *s_lm;                          // verify: the matrices in the R32 layout (small trees); NULL = not built
   float* vsplit;                                                    // verify: split-K partial sums
   unsigned* vcount;                                                 // verify: arrivals per (row block, row quadrant)
   float* vssq;                                                      // verify chain: partial sums of squares, 2 x [256][64]
   unsigned* vgbar;                                                  // verify chain: grid arrival counters per launch and phase
   void* vrope;                                                      // verify: (cos, sin) per (token, rotation pair)
-  int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs, 2: tcgen05 GEMMs, 3: tcgen05 GEMM chains
+  int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs (bf16), 2: tcgen05 GEMMs, 3: tcgen05 GEMM chains, 4: warp-level MMA GEMMs on fp16 subnormals
   int max_fly, poll_words;
 };

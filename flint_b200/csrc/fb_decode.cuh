@@ -121,6 +121,9 @@ __device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
 #ifndef FB_FLAG_SETS
 #define FB_FLAG_SETS 1       // poll rounds kept in flight (staggered): a posted flag is seen after ~RTT/2 + RTT/(2 sets)
 #endif
+#ifndef FB_FLAG_SLACK
+#define FB_FLAG_SLACK 0      // producers that may still be missing when the gather starts: their tagged words are
+#endif                       // simply polled again by the gather, so the last flag's round trip leaves the critical path
 __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
                                            int layer) {
   if (cw == 0) {
@@ -132,10 +135,17 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_
       for (int j = 0; j < 8; j++) d[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
     };
     auto all_set = [&](const uint32_t (&d)[8]) {
-      bool ok = true;
+      if constexpr (FB_FLAG_SLACK == 0) {
+        bool ok = true;
 #pragma unroll
-      for (int j = 0; j < 8; j++) ok = ok && (d[j] == tag);
-      return __all_sync(0xffffffffu, ok) != 0;
+        for (int j = 0; j < 8; j++) ok = ok && (d[j] == tag);
+        return __all_sync(0xffffffffu, ok) != 0;
+      } else {
+        unsigned miss = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) miss += (d[j] != tag);
+        return __reduce_add_sync(0xffffffffu, miss) <= (unsigned)FB_FLAG_SLACK;
+      }
     };
 #pragma unroll
     for (int s = 0; s < NS; s++) {

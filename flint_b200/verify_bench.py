@@ -24,7 +24,7 @@ def main():
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--path", type=int, default=0, help="GEMM implementation (fb_set_option 7): 0 by tree size, 1 warp-level, 2 tcgen05, 3 tcgen05 chains")
+    ap.add_argument("--path", type=int, default=0, help="GEMM implementation (fb_set_option 7): 0 by tree size, 1 warp-level bf16, 2 tcgen05, 3 tcgen05 chains, 4 warp-level fp16 subnormals")
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
     W = packing.synth_packed(cfg, 0, device="cuda")

@@ -34,12 +34,13 @@ def _prefix(orc, eng, toks):
         eng.decode(t, p, want_logits=False)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 @pytest.mark.parametrize("asym", [False, True])
 @pytest.mark.parametrize("M", [1, 5, 16, 26, 40])
 def test_tiny_chain_verify_vs_oracle(M, asym, path):
-    """Both GEMM implementations of the verify path (1 = warp-level mma.sync, 2 = tcgen05 with accumulators in tensor
-    memory) at every padded token count (16 / 32 / 64), symmetric and asymmetric weights."""
+    """Every GEMM implementation of the verify path (1 = warp-level mma.sync on bf16, 2 = tcgen05 with accumulators in
+    tensor memory, 3 = tcgen05 chains, 4 = warp-level mma.sync on fp16 subnormals for up to 26 tokens) at every padded
+    token count, symmetric and asymmetric weights. A path that does not cover a case runs the library's fallback."""
     cfg = ModelArgs.from_name("tiny")
     P = packing.synth_packed(cfg, 0, asym=asym)
     orc, eng = O.OracleModel(cfg, P, 128), DecodeEngine(cfg, _cuda(P), max_seq=128)
@@ -173,7 +174,7 @@ def _verify_rows_ok(lg, ref_lg, bound=0.02):
     assert _argmax_ok(lg, ref_lg)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3])
+@pytest.mark.parametrize("path", [1, 2, 3, 4])
 @pytest.mark.parametrize("M", [16, 26, 64])
 def test_granite3b_shape_verify_over_1024_token_cache(M, path):
     """The benchmark's verify configuration: static trees of 16 / 26 / 64 nodes over a cache of 1024 positions (seeded
