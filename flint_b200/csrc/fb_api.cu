@@ -497,7 +497,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
-  if (what == 7) { if (value < 0 || value > 5) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
+  if (what == 7) { if (value < 0 || value > 4) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
   return FB_ERR_ARG;
@@ -832,14 +832,16 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   memset(&p, 0, sizeof(p));
   p.M = M; p.has_zeros = hz; p.depth = d_depth; p.invf = c->invf; p.n_head = d.n_head; p.nkv = d.n_kv_head; p.pos = pos;
   p.resid = d.resid_mult; p.logits_scaling = d.logits_scaling;
-  // small trees: every GEMM whose matrix has an R32 copy runs on the subnormal-operand kernel; same activation buffers
-  const bool use_sub = (c->verify_path == 4 || c->verify_path == 5) && M <= kVsMaxTokens && !hz;
-  const bool fuse_norm = c->verify_path != 5;            // 5: the same kernels with the separate RMSNorm launches (diagnostic)
+  // small trees: every GEMM whose matrix has an R32 copy runs on the subnormal-operand kernel. It reads the same
+  // activation buffers; the QKV and gate/up GEMMs read the residual rows and apply the RMSNorm themselves
+  // by tree size: up to 8 tokens (one B tile) this kernel wins (2.07 vs 2.40 ms per pass of the 3B model); above, its
+  // per-CTA conversion of the activations (linear in the tokens) costs more than the dequantisation it saves
+  const bool use_sub = (c->verify_path == 4 || (c->verify_path == 0 && M <= 8)) && M <= kVsMaxTokens && !hz;
   VsubParams sp;
   memset(&sp, 0, sizeof(sp));
   sp.M = M; sp.part = c->vsplit; sp.counters = (int*)c->vcount; sp.status = c->status; sp.spin_limit = c->spin_limit;
   sp.rope = (const float2*)c->vrope; sp.n_head = d.n_head; sp.nkv = d.n_kv_head; sp.pos = pos; sp.head_dim = HD;
-  sp.resid = d.resid_mult; sp.logits_scaling = d.logits_scaling;
+  sp.resid = d.resid_mult; sp.logits_scaling = d.logits_scaling; sp.eps = d.rms_eps;
   if (use_sub && c->s_qkv)
     FB_CUDA(c, launch_pdl(v_rope_table, dim3(M), dim3(64), 0, st, d_depth, (const float*)c->invf, (int)pos, HD / 2, (float2*)c->vrope));
   int nsub = 0;
@@ -847,49 +849,51 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     if (!use_sub || !sw) return false;
     sp.plan = vs_plan(K, M, (rows + 31) / 32);
     if (!sp.plan.ok) return false;
-    sp.w = sw + layer * vs_matrix_bytes(rows, K); sp.rows = rows; sp.K = K;
+    sp.w = sw + layer * vs_matrix_bytes(rows, K); sp.rows = rows; sp.K = K; sp.norm_w = nullptr;
     sp.dbg = (c->prof && layer == 1) ? c->prof + 8 * (nsub++ & 7) : nullptr;   // stamps of the second layer's GEMMs
     return true;
   };
   for (int l = 0; l < d.n_layer; l++) {
     uint16_t* kcl = (uint16_t*)c->kc + (size_t)l * c->max_seq * d.n_kv_head * HD;
     uint16_t* vcl = (uint16_t*)c->vc + (size_t)l * c->max_seq * d.n_kv_head * HD;
-    const bool sq = sub(c->s_qkv, l, QKV, D);
-    const bool fuse1 = sq && fuse_norm && sp.plan.nkc == 1;          // the GEMM normalises the residual rows while it stages them
-    if (!fuse1) FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
-    if (sq) {
-      sp.x_t = fuse1 ? c->vh : c->vxn; sp.norm_w = fuse1 ? (const uint16_t*)c->n1 + (size_t)l * D : nullptr; sp.eps = d.rms_eps;
+    if (sub(c->s_qkv, l, QKV, D)) {
+      if (sp.plan.nkc == 1) { sp.x = c->vh; sp.norm_w = (const uint16_t*)c->n1 + (size_t)l * D; }
+      else {
+        FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+        sp.x = c->vxn;
+      }
       sp.q = c->vq; sp.kc = kcl; sp.vc = vcl;
       FB_CUDA(c, launch_vsub<EPI_QKV>(sp, c->sm_count, st));
-      sp.norm_w = nullptr;
     } else {
+      FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n1 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
       p.w = c->w_qkv + l * strQ; p.x_t = c->vxn; p.rows = QKV;
       p.q = c->vq; p.kc = kcl; p.vc = vcl;
       FB_CUDA(c, launch_vgemm_mt<EPI_QKV>(p, MT, D, HD, c->sm_count, st));
     }
     FB_CUDA(c, launch_vattn(c, c->vq, kcl, vcl, d_amask, c->vao, pos, M, 0, st));
     if (sub(c->s_o, l, D, QD)) {
-      sp.x_t = c->vao; sp.h = c->vh; sp.out_ld = D;
+      sp.x = c->vao; sp.h = c->vh; sp.out_ld = D;
       FB_CUDA(c, launch_vsub<EPI_RESID>(sp, c->sm_count, st));
     } else {
       p.w = c->w_o + l * strO; p.x_t = c->vao; p.rows = D; p.h = c->vh; p.out_ld = D;
       FB_CUDA(c, launch_vgemm_mt<EPI_RESID>(p, MT, QD, HD, c->sm_count, st));
     }
-    const bool sg = sub(c->s_gu, l, 2 * FF, D);
-    const bool fuse2 = sg && fuse_norm && sp.plan.nkc == 1;
-    if (!fuse2) FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
-    if (sg) {
-      sp.x_t = fuse2 ? c->vh : c->vxn; sp.norm_w = fuse2 ? (const uint16_t*)c->n2 + (size_t)l * D : nullptr; sp.eps = d.rms_eps;
+    if (sub(c->s_gu, l, 2 * FF, D)) {
+      if (sp.plan.nkc == 1) { sp.x = c->vh; sp.norm_w = (const uint16_t*)c->n2 + (size_t)l * D; }
+      else {
+        FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
+        sp.x = c->vxn;
+      }
       sp.act_t = c->vact; sp.out_ld = FF;
       FB_CUDA(c, launch_vsub<EPI_SWIGLU>(sp, c->sm_count, st));
-      sp.norm_w = nullptr;
     } else {
+      FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->n2 + (size_t)l * D, c->vxn, nullptr, D, M, d.rms_eps, st));
       p.w = c->w_gu + l * strG; p.x_t = c->vxn; p.rows = 2 * FF; p.act_t = c->vact;
       p.out_ld = FF;
       FB_CUDA(c, launch_vgemm_mt<EPI_SWIGLU>(p, MT, D, HD, c->sm_count, st));
     }
     if (sub(c->s_d, l, D, FF)) {
-      sp.x_t = c->vact; sp.h = c->vh; sp.out_ld = D;
+      sp.x = c->vact; sp.h = c->vh; sp.out_ld = D;
       FB_CUDA(c, launch_vsub<EPI_RESID>(sp, c->sm_count, st));
     } else {
       p.w = c->w_d + l * strF; p.x_t = c->vact; p.rows = D; p.h = c->vh; p.out_ld = D;
@@ -899,7 +903,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
   FB_CUDA(c, launch_vnorm(c->vh, (const uint16_t*)c->nf, c->vxn, (uint16_t*)d_feat, D, M, d.rms_eps, st));
   if (d_logits) {
     if (sub(c->s_lm, 0, d.vocab, D)) {
-      sp.x_t = c->vxn; sp.logits = d_logits; sp.out_ld = d.vocab;
+      sp.x = c->vxn; sp.logits = d_logits; sp.out_ld = d.vocab;
       FB_CUDA(c, launch_vsub<EPI_LOGITS>(sp, c->sm_count, st));
     } else {
       p.w = c->w_lm; p.x_t = c->vxn; p.rows = d.vocab; p.logits = d_logits; p.out_ld = d.vocab;

@@ -121,9 +121,11 @@ __device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
 #ifndef FB_FLAG_SETS
 #define FB_FLAG_SETS 1       // poll rounds kept in flight (staggered): a posted flag is seen after ~RTT/2 + RTT/(2 sets)
 #endif
-#ifndef FB_FLAG_SLACK
-#define FB_FLAG_SLACK 0      // producers that may still be missing when the gather starts: their tagged words are
-#endif                       // simply polled again by the gather, so the last flag's round trip leaves the critical path
+#ifndef FB_FLAG_SLACK_DIV
+#define FB_FLAG_SLACK_DIV 3  // the gather starts when all but n / 3 producers have posted (0: wait for every flag). The tagged
+#endif                       // words of the stragglers are simply polled again by the gather, so the last flags' round trip
+                             // leaves the critical path: measured +2.6 % tokens/s at a third, +1.8 % at a sixth, -0.9 % with
+                             // no flag wait at all (every consumer polling words floods L2)
 __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_t tag, int cw, int lane, const WaitCtl& wc,
                                            int layer) {
   if (cw == 0) {
@@ -135,7 +137,7 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_
       for (int j = 0; j < 8; j++) d[j] = (lane + 32 * j < n) ? ld_relaxed_u32(flags + lane + 32 * j) : tag;
     };
     auto all_set = [&](const uint32_t (&d)[8]) {
-      if constexpr (FB_FLAG_SLACK == 0) {
+      if constexpr (FB_FLAG_SLACK_DIV == 0) {
         bool ok = true;
 #pragma unroll
         for (int j = 0; j < 8; j++) ok = ok && (d[j] == tag);
@@ -144,7 +146,7 @@ __device__ __forceinline__ void wait_flags(const uint32_t* flags, int n, uint32_
         unsigned miss = 0;
 #pragma unroll
         for (int j = 0; j < 8; j++) miss += (d[j] != tag);
-        return __reduce_add_sync(0xffffffffu, miss) <= (unsigned)FB_FLAG_SLACK;
+        return __reduce_add_sync(0xffffffffu, miss) <= (unsigned)(n / FB_FLAG_SLACK_DIV);
       }
     };
 #pragma unroll

@@ -11,8 +11,9 @@
 // One CTA per SM, persistent. A producer lane streams the CTA's units into a ring whose stages are owned one-to-one
 // by consumer warps: warp (slot, u) multiplies unit u of the tile in flight on `slot`, the `upi` warps of a slot meet
 // through their (consumed) stage buffers, add their partial sums in unit order and share the epilogue. The tokens'
-// activations (all of K, or this CTA's K slice when K is split over CTAs) are converted once per launch to fp16 in
-// B-operand order with one power-of-two factor per (token, group). K slices of different CTAs meet in global memory;
+// activations (all of K, or this CTA's K slice when K is split over CTAs) are copied into shared memory and converted
+// there to fp16 in B-operand order with one power-of-two factor per (token, group); the QKV and gate/up GEMMs apply the
+// RMSNorm on the way, so no norm kernel runs between GEMMs. K slices of different CTAs meet in global memory;
 // the CTA that arrives last adds the partials in slice order, so results do not depend on timing.
 #pragma once
 #include "fb_verify.cuh"
@@ -32,7 +33,7 @@ __host__ __device__ constexpr size_t vs_matrix_bytes(int rows, int k) {
 
 struct VsPlan {
   int ok, ug, upi, nkc, nslot, kcg;           // groups per unit, units per item, K slices, tiles in flight, groups per slice
-  int xs, acts_off, f_off, sq_off, bar_off;   // activation row stride (bytes) and shared-memory offsets
+  int xs, acts_off, f_off, bar_off;           // activation row stride (bytes) and shared-memory offsets
 };
 
 // Geometry of one launch. K is cut into as few CTA slices as let the activations of a slice (for the largest tree), their
@@ -53,14 +54,13 @@ __host__ __device__ inline VsPlan vs_plan(int K, int M, int tiles) {
     if (upi > 6) continue;
     if (nkc > 1 && tiles * 8 > kVsCounters) continue;
     const int xs = kcg * 256 + 32;
-    if ((kVsSmem - (kVsMaxTokens * (xs + kcg * 20) + 1024)) / (upi * vs_unit_bytes(ug)) < 2) continue;
-    int nslot = (kVsSmem - (M * (xs + kcg * 20) + 1024)) / (upi * vs_unit_bytes(ug));
+    if ((kVsSmem - (kVsMaxTokens * (xs + kcg * 16 + 16) + 1024)) / (upi * vs_unit_bytes(ug)) < 2) continue;
+    int nslot = (kVsSmem - (M * (xs + kcg * 16 + 16) + 1024)) / (upi * vs_unit_bytes(ug));
     if (nslot > kVsWarps / upi) nslot = kVsWarps / upi;
     p.ok = 1; p.ug = ug; p.upi = upi; p.nkc = nkc; p.nslot = nslot; p.kcg = kcg; p.xs = xs;
     p.acts_off = nslot * upi * vs_unit_bytes(ug);
     p.f_off = p.acts_off + M * xs;
-    p.sq_off = p.f_off + M * kcg * 16;
-    p.bar_off = (p.sq_off + M * kcg * 4 + 15) & ~15;
+    p.bar_off = p.f_off + M * (kcg * 16 + 16);             // factor rows are padded by 16 bytes: conflict-free reads
     return p;
   }
   return p;
@@ -102,7 +102,7 @@ __global__ void vs_repack(const uint32_t* q, const uint16_t* sc, int rows, int K
 
 struct VsubParams {
   const uint8_t* w;          // R32 layout of this matrix (layer offset applied)
-  const uint16_t* x_t;       // bf16 [>= M][K], B-operand order inside every 16 columns; with norm_w: the residual rows in
+  const uint16_t* x;         // bf16 [>= M][K], B-operand order inside every 16 columns; with norm_w: the residual rows in
                              // natural order, normalised while they are staged (K not split over CTAs)
   const uint16_t* norm_w;    // RMSNorm weight bf16 [K] or NULL
   float eps;
@@ -131,93 +131,95 @@ __device__ __forceinline__ float4 ld_cg_f4(const float4* p) {
   return v;
 }
 
-// Bring this CTA's K slice of every token into shared memory (asynchronous 16-byte copies), then convert it in place to
-// fp16 in B-operand order and write the per-(token, group) factors {2^24 / m, 2^20 / m, -8 * sum x, sum x}; one warp
-// converts one (token, group) at a time. With a norm weight the rows are the residual stream in natural order:
-// xn = bf16((float(h) * r) * float(w)) is formed on the way (two passes: per-group sums of squares added in group order,
-// then the conversion). Ends with a consumer barrier.
-__device__ __forceinline__ void vs_stage_acts(const VsubParams& P, int kc, uint8_t* acts, float4* xf, float* sq, float* rinv,
-                                              int tid, int warp, int lane) {
+__device__ __forceinline__ uint32_t vmaxu2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Bring this CTA's K slice of every token into shared memory (asynchronous 16-byte copies; every CTA copies the same rows,
+// so each starts at a different 128-byte line and they do not walk L2 in lockstep), then convert it in place to fp16 in
+// B-operand order with one power of two m per (token, group of 128): x * m has its largest magnitude in [2^14, 2^15).
+// xf = {2^24 / m, 2^20 / m, -8 * sum x, sum x} per (token, group). A lane converts one block of 16 columns (the unit of the
+// B-order permutation), eight lanes a group, a warp four groups at a time. With a norm weight the rows are the residual
+// stream in natural order and xn = bf16((float(h) * r) * float(w)) is formed on the way. Ends with a consumer barrier.
+__device__ __forceinline__ void vs_stage_acts(const VsubParams& P, int kc, uint8_t* acts, float4* xf, float* rinv, int tid,
+                                              int warp, int lane) {
   const VsPlan& pl = P.plan;
   const bool norm = P.norm_w != nullptr;
   const int ppr = pl.kcg * 16, npiece = P.M * ppr;          // 16-byte pieces per token row
-  for (int i = tid; i < npiece; i += kVsWarps * 32) {
+  const int rot = (int)(((long long)blockIdx.x * (npiece / 8)) / gridDim.x) * 8;
+  for (int i0 = tid; i0 < npiece; i0 += kVsWarps * 32) {
+    const int i = i0 + rot < npiece ? i0 + rot : i0 + rot - npiece;
     const int m = i / ppr, c = i % ppr;
-    cp_async16(acts + (size_t)m * pl.xs + c * 16, P.x_t + (size_t)m * P.K + (size_t)kc * pl.kcg * 128 + c * 8);
+    cp_async16(acts + (size_t)m * pl.xs + c * 16, P.x + (size_t)m * P.K + (size_t)kc * pl.kcg * 128 + c * 8);
   }
   cp_async_commit();
   cp_async_wait<0>();
   named_bar_sync(7, kVsWarps * 32);
-  const int ntask = P.M * pl.kcg;
-  if (norm) {
-    for (int task = warp; task < ntask; task += kVsWarps) {
-      const int m = task / pl.kcg, grp = task % pl.kcg;
-      const uint2 v = *(reinterpret_cast<const uint2*>(acts + (size_t)m * pl.xs + (size_t)grp * 256) + lane);
-      float ss = bflo(v.x) * bflo(v.x);
-      ss = fmaf(bfhi(v.x), bfhi(v.x), ss); ss = fmaf(bflo(v.y), bflo(v.y), ss); ss = fmaf(bfhi(v.y), bfhi(v.y), ss);
+  if (norm) {                                               // 1 / rms of every token (K is not split: the row is whole)
+    for (int m = warp; m < P.M; m += kVsWarps) {
+      float ss = 0.f;
+      for (int c = lane; c < ppr; c += 32) {
+        const uint4 v = *reinterpret_cast<const uint4*>(acts + (size_t)m * pl.xs + c * 16);
+        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) { ss = fmaf(bflo(p[e]), bflo(p[e]), ss); ss = fmaf(bfhi(p[e]), bfhi(p[e]), ss); }
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) sq[task] = ss;
-    }
-    named_bar_sync(7, kVsWarps * 32);
-    if (tid < P.M) {                                        // 1 / rms of every token, groups added in order
-      float tot = 0.f;
-      for (int gq = 0; gq < pl.kcg; gq++) tot += sq[tid * pl.kcg + gq];
-      rinv[tid] = 1.0f / sqrtf(tot / (float)P.K + P.eps);
+      if (lane == 0) rinv[m] = 1.0f / sqrtf(ss / (float)P.K + P.eps);
     }
     named_bar_sync(7, kVsWarps * 32);
   }
-  constexpr int TB = 4;                                     // tasks a warp works on at once (independent shuffle chains)
-  for (int base = warp; base < ntask; base += kVsWarps * TB) {
-    uint32_t p01[TB], p23[TB];
-    float sx[TB];
-    uint32_t ex[TB];
+  const int qpr = (pl.kcg + 3) / 4, nquad = P.M * qpr;      // quads of groups per token row
+  const int sg = lane >> 3, sl = lane & 7;
+  for (int qi = warp; qi < nquad; qi += kVsWarps) {
+    const int m = qi / qpr, grp = (qi % qpr) * 4 + sg;
+    const bool valid = grp < pl.kcg;
+    uint8_t* cell = acts + (size_t)m * pl.xs + (size_t)(valid ? grp : 0) * 256 + sl * 32;
+    const uint4 v0 = *reinterpret_cast<const uint4*>(cell), v1 = *reinterpret_cast<const uint4*>(cell + 16);
+    uint32_t p[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};       // pairs, in storage order
+    if (norm) {
+      const float r = rinv[m];
+      const uint4* wp = reinterpret_cast<const uint4*>(P.norm_w + (size_t)(valid ? grp : 0) * 128 + sl * 16);
+      const uint4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+      const uint32_t q[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      uint32_t n[8];
 #pragma unroll
-    for (int k = 0; k < TB; k++) {
-      const int task = base + k * kVsWarps;
-      p01[k] = p23[k] = 0u; ex[k] = 0u; sx[k] = 0.f;
-      if (task >= ntask) continue;                           // warp-uniform; the reductions below run on zeros
-      const int m = task / pl.kcg, grp = task % pl.kcg;
-      const uint2 v = *(reinterpret_cast<const uint2*>(acts + (size_t)m * pl.xs + (size_t)grp * 256) + lane);
-      p01[k] = v.x; p23[k] = v.y;
-      if (norm) {
-        const float r = rinv[m];
-        const uint2 wv = __ldg(reinterpret_cast<const uint2*>(P.norm_w + (size_t)grp * 128) + lane);
-        p01[k] = (uint32_t)f2bf(bflo(v.x) * r * bflo(wv.x)) | ((uint32_t)f2bf(bfhi(v.x) * r * bfhi(wv.x)) << 16);
-        p23[k] = (uint32_t)f2bf(bflo(v.y) * r * bflo(wv.y)) | ((uint32_t)f2bf(bfhi(v.y) * r * bfhi(wv.y)) << 16);
-      }
-      ex[k] = max(max((p01[k] >> 7) & 255, (p01[k] >> 23) & 255), max((p23[k] >> 7) & 255, (p23[k] >> 23) & 255));
-      sx[k] = (bflo(p01[k]) + bfhi(p01[k])) + (bflo(p23[k]) + bfhi(p23[k]));
+      for (int e = 0; e < 8; e++)
+        n[e] = (uint32_t)f2bf(bflo(p[e]) * r * bflo(q[e])) | ((uint32_t)f2bf(bfhi(p[e]) * r * bfhi(q[e])) << 16);
+      // natural pair k = columns (2k, 2k+1) of the block goes to B-order slot 2k (k < 4) or 2(k - 4) + 1
+#pragma unroll
+      for (int e = 0; e < 4; e++) { p[2 * e] = n[e]; p[2 * e + 1] = n[e + 4]; }
     }
+    uint32_t em = 0;
+    float sx = 0.f;
 #pragma unroll
-    for (int k = 0; k < TB; k++) ex[k] = __reduce_max_sync(0xffffffffu, ex[k]);
+    for (int e = 0; e < 8; e++) {
+      em = vmaxu2(em, p[e] & 0x7F807F80u);
+      sx += bflo(p[e]) + bfhi(p[e]);
+    }
+    em = max(em & 0xFFFFu, em >> 16) >> 7;                  // largest exponent field of the lane's 16 values
+    if (!valid) { em = 0; sx = 0.f; }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int k = 0; k < TB; k++) sx[k] += __shfl_xor_sync(0xffffffffu, sx[k], o);
-    __syncwarp();                                           // natural -> B order permutes inside a block of 16: read first
-#pragma unroll
-    for (int k = 0; k < TB; k++) {
-      const int task = base + k * kVsWarps;
-      if (task >= ntask) continue;
-      const int m = task / pl.kcg, grp = task % pl.kcg;
-      uint32_t mf = 268u - ex[k];               // exponent field of m: the group's largest magnitude lands in [2^14, 2^15)
+    for (int o = 4; o > 0; o >>= 1) {                       // the group's eight lanes
+      em = max(em, __shfl_xor_sync(0xffffffffu, em, o));
+      sx += __shfl_xor_sync(0xffffffffu, sx, o);
+    }
+    if (valid) {
+      uint32_t mf = 268u - em;
       mf = mf > 253u ? 253u : (mf < 24u ? 24u : mf);
       const float mult = __uint_as_float(mf << 23), inv = __uint_as_float((254u - mf) << 23);
-      const __half2 h01 = __floats2half2_rn(bflo(p01[k]) * mult, bfhi(p01[k]) * mult);
-      const __half2 h23 = __floats2half2_rn(bflo(p23[k]) * mult, bfhi(p23[k]) * mult);
-      __half2* blk = reinterpret_cast<__half2*>(acts + (size_t)m * pl.xs + (size_t)grp * 256 + (lane >> 2) * 32);
-      if (norm) {
-        // element c = 4 * (lane % 4) + e of the block of 16 columns; the pair (c, c+1) goes to half2 slot
-        // 2 * ((c % 8) / 2) + c / 8
-        const int c = (lane & 3) * 4;
-        blk[((c % 8) / 2) * 2 + (c / 8)] = h01;
-        blk[(((c + 2) % 8) / 2) * 2 + ((c + 2) / 8)] = h23;
-      } else {
-        blk[2 * (lane & 3)] = h01;
-        blk[2 * (lane & 3) + 1] = h23;
+      uint32_t hq[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        const __half2 hh = __floats2half2_rn(bflo(p[e]) * mult, bfhi(p[e]) * mult);
+        hq[e] = *reinterpret_cast<const uint32_t*>(&hh);
       }
-      if (lane == 0) xf[m * pl.kcg + grp] = make_float4(inv * 16777216.f, inv * 1048576.f, -8.f * sx[k], sx[k]);
+      *reinterpret_cast<uint4*>(cell) = make_uint4(hq[0], hq[1], hq[2], hq[3]);
+      *reinterpret_cast<uint4*>(cell + 16) = make_uint4(hq[4], hq[5], hq[6], hq[7]);
+      if (sl == 0) xf[m * (pl.kcg + 1) + grp] = make_float4(inv * 16777216.f, inv * 1048576.f, -8.f * sx, sx);
     }
   }
   named_bar_sync(7, kVsWarps * 32);
@@ -230,16 +232,20 @@ __device__ __forceinline__ void vs_epilogue(const VsubParams& P, int row_base, i
   const int g = lane >> 2, t = lane & 3;
   if (EPI == EPI_RESID || EPI == EPI_LOGITS) {
     const float val[4] = {v.x, v.y, v.z, v.w};
+    uint16_t old[4] = {0, 0, 0, 0};
+    if (EPI == EPI_RESID) {                               // all four reads are in flight before the first write
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int r = row_base + g + (e >> 1) * 8, m = j * 8 + 2 * t + (e & 1);
+        if (r < P.rows && m < P.M) old[e] = ld_cg_u16(P.h + (size_t)m * P.out_ld + r);
+      }
+    }
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       const int r = row_base + g + (e >> 1) * 8, m = j * 8 + 2 * t + (e & 1);
       if (r < P.rows && m < P.M) {
-        if (EPI == EPI_RESID) {
-          uint16_t* hp = P.h + (size_t)m * P.out_ld + r;
-          *hp = f2bf(bf2f(*hp) + val[e] * P.resid);
-        } else {
-          P.logits[(size_t)m * P.out_ld + r] = val[e] / P.logits_scaling;
-        }
+        if (EPI == EPI_RESID) P.h[(size_t)m * P.out_ld + r] = f2bf(bf2f(old[e]) + val[e] * P.resid);
+        else P.logits[(size_t)m * P.out_ld + r] = val[e] / P.logits_scaling;
       }
     }
   } else {
@@ -261,7 +267,7 @@ __device__ __forceinline__ void vs_epilogue(const VsubParams& P, int row_base, i
           if (head < P.n_head + P.nkv) {
             const int i = within >> 1;
             const float x0 = rbf(a0), x1 = rbf(a1);
-            const float2 cs = P.rope[(size_t)m * HP + i];
+            const float2 cs = __ldg(P.rope + (size_t)m * HP + i);
             const uint16_t y0 = f2bf(x0 * cs.x - x1 * cs.y), y1 = f2bf(x1 * cs.x + x0 * cs.y);
             if (head < P.n_head) {
               P.q[(size_t)m * QD + head * HD + i] = y0;
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(kVsThreads, 1) v_gemm_sub(const VsubParams P) 
     VS_STAMP(0);
     pdl_wait();
     VS_STAMP(1);
-    vs_stage_acts(P, kc, acts, xf, reinterpret_cast<float*>(vsm + pl.sq_off), reinterpret_cast<float*>(vsm + pl.bar_off + 384), tid, warp, lane);
+    vs_stage_acts(P, kc, acts, xf, reinterpret_cast<float*>(vsm + pl.bar_off + 384), tid, warp, lane);
     VS_STAMP(2);
     if (warp < nst) {
       const int slot = warp / pl.upi, u = warp % pl.upi;
@@ -351,7 +357,7 @@ __global__ void __launch_bounds__(kVsThreads, 1) v_gemm_sub(const VsubParams P) 
 #pragma unroll
         for (int e = 0; e < 2; e++) {
           const int mc = min(j * 8 + 2 * t + e, P.M - 1);
-          fa[j][e] = smem_u32(xf) + (uint32_t)(mc * pl.kcg + u * pl.ug) * 16;
+          fa[j][e] = smem_u32(xf) + (uint32_t)(mc * (pl.kcg + 1) + u * pl.ug) * 16;
         }
       }
       bool alive = true;
@@ -367,7 +373,7 @@ __global__ void __launch_bounds__(kVsThreads, 1) v_gemm_sub(const VsubParams P) 
         if (k == 0) VS_STAMP(3);
         if (alive) {
           // Loads run one step (activations) and one block of 4 steps (weights) ahead of the MMAs that use them.
-          const int nblk = pl.ug * 2, nstep = pl.ug * 8;
+          // (the look-ahead of the last step / block reads the row's pad bytes / the bytes after the nibbles: unused)
           uint4 wc0 = lds128(wa), wc1 = lds128(wa + 512);
           uint2 bcur[NT];
 #pragma unroll
@@ -376,13 +382,12 @@ __global__ void __launch_bounds__(kVsThreads, 1) v_gemm_sub(const VsubParams P) 
             float cg[2][NT][4];
 #pragma unroll
             for (int bq = 0; bq < 2; bq++) {
-              const int blk = grp * 2 + bq;
-              const uint32_t nb = (uint32_t)min(blk + 1, nblk - 1) * 1024;       // the last block fetches itself again
+              const uint32_t nb = (uint32_t)(grp * 2 + bq + 1) * 1024;
               const uint4 wn0 = lds128(wa + nb), wn1 = lds128(wa + nb + 512);
               const uint32_t ws0[4] = {wc0.x, wc0.y, wc0.z, wc0.w}, ws1[4] = {wc1.x, wc1.y, wc1.z, wc1.w};
 #pragma unroll
               for (int s4 = 0; s4 < 4; s4++) {
-                const uint32_t xo = (uint32_t)min(blk * 4 + s4 + 1, nstep - 1) * 32;
+                const uint32_t xo = (uint32_t)(grp * 8 + bq * 4 + s4 + 1) * 32;
                 uint2 bnext[NT];
 #pragma unroll
                 for (int j = 0; j < NT; j++) bnext[j] = lds64(xa[j] + xo);
