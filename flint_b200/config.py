@@ -106,6 +106,9 @@ transformer_configs = {
     # Same model with a 32768-position KV cache (long-context decode).
     "granite-3b-class-32k": dict(block_size=32768 + 256, vocab_size=49160, n_layer=40, n_head=32, n_local_heads=8,
                                  dim=2560, intermediate_size=8192, rope_base=10000),
+    # 1B-class Llama-shaped decoder (32 query / 8 kv heads of 64, tied head): a fourth width for the kernel table.
+    "llama-1b-class": dict(block_size=8192, vocab_size=128256, n_layer=16, n_head=32, n_local_heads=8, dim=2048,
+                           intermediate_size=8192, rope_base=500000),
     # 8B-class Llama-shaped decoder, untied head (the tensor-parallel config); same shape as the
     # reference's "llama-3-8b" entry (reference: engine/model.py:74).
     "llama-8b-class": dict(block_size=8192, vocab_size=128256, n_layer=32, n_head=32, n_local_heads=8, dim=4096,

@@ -44,6 +44,10 @@ const KernelEntry kDecodeKernels[] = {
     FB_DECODE_ENTRY(4096, 2048, 7168, 128, 4),    // 8B-class over 2 GPUs
     FB_DECODE_ENTRY(4096, 1024, 3584, 128, 4),    // 8B-class over 4 GPUs
     FB_DECODE_ENTRY(4096, 512, 1792, 128, 4),     // 8B-class over 8 GPUs
+    FB_DECODE_ENTRY(2048, 2048, 8192, 64, 4),     // 1B-class (32 q / 8 kv heads of 64)
+#endif
+#ifdef FB_EXTRA_DECODE_ENTRIES                    // further shapes named at build time (csrc/build.py: FLINT_B200_EXTRA_SHAPES)
+    FB_EXTRA_DECODE_ENTRIES
 #endif
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
@@ -99,7 +103,10 @@ int chunks_for(const fb_ctx* c, int T) {
 }
 
 // every K the stand-alone entry points (re-layout, dequantise, GEMV) are built for
-#define FB_FOR_EACH_K(X) X(256) X(384) X(512) X(640) X(768) X(1024) X(1280) X(1408) X(1536) X(1792) X(2048) X(2560) X(3584) X(4096) X(7168) X(8192) X(14336)
+#ifndef FB_EXTRA_K
+#define FB_EXTRA_K(X)                             // widths of the build-time extra shapes that this list lacks
+#endif
+#define FB_FOR_EACH_K(X) X(256) X(384) X(512) X(640) X(768) X(1024) X(1280) X(1408) X(1536) X(1792) X(2048) X(2560) X(3584) X(4096) X(7168) X(8192) X(14336) FB_EXTRA_K(X)
 
 template <int K>
 int launch_gemv_k(bool hz, const GemvParams& p, int grid, cudaStream_t st) {
@@ -185,6 +192,15 @@ cudaError_t launch_vgemm_k(const VGemmParams& p, int sms, cudaStream_t st) {
   return launch_vgemm_r<MT, K, EPI, HD, 32>(p, sms, st);
 }
 // the shapes the decode kernel table knows: K = model width for QKV / gate-up / LM head and O, FFN width for down
+// whether the bf16 warp-level verify GEMM is instantiated for a model's widths (the other verify kernels take them at
+// run time)
+bool vgemm_known(int D, int QD, int FF, int HD) {
+  const bool qkv = (D == 512 && HD == 64) || (D == 2560 && (HD == 80 || HD == 64)) || (D == 4096 && HD == 128);
+  const bool kd = D == 512 || D == 2560 || D == 4096, kq = QD == 512 || QD == 2560 || QD == 4096;
+  const bool kf = FF == 1408 || FF == 8192 || FF == 14336 || FF == 512 || FF == 2560 || FF == 4096;
+  return qkv && kd && kq && kf;
+}
+
 template <int MT, int EPI>
 cudaError_t launch_vgemm_shape(const VGemmParams& p, int k, int hd, int sms, cudaStream_t st) {
   if constexpr (EPI == EPI_QKV) {
@@ -793,7 +809,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     FB_CUDA(c, cudaGetLastError());
     return FB_OK;
   }
-  if (c->verify_path == 2 || (c->verify_path == 0 && M > 32)) {
+  if (c->verify_path == 2 || (c->verify_path == 0 && M > 32) || (c->verify_path != 3 && !vgemm_known(D, QD, FF, HD))) {
     // ---- tcgen05 path: natural-order activations, the matrices in the TC layout ----
     const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),
                  tF = tc_matrix_bytes(D, FF, hz);

@@ -27,13 +27,19 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="granite-3b-class")
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--graph", action="store_true", help="also time the sequence replayed from a CUDA graph")
     a = ap.parse_args()
     cfg = ModelArgs.from_name(a.config)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
+
+    def say(msg):
+        if rank == 0:
+            print(f"# {msg}", flush=True)
     x = torch.zeros(cfg.dim, dtype=torch.float32, device=dev)
     n = 2 * cfg.n_layer
 
@@ -41,9 +47,11 @@ def main() -> None:
         for _ in range(n):
             dist.all_reduce(x)
 
+    say("process group up")
     for _ in range(5):
         token()
     torch.cuda.synchronize()
+    say("warm-up done")
 
     def timed(fn) -> float:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -59,21 +67,18 @@ def main() -> None:
         return float(t.item())
 
     eager_ms = timed(token)
+    say(f"eager {eager_ms:.3f} ms per token")
     graph_ms = None
-    try:
+    if a.graph:
+      try:
         g = torch.cuda.CUDAGraph()
-        s = torch.cuda.Stream(dev)
-        with torch.cuda.stream(s):
+        with torch.cuda.graph(g):
             token()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=s):
-                token()
         torch.cuda.synchronize()
         graph_ms = timed(g.replay)
-    except Exception as e:  # graph capture of NCCL needs a recent NCCL; the eager figure stands alone otherwise
+      except Exception as e:  # the eager figure stands alone where NCCL cannot be captured
         graph_ms = None
-        if rank == 0:
-            print(f"# graph capture unavailable: {type(e).__name__}", flush=True)
+        say(f"graph capture unavailable: {type(e).__name__}")
     if rank == 0:
         print(json.dumps({"what": "NCCL all-reduce x (2 x n_layer) per token, collectives only", "config": a.config, "world": world,
                           "collectives_per_token": n, "floats_per_collective": cfg.dim, "eager_ms_per_token": eager_ms,

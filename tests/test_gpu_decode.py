@@ -306,6 +306,40 @@ def test_llama8b_class_shape_two_layers_vs_oracle():
     assert agree == len(toks)
 
 
+def test_llama1b_class_shape_two_layers_decode_and_verify_vs_oracle():
+    """A fourth model width (d 2048, 32/8 heads of 64, FFN 8192) at a depth of 2 layers: decode against the oracle, then a
+    16-node tree verify (this width has no bf16 warp-level GEMM instantiation: the library routes it to the kernels that
+    take the width at run time)."""
+    from flint_b200.tree import static_tree
+    cfg = ModelArgs.from_name("llama-1b-class")
+    cfg.n_layer = 2
+    W = packing.synth_packed(cfg, 0, device="cuda")
+    P = {k: v.cpu() for k, v in W.items()}
+    orc = O.OracleModel(cfg, P, 64)
+    eng = DecodeEngine(cfg, W, max_seq=64)
+    worst, agree = 0.0, 0
+    toks = [17, 120000, 123, 4567, 9, 31000]
+    for pos, t in enumerate(toks):
+        ref = orc.decode(t, pos)
+        got = eng.decode(t, pos).cpu().numpy()
+        eng.check()
+        worst = max(worst, float(np.abs(got - ref).max()) / logit_tol(ref))
+        tok = int(eng.next_token.item())
+        agree += int(tok == O.argmax_first(ref) or ref[tok] >= ref.max() - logit_tol(ref))
+    assert worst < 1.0, worst
+    assert agree == len(toks)
+    for M in (6, 16):
+        parent, depth = static_tree(M)
+        amask = O.tree_mask(parent)
+        cand = torch.randint(0, cfg.vocab_size, (M,), generator=torch.Generator().manual_seed(M)).tolist()
+        ref_lg, _ = orc.verify(cand, len(toks), np.asarray(depth, np.int32), amask)
+        lg, _ = eng.verify(cand, len(toks), depth, torch.from_numpy(amask))
+        eng.check()
+        lg = lg.cpu().numpy()
+        rel = max(float(np.linalg.norm(lg[m] - ref_lg[m]) / np.linalg.norm(ref_lg[m])) for m in range(M))
+        assert rel < 0.02, rel
+
+
 def test_granite3b_class_256_greedy_steps_agree_with_oracle():
     """The agreement gate at the configuration it is stated for: all 40 layers, 128-token prompt, 256 greedy steps,
     teacher-forced on the oracle's tokens.

@@ -61,3 +61,24 @@ def test_accept_walks_and_kv_moves():
     assert tree.kv_moves(path, 100) == ([103, 106], [102, 103])
     assert tree.chain_accept([1, 2, 3], [1, 2, 4]) == 2 == O.chain_accept([1, 2, 3], [1, 2, 4])
     assert tree.chain_accept([5], []) == 0
+
+
+def test_build_time_extra_shapes_become_kernel_table_macros():
+    """A model shape the built-in kernel table lacks is added by an environment variable at build time: the macros name
+    one decode entry per shape and only the widths the re-layout kernels do not have yet."""
+    from flint_b200.csrc.build import BUILT_IN_K, extra_shape_flags
+    assert extra_shape_flags("") == []
+    flags = extra_shape_flags("4096,4096,11008,128,1; 3072,3072,8192,128,3")
+    assert flags[0] == "-DFB_EXTRA_DECODE_ENTRIES=FB_DECODE_ENTRY(4096,4096,11008,128,1),FB_DECODE_ENTRY(3072,3072,8192,128,3),"
+    assert flags[1] == "-DFB_EXTRA_K(X)=X(3072) X(11008)"
+    # the Python list mirrors the C++ one
+    import os, re
+    src = open(os.path.join(os.path.dirname(__file__), "..", "flint_b200", "csrc", "fb_api.cu")).read()
+    line = [l for l in src.splitlines() if l.startswith("#define FB_FOR_EACH_K(X)")][0]
+    assert tuple(int(v) for v in re.findall(r"X\((\d+)\)", line)) == BUILT_IN_K
+    assert extra_shape_flags("2560,2560,8192,80,4") == ["-DFB_EXTRA_DECODE_ENTRIES=FB_DECODE_ENTRY(2560,2560,8192,80,4),"]
+    import pytest
+    with pytest.raises(ValueError):
+        extra_shape_flags("4096,4096,11000,128,1")
+    with pytest.raises(ValueError):
+        extra_shape_flags("4096,4096,11008,128")
