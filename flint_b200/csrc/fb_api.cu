@@ -21,23 +21,30 @@ namespace {
 struct KernelEntry {
   int dim, ko, ffn, head_dim, rgqa, hz;
   const void* fn2;
+  const void* fn_long;     // the variant whose attention reads K/V through the weight ring (long caches), or NULL
 };
 
 // KD: model width, KO: attention output width of this rank, KF: FFN width of this rank
-#define FB_DECODE_ENTRY(KD, KO, KF, HD, R)                                     \
-  {KD, KO, KF, HD, R, 0, (const void*)decode_mega2<KD, KO, KF, HD, R, false>},  \
-  {KD, KO, KF, HD, R, 1, (const void*)decode_mega2<KD, KO, KF, HD, R, true>}
+#define FB_DECODE_ENTRY(KD, KO, KF, HD, R)                                              \
+  {KD, KO, KF, HD, R, 0, (const void*)decode_mega2<KD, KO, KF, HD, R, false>, nullptr},  \
+  {KD, KO, KF, HD, R, 1, (const void*)decode_mega2<KD, KO, KF, HD, R, true>, nullptr}
+// ... with the long-cache variant as well
+#define FB_DECODE_ENTRY_LONG(KD, KO, KF, HD, R)                                                            \
+  {KD, KO, KF, HD, R, 0, (const void*)decode_mega2<KD, KO, KF, HD, R, false>,                               \
+   (const void*)decode_mega2<KD, KO, KF, HD, R, false, true>},                                             \
+  {KD, KO, KF, HD, R, 1, (const void*)decode_mega2<KD, KO, KF, HD, R, true>,                                \
+   (const void*)decode_mega2<KD, KO, KF, HD, R, true, true>}
 
 const KernelEntry kDecodeKernels[] = {
-    FB_DECODE_ENTRY(512, 512, 1408, 64, 4),       // tiny test decoder
+    FB_DECODE_ENTRY_LONG(512, 512, 1408, 64, 4),  // tiny test decoder
     FB_DECODE_ENTRY(512, 512, 1536, 64, 4),       // tiny decoder whose FFN splits into whole groups over 2 ranks
     FB_DECODE_ENTRY(512, 256, 768, 64, 4),        // ... and its 2-rank slice
     FB_DECODE_ENTRY(640, 640, 1024, 80, 4),       // small decoder with heads of 80 ...
     FB_DECODE_ENTRY(640, 384, 512, 80, 4),        // ... whose 2-rank slice reads a widened O window (320 columns in 3 groups)
-    FB_DECODE_ENTRY(2560, 2560, 8192, 80, 4),     // 3B-class (32 q / 8 kv heads of 80)
+    FB_DECODE_ENTRY_LONG(2560, 2560, 8192, 80, 4),   // 3B-class (32 q / 8 kv heads of 80)
 #ifndef FB_KERNELS_MINIMAL                        // (a build for kernel experiments keeps only the shapes above)
     FB_DECODE_ENTRY(2560, 2560, 8192, 64, 5),     // the reference's native Granite shape (40 q / 8 kv heads of 64)
-    FB_DECODE_ENTRY(4096, 4096, 14336, 128, 4),   // 8B-class
+    FB_DECODE_ENTRY_LONG(4096, 4096, 14336, 128, 4),   // 8B-class
     FB_DECODE_ENTRY(2560, 1280, 4096, 80, 4),     // 3B-class over 2 GPUs
     FB_DECODE_ENTRY(2560, 640, 2048, 80, 4),      // 3B-class over 4 GPUs
     FB_DECODE_ENTRY(2560, 384, 1024, 80, 4),      // 3B-class over 8 GPUs (320 attention columns inside 3 whole groups)
@@ -51,6 +58,7 @@ const KernelEntry kDecodeKernels[] = {
 #endif
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
+constexpr int kLongKvMin = 3072;                  // cached positions from which the long-cache variant runs (fb_set_option 8 overrides)
 
 // columns of the O projection a rank reads: its heads' columns widened to whole int4 groups (a rank of the 3B-class
 // model split 8 ways owns 320 columns = 2.5 groups: it reads 384 and feeds zeros for its neighbour's 64)
@@ -484,6 +492,8 @@ int fb_ctx_create_tp(const fb_model_desc* desc, int device, int32_t tp_rank, int
     A(cudaMemcpy(c->invf, invf, sizeof(float) * (d.head_dim / 2), cudaMemcpyHostToDevice));
     A(cudaMemset(c->status, 0, sizeof(DevStatus)));
     A(cudaFuncSetAttribute(kDecodeKernels[kid].fn2, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    if (kDecodeKernels[kid].fn_long)
+      A(cudaFuncSetAttribute(kDecodeKernels[kid].fn_long, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
   }
   if (e != cudaSuccess) {
     fb_ctx_destroy(c);
@@ -513,6 +523,7 @@ int fb_set_option(fb_ctx* c, int32_t what, int64_t value) {
   if (what == 0) { c->spin_limit = (unsigned)value; return FB_OK; }       // spin limit of every device-side wait
   if (what == 1) { c->force_chunks = (int)value; return FB_OK; }          // attention chunks per kv head (0 = auto)
   if (what == 5) { c->poll_words = value != 0; return FB_OK; }
+  if (what == 8) { if (value < 0 || value > 2) return FB_ERR_ARG; c->long_kv = (int)value; return FB_OK; }
   if (what == 7) { if (value < 0 || value > 4) return FB_ERR_ARG; c->verify_path = (int)value; return FB_OK; }
   if (what == 4) { if (value < 1 || value > kStages / 2) return FB_ERR_ARG; c->max_fly = (int)value; return FB_OK; }
   if (what == 2) { c->prof = (long long*)(uintptr_t)value; return FB_OK; } // device int64[sm_count * n_layer * 16] phase stamps (ns), 0 = off
@@ -682,10 +693,45 @@ int fb_bind_weights(fb_ctx* c, const fb_weight_ptrs* w, void* stream) {
   return FB_OK;
 }
 
+// The caches as 3-D tensors for the long-cache decode variant: [n_layer * max_seq rows][n_kv heads][HD], box = HD x 1 head x
+// one stage of positions. Returns false where the driver entry point is missing or refuses the shape: the plain variant runs.
+static bool make_kv_maps(fb_ctx* c) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+      qres != cudaDriverEntryPointSuccess)
+    return false;
+  const fb_model_desc& d = c->d;
+  const int HD = d.head_dim, R = d.n_head / d.n_kv_head;
+  int nps = 0;
+  if (HD == 64 && R == 4) nps = AttnCfg<64, 4>::NPS;
+  else if (HD == 80 && R == 4) nps = AttnCfg<80, 4>::NPS;
+  else if (HD == 128 && R == 4) nps = AttnCfg<128, 4>::NPS;
+  else return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)d.n_kv_head, (cuuint64_t)d.n_layer * (cuuint64_t)c->max_seq};
+  const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)d.n_kv_head * HD * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)HD, 1u, (cuuint32_t)nps};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  void* bases[2] = {c->kc, c->vc};
+  CUtensorMap* maps[2] = {&c->kmap, &c->vmap};
+  for (int i = 0; i < 2; i++) {
+    const CUresult r = ((EncodeFn)fn)(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, bases[i], dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+  }
+  return true;
+}
+
 int fb_bind_kv(fb_ctx* c, void* d_k, void* d_v, int32_t max_seq) {
   if (!c || !d_k || !d_v || max_seq <= 0) return FB_ERR_ARG;
   if (((uintptr_t)d_k & 15) || ((uintptr_t)d_v & 15)) return FB_ERR_ARG;
   c->kc = d_k; c->vc = d_v; c->max_seq = max_seq;
+  DeviceGuard g(c->device);
+  c->kv_maps = kDecodeKernels[c->kernel_id].fn_long != nullptr && c->tp_size == 1 && make_kv_maps(c);
   return FB_OK;
 }
 
@@ -705,6 +751,7 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
   Q.n1 = (const uint16_t*)c->n1; Q.n2 = (const uint16_t*)c->n2; Q.nf = (const uint16_t*)c->nf;
   Q.embed = (const uint16_t*)c->embed; Q.invf = c->invf;
   Q.kc = (uint16_t*)c->kc; Q.vc = (uint16_t*)c->vc;
+  if (c->kv_maps) { Q.kmap = c->kmap; Q.vmap = c->vmap; }
   Q.h_ll = c->h_ll; Q.q_ll = c->q_ll; Q.k_ll = c->k_ll; Q.v_ll = c->v_ll; Q.ao_ll = c->ao_ll; Q.act_ll = c->act_ll;
   Q.h_flags = c->flags; Q.act_flags = c->flags + 256; Q.ao_flags = c->flags + 512;
   Q.cand_ll = c->cand_ll; Q.part_ll = c->part_ll; Q.status = c->status;
@@ -724,7 +771,10 @@ int fb_decode(fb_ctx* c, int32_t token, const int32_t* d_token, void* d_h, int32
     Q.peer_inbox[p] = c->peer_inbox[p];
   }
   void* args2[] = {&Q};
-  FB_CUDA(c, cudaLaunchCooperativeKernel(kDecodeKernels[c->kernel_id].fn2, dim3(c->sm_count), dim3(kThreads), args2,
+  // long caches: the variant whose producer warp streams the K/V rows through the ring (8 x the bytes in flight)
+  const KernelEntry& ke = kDecodeKernels[c->kernel_id];
+  const bool long_kv = ke.fn_long && c->kv_maps && (c->long_kv == 1 || (c->long_kv == 0 && pos + 1 >= kLongKvMin));
+  FB_CUDA(c, cudaLaunchCooperativeKernel(long_kv ? ke.fn_long : ke.fn2, dim3(c->sm_count), dim3(kThreads), args2,
                                          (size_t)kSmemBytes, (cudaStream_t)stream));
   c->tag_base += span;
   return FB_OK;

@@ -1,5 +1,6 @@
 // The context object behind the C ABI's opaque `fb_ctx`, shared by the translation units of the library.
 #pragma once
+#include <cuda.h>
 #include <stdint.h>
 
 #include "../../include/flint_b200.h"
@@ -39,4 +40,7 @@ struct fb_ctx {
   void* vrope;                                                      // verify: (cos, sin) per (token, rotation pair)
   int verify_path;                                                  // 0: by tree size, 1: warp-level MMA GEMMs (bf16), 2: tcgen05 GEMMs, 3: tcgen05 GEMM chains, 4: warp-level MMA GEMMs on fp16 subnormals
   int max_fly, poll_words;
+  CUtensorMap kmap, vmap;                                           // the caches as tensors for the long-cache variant
+  bool kv_maps;
+  int long_kv;                                                      // 0: long-cache decode variant by cached length, 1: always (where built), 2: never
 };

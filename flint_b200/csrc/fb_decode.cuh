@@ -10,6 +10,8 @@
 // Why single buffers are enough: every phase consumes a vector that ALL CTAs contributed to, so a CTA can only be
 // one full phase ahead of the slowest one; a buffer is rewritten two phases after its last reader at the earliest.
 #pragma once
+#include <cuda.h>
+
 #include "fb_pipe.cuh"
 
 #ifndef FB_ATTN_BATCH
@@ -28,7 +30,11 @@ struct AttnCfg {
   static constexpr int LPR = HD / 8;
   static constexpr int SEG = LPR <= 8 ? 8 : 16;
   static constexpr int PPW = 32 / SEG;
+  // long caches: K/V rows travel through the weight ring, NPS positions per stage (K rows, then V rows)
+  static constexpr int NPS = 2 * 64 * HD * 2 <= kStageBytes ? 64 : 32;
+  static constexpr int KV_STAGE_BYTES = 2 * NPS * HD * 2;
   static_assert(HD % 8 == 0 && LPR <= 16, "head_dim must be a multiple of 8 and <= 128");
+  static_assert(KV_STAGE_BYTES <= kStageBytes && (HD * 2) % 16 == 0, "a ring stage holds one sweep of K and V rows");
 };
 
 // ------------------------------------------------------------------------------------------------ tagged words
@@ -288,9 +294,9 @@ struct Attn2Args {
   uint32_t tag_in, tag_part, tag_out;
 };
 
-template <int HD, int R>
+template <int HD, int R, bool LONGKV = false>
 __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch, int* misc, int cw, int lane, int tid_c,
-                                            const WaitCtl& wc, int layer) {
+                                            const WaitCtl& wc, int layer, Pipe* pipe = nullptr, int* tdone = nullptr) {
   using C = AttnCfg<HD, R>;
   constexpr int HP = HD / 2;
   float* wacc = reinterpret_cast<float*>(scratch);                 // [CW][R][HD]  (dims in lane order, see below)
@@ -332,127 +338,263 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
-    float q[R][8];
+    if constexpr (LONGKV) {
+      // ---- long caches: K/V stages from the ring, tensor-core flash-decode. Warp w takes stages w, w + 14, ... whole: the
+      // R query heads are rows 0..R-1 of one 16-row MMA tile, NPS positions the N dimension of Q K^T and the K dimension of
+      // P V (probabilities as hi + lo bf16 pairs, ~2^-17), running maximum / denominator per row as in the scalar path.
+      constexpr int KSTEPS = HD / 16, NTD = HD / 8, NPS = C::NPS, NTS = NPS / 8, ROWB = HD * 2;
+      static_assert(HD % 16 == 0 && NPS % 16 == 0 && R <= 8, "MMA flash-decode geometry");
+      const int g = lane >> 2, t = lane & 3;
+      uint32_t aq[KSTEPS][4];
 #pragma unroll
-    for (int r = 0; r < R; r++)
+      for (int ks = 0; ks < KSTEPS; ks++) {
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const uint32_t u = active ? qs[r * HP + 4 * sl + e] : 0u;
-        q[r][e] = bflo(u);        // dim 4sl+e
-        q[r][4 + e] = bfhi(u);    // dim HP+4sl+e
-      }
-    float m[R], den[R], acc[R][8];
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-      m[r] = -1e30f; den[r] = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
-    }
-    constexpr int BATCH = FB_ATTN_BATCH;
-    const int stride = kConsumerWarps * C::PPW;
-    for (int tb = t0 + cw * C::PPW; tb < t1; tb += BATCH * stride) {
-      uint2 klo[BATCH], khi[BATCH], vlo[BATCH], vhi[BATCH];
-      bool valid[BATCH];
-#pragma unroll
-      for (int j = 0; j < BATCH; j++) {
-        const int t = tb + j * stride + seg;
-        valid[j] = t < t1;
-        klo[j] = khi[j] = vlo[j] = vhi[j] = make_uint2(0, 0);
-        if (valid[j] && active) {
-          if (t == a.pos) {      // this step's own k / v: from the tagged words (the cache row is for later steps)
-            const uint32_t* kp = qs + R * HP + 4 * sl;
-            const uint32_t* vp = qs + R * HP + HP;
-            klo[j] = make_uint2((kp[0] & 0xffffu) | (kp[1] << 16), (kp[2] & 0xffffu) | (kp[3] << 16));
-            khi[j] = make_uint2((kp[0] >> 16) | (kp[1] & 0xffff0000u), (kp[2] >> 16) | (kp[3] & 0xffff0000u));
-            vlo[j] = make_uint2(vp[2 * sl], vp[2 * sl + 1]);
-            vhi[j] = make_uint2(vp[HP / 2 + 2 * sl], vp[HP / 2 + 2 * sl + 1]);
-          } else {
-            const size_t off = ((size_t)t * a.nkv + kvh) * HD + 4 * sl;
-            klo[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off));
-            khi[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off + HP));
-            vlo[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off));
-            vhi[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off + HP));
+        for (int hf = 0; hf < 2; hf++) {
+          const int d = 16 * ks + 2 * t + 8 * hf;           // dims d, d + 1 of head g (pair-major words: (x[p], x[p + HP]))
+          uint32_t v = 0;
+          if (g < R) {
+            const uint32_t w0 = qs[g * HP + (d < HP ? d : d - HP)], w1 = qs[g * HP + (d + 1 < HP ? d + 1 : d + 1 - HP)];
+            v = (d < HP ? (w0 & 0xffffu) : (w0 >> 16)) | ((d + 1 < HP ? (w1 & 0xffffu) : (w1 >> 16)) << 16);
           }
+          aq[ks][2 * hf] = v;
+          aq[ks][2 * hf + 1] = 0u;                           // rows 8..15 of the tile are unused
         }
       }
-      // long chunks: ask L2 for the rows this warp will load two rounds from now (costs no registers)
-      if (sl < (HD * 2 + 63) / 64) {
+      float o[NTD][4];
+#pragma unroll
+      for (int j = 0; j < NTD; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+      float mrun = -1e30f, lrun = 0.f;
+      const int nst = t1 > t0 ? (t1 - t0 + NPS - 1) / NPS : 0;
+      for (int st = cw; st < nst; st += kConsumerWarps) {
+        const uint32_t it = pipe->it + st;
+        const int sslot = it % kStages;
+        bool ok = true;
+        if (it >= (uint32_t)kStages) {                     // the stage's previous load must be complete before its phase bit is read
+          ok = false;
+          for (unsigned i = 0; i < wc.limit; i++) {
+            if ((uint32_t)*pipe->landed > it - kStages) { ok = true; break; }
+            if ((i & 63) == 63 && *wc.s_abort) break;
+          }
+          if (!ok && *wc.s_abort == 0) report_fail(wc, W_LANDED, layer, (int)it, *pipe->landed);
+        }
+        if (ok) ok = mbar_wait(&pipe->full[sslot], (it / kStages) & 1, wc, W_FULL, layer);
+        if (!ok) break;
+        uint8_t* k_s = pipe->stages + (size_t)sslot * kStageBytes;
+        uint8_t* v_s = k_s + C::KV_STAGE_BYTES / 2;
+        const int base = t0 + st * NPS, nvalid = min(NPS, t1 - base);
+        if (a.pos >= base && a.pos < base + NPS) {           // this step's own row: from the tagged words, not the cache
+          const uint32_t* kp = qs + R * HP;
+          const uint32_t* vp = kp + HP;
+          uint16_t* krow = reinterpret_cast<uint16_t*>(k_s + (size_t)(a.pos - base) * ROWB);
+          uint32_t* vrow = reinterpret_cast<uint32_t*>(v_s + (size_t)(a.pos - base) * ROWB);
+          for (int p2 = lane; p2 < HP; p2 += 32) {
+            krow[p2] = (uint16_t)(kp[p2] & 0xffffu);
+            krow[p2 + HP] = (uint16_t)(kp[p2] >> 16);
+            vrow[p2] = vp[p2];
+          }
+        }
+        // rows past the chunk are other cache rows (or never written): their V must not meet a zero probability as NaN
+        for (int i = lane; i < (NPS - nvalid) * (ROWB / 16); i += 32)
+          *reinterpret_cast<uint4*>(v_s + (size_t)nvalid * ROWB + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
+        __syncwarp();
+        float sc[NTS][4];
+#pragma unroll
+        for (int nt = 0; nt < NTS; nt++) {
+          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ks++) {
+            const uint8_t* kr = k_s + (size_t)(nt * 8 + g) * ROWB + (16 * ks + 2 * t) * 2;
+            mma_bf16(sc[nt], aq[ks], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 16));
+          }
+        }
+        float mx = -INFINITY;                                // row g (rows 8..15 of the tile carry nothing)
+#pragma unroll
+        for (int nt = 0; nt < NTS; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const float v = (nt * 8 + 2 * t + e) < nvalid ? sc[nt][e] * a.scale : -INFINITY;
+            sc[nt][e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(mrun, mx);                   // finite: the running maximum starts at -1e30
+        const float corr = __expf(mrun - mn);
+        mrun = mn;
+        lrun *= corr;
+#pragma unroll
+        for (int j = 0; j < NTD; j++) { o[j][0] *= corr; o[j][1] *= corr; }
+#pragma unroll
+        for (int nt = 0; nt < NTS; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const float pv = __expf(sc[nt][e] - mrun);
+            sc[nt][e] = pv;
+            lrun += pv;                                      // this lane's columns; the quad is summed at the end
+          }
+#pragma unroll
+        for (int kk = 0; kk < NPS / 16; kk++) {
+          uint32_t ah[4], al[4];
+#pragma unroll
+          for (int e = 0; e < 2; e++) {                      // A rows g: positions 16kk + 2t (+1) and + 8; rows g + 8: zero
+            const float p0 = sc[2 * kk + e][0], p1 = sc[2 * kk + e][1];
+            const float h0 = rbf(p0), h1 = rbf(p1);
+            ah[2 * e] = pack_bf16(h0, h1);
+            al[2 * e] = pack_bf16(p0 - h0, p1 - h1);
+            ah[2 * e + 1] = 0u;
+            al[2 * e + 1] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < NTD; j += 2) {
+            uint32_t bv[4];
+            const int mat = lane >> 3;
+            ldmatrix_x4_trans(bv, v_s + (size_t)(kk * 16 + (mat & 1) * 8 + (lane & 7)) * ROWB + (j + (mat >> 1)) * 16);
+            mma_bf16(o[j], ah, bv[0], bv[1]);
+            mma_bf16(o[j], al, bv[0], bv[1]);
+            mma_bf16(o[j + 1], ah, bv[2], bv[3]);
+            mma_bf16(o[j + 1], al, bv[2], bv[3]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {                                     // this warp alone read the stage
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(&pipe->empty[sslot]);
+        }
+      }
+      pipe->it += (uint32_t)nst;                             // producer and consumers count alike
+      lrun += __shfl_xor_sync(0xffffffffu, lrun, 1);
+      lrun += __shfl_xor_sync(0xffffffffu, lrun, 2);
+      if (g < R) {
+        float* dst = wacc + ((size_t)cw * R + g) * HD;
+#pragma unroll
+        for (int j = 0; j < NTD; j++) { dst[j * 8 + 2 * t] = o[j][0]; dst[j * 8 + 2 * t + 1] = o[j][1]; }
+        if (t == 0) { wm[cw * R + g] = mrun; wd[cw * R + g] = lrun; }
+      }
+    } else {
+      float q[R][8];
+#pragma unroll
+      for (int r = 0; r < R; r++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const uint32_t u = active ? qs[r * HP + 4 * sl + e] : 0u;
+          q[r][e] = bflo(u);        // dim 4sl+e
+          q[r][4 + e] = bfhi(u);    // dim HP+4sl+e
+        }
+      float m[R], den[R], acc[R][8];
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        m[r] = -1e30f; den[r] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[r][e] = 0.f;
+      }
+      constexpr int BATCH = FB_ATTN_BATCH;
+      const int stride = kConsumerWarps * C::PPW;
+      for (int tb = t0 + cw * C::PPW; tb < t1; tb += BATCH * stride) {
+        uint2 klo[BATCH], khi[BATCH], vlo[BATCH], vhi[BATCH];
+        bool valid[BATCH];
 #pragma unroll
         for (int j = 0; j < BATCH; j++) {
-          const int tp = tb + (FB_ATTN_PFD * BATCH + j) * stride + seg;
-          if (tp < t1) {
-            const size_t off = ((size_t)tp * a.nkv + kvh) * HD;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.kc + off) + sl * 64));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.vc + off) + sl * 64));
+          const int t = tb + j * stride + seg;
+          valid[j] = t < t1;
+          klo[j] = khi[j] = vlo[j] = vhi[j] = make_uint2(0, 0);
+          if (valid[j] && active) {
+            if (t == a.pos) {      // this step's own k / v: from the tagged words (the cache row is for later steps)
+              const uint32_t* kp = qs + R * HP + 4 * sl;
+              const uint32_t* vp = qs + R * HP + HP;
+              klo[j] = make_uint2((kp[0] & 0xffffu) | (kp[1] << 16), (kp[2] & 0xffffu) | (kp[3] << 16));
+              khi[j] = make_uint2((kp[0] >> 16) | (kp[1] & 0xffff0000u), (kp[2] >> 16) | (kp[3] & 0xffff0000u));
+              vlo[j] = make_uint2(vp[2 * sl], vp[2 * sl + 1]);
+              vhi[j] = make_uint2(vp[HP / 2 + 2 * sl], vp[HP / 2 + 2 * sl + 1]);
+            } else {
+              const size_t off = ((size_t)t * a.nkv + kvh) * HD + 4 * sl;
+              klo[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off));
+              khi[j] = __ldcg(reinterpret_cast<const uint2*>(a.kc + off + HP));
+              vlo[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off));
+              vhi[j] = __ldcg(reinterpret_cast<const uint2*>(a.vc + off + HP));
+            }
+          }
+        }
+        // long chunks: ask L2 for the rows this warp will load two rounds from now (costs no registers)
+        if (sl < (HD * 2 + 63) / 64) {
+#pragma unroll
+          for (int j = 0; j < BATCH; j++) {
+            const int tp = tb + (FB_ATTN_PFD * BATCH + j) * stride + seg;
+            if (tp < t1) {
+              const size_t off = ((size_t)tp * a.nkv + kvh) * HD;
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.kc + off) + sl * 64));
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.vc + off) + sl * 64));
+            }
+          }
+        }
+        // scores of the whole batch first (independent chains), then ONE rescale per head and batch
+        float sc[BATCH][R];
+#pragma unroll
+        for (int j = 0; j < BATCH; j++) {
+          const float kf[8] = {bflo(klo[j].x), bfhi(klo[j].x), bflo(klo[j].y), bfhi(klo[j].y),
+                               bflo(khi[j].x), bfhi(khi[j].x), bflo(khi[j].y), bfhi(khi[j].y)};
+#pragma unroll
+          for (int r = 0; r < R; r++) {
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
+#pragma unroll
+            for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            sc[j][r] = valid[j] ? s * a.scale : -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          float mb = sc[0][r];
+#pragma unroll
+          for (int j = 1; j < BATCH; j++) mb = fmaxf(mb, sc[j][r]);
+          const float m2 = fmaxf(m[r], mb);                 // finite: m starts at -1e30
+          const float corr = __expf(m[r] - m2);
+          den[r] *= corr;
+#pragma unroll
+          for (int e = 0; e < 8; e++) acc[r][e] *= corr;
+          m[r] = m2;
+        }
+#pragma unroll
+        for (int j = 0; j < BATCH; j++) {
+          const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
+                               bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
+#pragma unroll
+          for (int r = 0; r < R; r++) {
+            const float w = __expf(sc[j][r] - m[r]);        // 0 for a position that does not exist
+            den[r] += w;
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[r][e] = fmaf(w, vf[e], acc[r][e]);
           }
         }
       }
-      // scores of the whole batch first (independent chains), then ONE rescale per head and batch
-      float sc[BATCH][R];
+      // merge the warp's segments
 #pragma unroll
-      for (int j = 0; j < BATCH; j++) {
-        const float kf[8] = {bflo(klo[j].x), bfhi(klo[j].x), bflo(klo[j].y), bfhi(klo[j].y),
-                             bflo(khi[j].x), bfhi(khi[j].x), bflo(khi[j].y), bfhi(khi[j].y)};
+      for (int off = C::SEG; off < 32; off <<= 1) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
-          float s = 0.f;
+          const float mo = __shfl_xor_sync(0xffffffffu, m[r], off);
+          const float dn = __shfl_xor_sync(0xffffffffu, den[r], off);
+          const float gm = fmaxf(m[r], mo);
+          const float wa = __expf(m[r] - gm), wb = __expf(mo - gm);
+          den[r] = den[r] * wa + dn * wb;
 #pragma unroll
-          for (int e = 0; e < 8; e++) s = fmaf(q[r][e], kf[e], s);
-#pragma unroll
-          for (int o = C::SEG / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          sc[j][r] = valid[j] ? s * a.scale : -INFINITY;
+          for (int e = 0; e < 8; e++) {
+            const float ao_ = __shfl_xor_sync(0xffffffffu, acc[r][e], off);
+            acc[r][e] = acc[r][e] * wa + ao_ * wb;
+          }
+          m[r] = gm;
         }
       }
-#pragma unroll
-      for (int r = 0; r < R; r++) {
-        float mb = sc[0][r];
-#pragma unroll
-        for (int j = 1; j < BATCH; j++) mb = fmaxf(mb, sc[j][r]);
-        const float m2 = fmaxf(m[r], mb);                 // finite: m starts at -1e30
-        const float corr = __expf(m[r] - m2);
-        den[r] *= corr;
-#pragma unroll
-        for (int e = 0; e < 8; e++) acc[r][e] *= corr;
-        m[r] = m2;
-      }
-#pragma unroll
-      for (int j = 0; j < BATCH; j++) {
-        const float vf[8] = {bflo(vlo[j].x), bfhi(vlo[j].x), bflo(vlo[j].y), bfhi(vlo[j].y),
-                             bflo(vhi[j].x), bfhi(vhi[j].x), bflo(vhi[j].y), bfhi(vhi[j].y)};
+      if (seg == 0 && active) {
 #pragma unroll
         for (int r = 0; r < R; r++) {
-          const float w = __expf(sc[j][r] - m[r]);        // 0 for a position that does not exist
-          den[r] += w;
+          float* dst = wacc + ((size_t)cw * R + r) * HD;
 #pragma unroll
-          for (int e = 0; e < 8; e++) acc[r][e] = fmaf(w, vf[e], acc[r][e]);
+          for (int e = 0; e < 4; e++) { dst[4 * sl + e] = acc[r][e]; dst[HP + 4 * sl + e] = acc[r][4 + e]; }
+          if (sl == 0) { wm[cw * R + r] = m[r]; wd[cw * R + r] = den[r]; }
         }
-      }
-    }
-    // merge the warp's segments
-#pragma unroll
-    for (int off = C::SEG; off < 32; off <<= 1) {
-#pragma unroll
-      for (int r = 0; r < R; r++) {
-        const float mo = __shfl_xor_sync(0xffffffffu, m[r], off);
-        const float dn = __shfl_xor_sync(0xffffffffu, den[r], off);
-        const float gm = fmaxf(m[r], mo);
-        const float wa = __expf(m[r] - gm), wb = __expf(mo - gm);
-        den[r] = den[r] * wa + dn * wb;
-#pragma unroll
-        for (int e = 0; e < 8; e++) {
-          const float ao_ = __shfl_xor_sync(0xffffffffu, acc[r][e], off);
-          acc[r][e] = acc[r][e] * wa + ao_ * wb;
-        }
-        m[r] = gm;
-      }
-    }
-    if (seg == 0 && active) {
-#pragma unroll
-      for (int r = 0; r < R; r++) {
-        float* dst = wacc + ((size_t)cw * R + r) * HD;
-#pragma unroll
-        for (int e = 0; e < 4; e++) { dst[4 * sl + e] = acc[r][e]; dst[HP + 4 * sl + e] = acc[r][4 + e]; }
-        if (sl == 0) { wm[cw * R + r] = m[r]; wd[cw * R + r] = den[r]; }
       }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
@@ -540,8 +682,43 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
   }
 }
 
+// Producer side of the long-cache attention: the K and V rows of this CTA's chunk(s), NPS positions per ring stage. The
+// caches are [layer * max_seq + position][kv head][HD]: one 3-D tensor copy (box HD x 1 head x NPS positions) per
+// matrix and stage brings the strided rows in one request. Rows past the chunk (the last stage) are real cache rows that
+// nobody reads; past the end of the cache the copy fills zeros. Called by the producer lane.
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+template <int HD, int R>
+__device__ __forceinline__ bool produce_kv(Pipe& p, const CUtensorMap* kmap, const CUtensorMap* vmap, int row0, int nkv, int nchunks,
+                                           int T, int b, int G, const WaitCtl& wc, int layer) {
+  using C = AttnCfg<HD, R>;
+  const int items = nkv * nchunks, chunk_len = (T + nchunks - 1) / nchunks;
+  for (int item = b; item < items; item += G) {
+    const int kvh = item / nchunks, c = item % nchunks, t0 = c * chunk_len, t1 = min(T, t0 + chunk_len);
+    for (int ts = t0; ts < t1; ts += C::NPS) {
+      const int s = (int)(p.it % kStages);
+      if (!mbar_wait(&p.empty[s], ((p.it / kStages) & 1) ^ 1, wc, W_EMPTY, layer)) return false;
+      mbar_expect_tx(&p.full[s], (uint32_t)C::KV_STAGE_BYTES);
+      uint8_t* dst = p.stages + (size_t)s * kStageBytes;
+      tma_load_3d(dst, kmap, 0, kvh, row0 + ts, &p.full[s]);
+      tma_load_3d(dst + C::KV_STAGE_BYTES / 2, vmap, 0, kvh, row0 + ts, &p.full[s]);
+      p.it++;
+      if (p.it > p.max_fly) {                         // same trailing wait as produce_rows: keeps `landed` current
+        const uint32_t j = p.it - 1 - p.max_fly;
+        if (!mbar_wait(&p.full[j % kStages], (j / kStages) & 1, wc, W_FULL, layer)) return false;
+        *p.landed = (int)(j + 1);
+      }
+    }
+  }
+  return true;
+}
+
 // ------------------------------------------------------------------------------------------------ kernel
 struct Decode2Params {
+  CUtensorMap kmap, vmap;     // long-cache variant: the K / V caches as [HD][n_kv][n_layer * max_seq] tensors (else unused)
   const uint8_t *w_qkv, *w_o, *w_gu, *w_d, *w_lm;
   const uint16_t *n1, *n2, *nf, *embed;
   const float* invf;
@@ -580,8 +757,9 @@ __host__ __device__ constexpr int small_ks(int k) {
 }
 __host__ __device__ constexpr int imax(int a, int b) { return a > b ? a : b; }
 
-template <int KDIM, int KOUT, int KFFN, int HD, int R, bool HZ>
-__global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params P) {
+// LONGKV: the attention phase reads K/V through the weight ring (produce_kv); chosen by the host for long caches.
+template <int KDIM, int KOUT, int KFFN, int HD, int R, bool HZ, bool LONGKV = false>
+__global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constant__ Decode2Params P) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem sm = carve_smem(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -614,7 +792,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
     if (lane == 0) {
       bool ok = true;
       for (int l = 0; l < L && ok; l++) {
-        ok = produce_rows(pipe, P.w_qkv + l * strQ + (size_t)q0 * recD, q1 - q0, CQ::TILE_ROWS, CQ::RT, recD, wc, l) &&
+        ok = produce_rows(pipe, P.w_qkv + l * strQ + (size_t)q0 * recD, q1 - q0, CQ::TILE_ROWS, CQ::RT, recD, wc, l);
+        if constexpr (LONGKV)
+          ok = ok && produce_kv<HD, R>(pipe, &P.kmap, &P.vmap, l * P.max_seq, P.n_kv, P.nchunks, P.pos + 1, b, G, wc, l);
+        ok = ok &&
              produce_rows(pipe, P.w_o + l * strO + (size_t)o0 * recO, o1 - o0, CO::TILE_ROWS, CO::RT, recO, wc, l) &&
              produce_rows(pipe, P.w_gu + l * strG + (size_t)g0 * recD, g1 - g0, CG::TILE_ROWS, CG::RT, recD, wc, l) &&
              produce_rows(pipe, P.w_d + l * strF + (size_t)o0 * recF, o1 - o0, CF::TILE_ROWS, CF::RT, recF, wc, l);
@@ -780,7 +961,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const Decode2Params 
         Attn2Args aa{P.q_ll, P.k_ll, P.v_ll, P.ao_ll + (P.ao_off >> 1), kcl, vcl, P.part_ll, P.ao_flags, P.n_kv, P.pos, P.nchunks,
                      P.maxchunks, P.attn_scale, tg_qkv, mk_tag(P.tag_base, l, PH_PART), tg_att};
         named_bar_sync(kBarConsumers, kConsumerThreads);        // scratch (the activations) is free: every warp left the GEMV
-        attn2_phase<HD, R>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l);
+        attn2_phase<HD, R, LONGKV>(aa, sm.scratch, sm.misc, cw, lane, tid_c, wc, l, &pipe, sm.tdone);
       }
       FB_STAMP(3);
       // ================= O projection + residual =================

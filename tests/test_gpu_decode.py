@@ -232,16 +232,19 @@ def test_granite3b_shape_two_layers_vs_oracle():
     assert agree == len(toks)
 
 
-def test_long_context_prefilled_cache_vs_oracle():
+@pytest.mark.parametrize("variant", [0, 2])
+def test_long_context_prefilled_cache_vs_oracle(variant):
     """The long-context configuration: K and V caches pre-filled for 32 768 positions with seeded N(0, 1) values (the
     same bf16 bits in the oracle and on the GPU), then decode steps whose attention is split over every CTA and merged.
-    Two layers of the 3B-class shape keep the oracle's run time at a few seconds."""
+    Two layers of the 3B-class shape keep the oracle's run time at a few seconds. Both attention variants: the default
+    at this length (K/V through the weight ring, tensor pipe) and the scalar one (option 8 = 2)."""
     cfg = _granite_shape(2)
     T0, steps = 32768, 3
     W = packing.synth_packed(cfg, 0, device="cuda")
     P = {k: v.cpu() for k, v in W.items()}
     orc = O.OracleModel(cfg, P, T0 + 16)
     eng = DecodeEngine(cfg, W, max_seq=T0 + 16)
+    eng.set_option(8, variant)
     g = torch.Generator().manual_seed(7)
     kv = torch.randn(2, cfg.n_layer, T0, cfg.n_local_heads, cfg.head_dim, generator=g).bfloat16()
     eng.kc[:, :T0].copy_(kv[0])
@@ -256,6 +259,38 @@ def test_long_context_prefilled_cache_vs_oracle():
         eng.check()
         worst = max(worst, float(np.abs(got - ref).max()) / logit_tol(ref))
         tok = int(eng.next_token.item())      # a near-tie may resolve either way: the pick must be within the logit tolerance of the best
+        agree += int(tok == O.argmax_first(ref) or ref[tok] >= ref.max() - logit_tol(ref))
+    assert worst < 1.0, worst
+    assert agree == len(toks)
+
+
+@pytest.mark.parametrize("T0", [3, 57, 64, 300, 5000])
+def test_tiny_long_cache_variant_vs_oracle(T0):
+    """The decode variant whose attention streams K/V through the weight ring as tensor copies and multiplies on the tensor
+    pipe (default from 3072 cached positions on), forced at every cached length: a chunk shorter than one stage, exactly one
+    stage, the step's own row inside a stage, many stages per CTA."""
+    cfg = ModelArgs.from_name("tiny")
+    P = packing.synth_packed(cfg, 0)
+    orc = O.OracleModel(cfg, P, T0 + 8)
+    eng = DecodeEngine(cfg, {k: v.cuda() for k, v in P.items()}, max_seq=T0 + 8)
+    eng.set_option(8, 1)
+    g = torch.Generator().manual_seed(11)
+    kv = torch.randn(2, cfg.n_layer, T0, cfg.n_local_heads, cfg.head_dim, generator=g).bfloat16()
+    eng.kc[:, :T0].copy_(kv[0])
+    eng.vc[:, :T0].copy_(kv[1])
+    eng.kc[:, T0:].fill_(float("nan"))                 # rows past the cached length must never reach the result
+    eng.vc[:, T0:].fill_(float("nan"))
+    orc.kc[:, :T0] = kv[0].view(torch.int16).numpy().view(np.uint16)
+    orc.vc[:, :T0] = kv[1].view(torch.int16).numpy().view(np.uint16)
+    worst, agree = 0.0, 0
+    toks = [17, 4000, 123, 9]
+    for i, t in enumerate(toks):
+        ref = orc.decode(t, T0 + i)
+        got = eng.decode(t, T0 + i).cpu().numpy()
+        eng.check()
+        assert np.isfinite(got).all()
+        worst = max(worst, float(np.abs(got - ref).max()) / logit_tol(ref))
+        tok = int(eng.next_token.item())
         agree += int(tok == O.argmax_first(ref) or ref[tok] >= ref.max() - logit_tol(ref))
     assert worst < 1.0, worst
     assert agree == len(toks)
