@@ -318,16 +318,18 @@ def test_granite3b_class_full_depth_vs_oracle():
     assert agree == len(toks)
 
 
-def test_llama8b_class_shape_two_layers_vs_oracle():
+@pytest.mark.parametrize("variant", [0, 1])
+def test_llama8b_class_shape_two_layers_vs_oracle(variant):
     """The 8B-class shape on ONE GPU (d 4096, 32/8 heads of 128, FFN 14336 = tiles of 2 rows, vocab 128256, untied LM
     head, RoPE base 500000) at a depth of 2 layers against the oracle: the kernel instantiation the tensor-parallel
-    configuration is built from."""
+    configuration is built from. variant 1 forces the long-cache attention (heads of 128: 32 positions per ring stage)."""
     cfg = ModelArgs.from_name("llama-8b-class")
     cfg.n_layer = 2
     W = packing.synth_packed(cfg, 0, device="cuda")
     P = {k: v.cpu() for k, v in W.items()}
     orc = O.OracleModel(cfg, P, 64)
     eng = DecodeEngine(cfg, W, max_seq=64)
+    eng.set_option(8, variant)
     worst, agree = 0.0, 0
     toks = [17, 120000, 123, 4567, 9, 31000]
     for pos, t in enumerate(toks):
