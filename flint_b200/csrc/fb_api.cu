@@ -158,22 +158,6 @@ cudaError_t launch_repack(const void* q, const void* s, const void* z, int layer
   return cudaGetLastError();
 }
 
-// launch with programmatic stream serialisation: the kernel may start while its predecessor drains (see pdl_wait)
-template <class... KArgs, class... Args>
-cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
-}
-
 template <int MT, int K, int EPI, int HD, int ROWS>
 cudaError_t launch_vgemm_r(const VGemmParams& p, int sms, cudaStream_t st) {
   static bool configured[64] = {};        // the attribute belongs to a device's copy of the function: once per device

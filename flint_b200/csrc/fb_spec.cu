@@ -53,8 +53,7 @@ cudaError_t launch_linear_tt(const DLin& p, int t0, int sms, cudaStream_t st) {
   per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
   int grid = (p.N + 7) / 8;
   if (grid > sms * per_sm) grid = sms * per_sm;
-  d_linear<TT, MODE><<<grid, 256, smem, st>>>(p, t0);
-  return cudaGetLastError();
+  return launch_pdl(d_linear<TT, MODE>, dim3(grid), dim3(256), smem, st, p, t0);
 }
 
 // all T tokens, in blocks of up to 8 (fewer tokens per block where 8 rows of inputs do not fit shared memory)
@@ -196,7 +195,7 @@ int fb_draft_forward(fb_draft* r, const void* d_feat, const void* d_emb, const i
   else { p.x1 = (const uint16_t*)r->w.embed; p.ldx1 = D; p.x1_tokens = d_tokens; }
   p.k1 = D; p.N = D; p.T = T; p.y = r->x; p.ldy = D;
   FB_DCUDA(r, launch_linear<DL_STORE>(p, sms, st));
-  d_rmsnorm<<<T, 256, 0, st>>>(r->x, D, (const uint16_t*)r->w.n1, r->h, D, D, d.rms_eps);
+  FB_DCUDA(r, launch_pdl(d_rmsnorm, dim3(T), dim3(256), 0, st, (const uint16_t*)r->x, D, (const uint16_t*)r->w.n1, r->h, D, D, d.rms_eps));
   // q, k, v
   const void* qkvw[3] = {r->w.q, r->w.k, r->w.v};
   uint16_t* qkvo[3] = {r->q, r->k, r->v};
@@ -206,16 +205,16 @@ int fb_draft_forward(fb_draft* r, const void* d_feat, const void* d_emb, const i
     p.W = (const uint16_t*)qkvw[i]; p.x0 = r->h; p.ldx0 = D; p.k0 = D; p.N = qkvn[i]; p.T = T; p.y = qkvo[i]; p.ldy = qkvn[i];
     FB_DCUDA(r, launch_linear<DL_STORE>(p, sms, st));
   }
-  d_rope_store<<<T, 128, 0, st>>>(r->q, r->k, r->v, d_positions, d_slots, r->kc, r->vc, d.n_head, d.n_kv_head, hd, d.rope_base,
-                                  d.max_roll);
-  d_attn<<<dim3(T, d.n_head), 128, (size_t)d.max_roll * 4, st>>>(r->q, d_slots, r->kc, r->vc, r->att, d.n_head, d.n_kv_head, hd,
-                                                                  d.max_roll);
+  FB_DCUDA(r, launch_pdl(d_rope_store, dim3(T), dim3(128), 0, st, r->q, (const uint16_t*)r->k, (const uint16_t*)r->v, d_positions,
+                         d_slots, r->kc, r->vc, d.n_head, d.n_kv_head, hd, d.rope_base, d.max_roll));
+  FB_DCUDA(r, launch_pdl(d_attn, dim3(T, d.n_head), dim3(128), (size_t)d.max_roll * 4, st, (const uint16_t*)r->q, d_slots,
+                         (const uint16_t*)r->kc, (const uint16_t*)r->vc, r->att, d.n_head, d.n_kv_head, hd, d.max_roll));
   // x2 = x + o(att)
   memset(&p, 0, sizeof(p));
   p.W = (const uint16_t*)r->w.o; p.x0 = r->att; p.ldx0 = D; p.k0 = D; p.N = D; p.T = T; p.y = r->x2; p.ldy = D;
   p.resid = r->x; p.ldr = D;
   FB_DCUDA(r, launch_linear<DL_RESID>(p, sms, st));
-  d_rmsnorm<<<T, 256, 0, st>>>(r->x2, D, (const uint16_t*)r->w.n2, r->h, D, D, d.rms_eps);
+  FB_DCUDA(r, launch_pdl(d_rmsnorm, dim3(T), dim3(256), 0, st, (const uint16_t*)r->x2, D, (const uint16_t*)r->w.n2, r->h, D, D, d.rms_eps));
   // act = silu(gate h) * up h
   memset(&p, 0, sizeof(p));
   p.W = (const uint16_t*)r->w.gate; p.W2 = (const uint16_t*)r->w.up; p.x0 = r->h; p.ldx0 = D; p.k0 = D; p.N = d.inter; p.T = T;
@@ -245,13 +244,15 @@ int fb_draft_head(fb_draft* r, const void* d_feat_rows, int32_t n, int32_t top_b
   cudaStream_t st = (cudaStream_t)stream;
   const int D = d.dim, F = d.fuse * d.dim;
   // the token head reads the HIGH slice (last dim elements) of the fused feature (reference: spec_mega.py:43-44)
-  d_rmsnorm<<<n, 256, 0, st>>>((const uint16_t*)d_feat_rows + (F - D), F, (const uint16_t*)r->w.nf, r->fn, D, D, d.rms_eps);
+  FB_DCUDA(r, launch_pdl(d_rmsnorm, dim3(n), dim3(256), 0, st, (const uint16_t*)d_feat_rows + (F - D), F, (const uint16_t*)r->w.nf, r->fn, D, D,
+                         d.rms_eps));
   DLin p;
   memset(&p, 0, sizeof(p));
   p.W = (const uint16_t*)r->w.embed; p.x0 = r->fn; p.ldx0 = D; p.k0 = D; p.N = d.vocab; p.T = n; p.yf = r->logits; p.ldy = d.vocab;
   p.scale = d.logits_scaling;
   FB_DCUDA(r, launch_linear<DL_LOGITS>(p, r->sm_count, st));
-  topb_rows<<<n, 1024, 0, st>>>(r->logits, (long long)d.vocab, d.vocab, top_b, d_tokens, d_scores);
+  FB_DCUDA(r, launch_pdl(topb_rows, dim3(n), dim3(1024), 0, st, (const float*)r->logits, (long long)d.vocab, d.vocab, top_b, d_tokens,
+                         d_scores));
   FB_DCUDA(r, cudaGetLastError());
   return FB_OK;
 }

@@ -119,6 +119,8 @@ __global__ void __launch_bounds__(1024) topb_rows(const float* logits, long long
   __shared__ int chosen[16];
   const int tid = threadIdx.x, row = blockIdx.x;
   const float* lg = logits + (long long)row * row_stride;
+  pdl_trigger();
+  pdl_wait();
   for (int r = 0; r < B; r++) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -233,6 +235,8 @@ __global__ void __launch_bounds__(256) d_linear(const DLin P, int t0) {
   extern __shared__ __align__(16) uint16_t d_xs[];
   const int K = P.k0 + P.k1, KV = K >> 3;
   const int tid = threadIdx.x, lane = tid & 31;
+  pdl_trigger();
+  pdl_wait();
   for (int idx = tid; idx < TT * KV; idx += 256) {
     const int t = idx / KV, c = (idx % KV) << 3, tok = t0 + t;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -301,6 +305,8 @@ __global__ void __launch_bounds__(256) d_linear(const DLin P, int t0) {
 __global__ void __launch_bounds__(256) d_rmsnorm(const uint16_t* x, int ldx, const uint16_t* w, uint16_t* y, int ldy, int D, float eps) {
   __shared__ float red[8];
   const int tid = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const uint16_t* xr = x + (size_t)blockIdx.x * ldx;
   float ss = 0.f;
   for (int i = tid; i < D; i += 256) {
@@ -325,6 +331,8 @@ __global__ void __launch_bounds__(256) d_rmsnorm(const uint16_t* x, int ldx, con
 __global__ void d_rope_store(uint16_t* q, const uint16_t* k, const uint16_t* v, const int32_t* positions, const int32_t* slots,
                              uint16_t* kc, uint16_t* vc, int nh, int nkv, int hd, float rope_base, int max_roll) {
   const int t = blockIdx.x, half = hd >> 1;
+  pdl_trigger();
+  pdl_wait();
   const float pos = (float)positions[t];
   const int slot = slots ? slots[t] : t;
   if (slot < 0 || slot >= max_roll) return;
@@ -357,6 +365,8 @@ __global__ void __launch_bounds__(128) d_attn(const uint16_t* q, const int32_t* 
   extern __shared__ float d_sc[];                  // [max_roll] scores, then [hd] is not needed: threads own dims
   __shared__ float red[4];
   const int t = blockIdx.x, head = blockIdx.y, kh = head / (nh / nkv), tid = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const int last = min(slots ? slots[t] : t, max_roll - 1);
   if (last < 0) return;
   const uint16_t* qr = q + ((size_t)t * nh + head) * hd;

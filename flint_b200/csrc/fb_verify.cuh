@@ -17,11 +17,6 @@
 
 namespace fb {
 
-// Programmatic dependent launch: every kernel of the verify chain is launched with the stream-serialisation attribute.
-// pdl_trigger() lets the next kernel's CTAs start (and prefetch what does not depend on this kernel) once every CTA of
-// this kernel has called it; pdl_wait() returns when the previous kernel has completed and its writes are visible.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __host__ __device__ __forceinline__ int k16_pos(int col) {       // where column `col` lives in B order
   const int c = col & 15;
