@@ -339,10 +339,10 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
     if constexpr (LONGKV) {
-      // ---- long caches: K/V stages from the ring, tensor-core flash-decode. Warp w takes stages w, w + 14, ... whole: the
-      // R query heads are rows 0..R-1 of one 16-row MMA tile, NPS positions the N dimension of Q K^T and the K dimension of
-      // P V (probabilities as hi + lo bf16 pairs, ~2^-17), running maximum / denominator per row as in the scalar path.
-      constexpr int KSTEPS = HD / 16, NTD = HD / 8, NPS = C::NPS, NTS = NPS / 8, ROWB = HD * 2;
+      // ---- long caches: K/V stages from the ring, tensor-core flash-decode. Warp w takes units (16 positions of a stage)
+      // w, w + 14, ...: the R query heads are rows 0..R-1 of one 16-row MMA tile, the positions the N dimension of Q K^T and
+      // the K dimension of P V (probabilities as hi + lo bf16 pairs, ~2^-17), running maximum / denominator per row as in the scalar path.
+      constexpr int KSTEPS = HD / 16, NTD = HD / 8, NPS = C::NPS, ROWB = HD * 2;
       static_assert(HD % 16 == 0 && NPS % 16 == 0 && R <= 8, "MMA flash-decode geometry");
       const int g = lane >> 2, t = lane & 3;
       uint32_t aq[KSTEPS][4];
@@ -366,8 +366,11 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
 #pragma unroll
         for (int e = 0; e < 4; e++) o[j][e] = 0.f;
       float mrun = -1e30f, lrun = 0.f;
+      // a stage is cut into units of 16 positions that different warps take: a chunk of a few stages keeps most warps busy
+      constexpr int UP = 16, SPLIT = NPS / UP;
       const int nst = t1 > t0 ? (t1 - t0 + NPS - 1) / NPS : 0;
-      for (int st = cw; st < nst; st += kConsumerWarps) {
+      for (int u = cw; u < nst * SPLIT; u += kConsumerWarps) {
+        const int st = u / SPLIT, part = u % SPLIT;
         const uint32_t it = pipe->it + st;
         const int sslot = it % kStages;
         bool ok = true;
@@ -381,65 +384,57 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
         }
         if (ok) ok = mbar_wait(&pipe->full[sslot], (it / kStages) & 1, wc, W_FULL, layer);
         if (!ok) break;
-        uint8_t* k_s = pipe->stages + (size_t)sslot * kStageBytes;
+        uint8_t* k_s = pipe->stages + (size_t)sslot * kStageBytes + (size_t)part * UP * ROWB;
         uint8_t* v_s = k_s + C::KV_STAGE_BYTES / 2;
-        const int base = t0 + st * NPS, nvalid = min(NPS, t1 - base);
-        if (a.pos >= base && a.pos < base + NPS) {           // this step's own row: from the tagged words, not the cache
-          const uint32_t* kp = qs + R * HP;
-          const uint32_t* vp = kp + HP;
-          uint16_t* krow = reinterpret_cast<uint16_t*>(k_s + (size_t)(a.pos - base) * ROWB);
-          uint32_t* vrow = reinterpret_cast<uint32_t*>(v_s + (size_t)(a.pos - base) * ROWB);
-          for (int p2 = lane; p2 < HP; p2 += 32) {
-            krow[p2] = (uint16_t)(kp[p2] & 0xffffu);
-            krow[p2 + HP] = (uint16_t)(kp[p2] >> 16);
-            vrow[p2] = vp[p2];
+        const int base = t0 + st * NPS + part * UP, nvalid = min(UP, t1 - base);
+        if (nvalid > 0) {
+          if (a.pos >= base && a.pos < base + UP) {          // this step's own row: from the tagged words, not the cache
+            const uint32_t* kp = qs + R * HP;
+            const uint32_t* vp = kp + HP;
+            uint16_t* krow = reinterpret_cast<uint16_t*>(k_s + (size_t)(a.pos - base) * ROWB);
+            uint32_t* vrow = reinterpret_cast<uint32_t*>(v_s + (size_t)(a.pos - base) * ROWB);
+            for (int p2 = lane; p2 < HP; p2 += 32) {
+              krow[p2] = (uint16_t)(kp[p2] & 0xffffu);
+              krow[p2 + HP] = (uint16_t)(kp[p2] >> 16);
+              vrow[p2] = vp[p2];
+            }
           }
-        }
-        // rows past the chunk are other cache rows (or never written): their V must not meet a zero probability as NaN
-        for (int i = lane; i < (NPS - nvalid) * (ROWB / 16); i += 32)
-          *reinterpret_cast<uint4*>(v_s + (size_t)nvalid * ROWB + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
-        __syncwarp();
-        float sc[NTS][4];
+          // rows past the chunk are other cache rows (or never written): their V must not meet a zero probability as NaN
+          for (int i = lane; i < (UP - nvalid) * (ROWB / 16); i += 32)
+            *reinterpret_cast<uint4*>(v_s + (size_t)nvalid * ROWB + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
+          __syncwarp();
+          float sc[2][4];
 #pragma unroll
-        for (int nt = 0; nt < NTS; nt++) {
-          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+          for (int nt = 0; nt < 2; nt++) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
 #pragma unroll
-          for (int ks = 0; ks < KSTEPS; ks++) {
-            const uint8_t* kr = k_s + (size_t)(nt * 8 + g) * ROWB + (16 * ks + 2 * t) * 2;
-            mma_bf16(sc[nt], aq[ks], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 16));
+            for (int ks = 0; ks < KSTEPS; ks++) {
+              const uint8_t* kr = k_s + (size_t)(nt * 8 + g) * ROWB + (16 * ks + 2 * t) * 2;
+              mma_bf16(sc[nt], aq[ks], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 16));
+            }
           }
-        }
-        float mx = -INFINITY;                                // row g (rows 8..15 of the tile carry nothing)
+          float mx = -INFINITY;                              // row g (rows 8..15 of the tile carry nothing)
 #pragma unroll
-        for (int nt = 0; nt < NTS; nt++)
+          for (int nt = 0; nt < 2; nt++)
 #pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const float v = (nt * 8 + 2 * t + e) < nvalid ? sc[nt][e] * a.scale : -INFINITY;
-            sc[nt][e] = v;
-            mx = fmaxf(mx, v);
-          }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float mn = fmaxf(mrun, mx);                   // finite: the running maximum starts at -1e30
-        const float corr = __expf(mrun - mn);
-        mrun = mn;
-        lrun *= corr;
+            for (int e = 0; e < 2; e++) {
+              const float v = (nt * 8 + 2 * t + e) < nvalid ? sc[nt][e] * a.scale : -INFINITY;
+              sc[nt][e] = v;
+              mx = fmaxf(mx, v);
+            }
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float mn = fmaxf(mrun, mx);                 // finite: the running maximum starts at -1e30
+          const float corr = __expf(mrun - mn);
+          mrun = mn;
+          lrun *= corr;
 #pragma unroll
-        for (int j = 0; j < NTD; j++) { o[j][0] *= corr; o[j][1] *= corr; }
-#pragma unroll
-        for (int nt = 0; nt < NTS; nt++)
-#pragma unroll
-          for (int e = 0; e < 2; e++) {
-            const float pv = __expf(sc[nt][e] - mrun);
-            sc[nt][e] = pv;
-            lrun += pv;                                      // this lane's columns; the quad is summed at the end
-          }
-#pragma unroll
-        for (int kk = 0; kk < NPS / 16; kk++) {
+          for (int j = 0; j < NTD; j++) { o[j][0] *= corr; o[j][1] *= corr; }
           uint32_t ah[4], al[4];
 #pragma unroll
-          for (int e = 0; e < 2; e++) {                      // A rows g: positions 16kk + 2t (+1) and + 8; rows g + 8: zero
-            const float p0 = sc[2 * kk + e][0], p1 = sc[2 * kk + e][1];
+          for (int e = 0; e < 2; e++) {                      // A rows g: positions 2t (+1) and + 8; rows g + 8: zero
+            const float p0 = __expf(sc[e][0] - mrun), p1 = __expf(sc[e][1] - mrun);
+            lrun += p0 + p1;                                 // this lane's columns; the quad is summed at the end
             const float h0 = rbf(p0), h1 = rbf(p1);
             ah[2 * e] = pack_bf16(h0, h1);
             al[2 * e] = pack_bf16(p0 - h0, p1 - h1);
@@ -450,7 +445,7 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
           for (int j = 0; j < NTD; j += 2) {
             uint32_t bv[4];
             const int mat = lane >> 3;
-            ldmatrix_x4_trans(bv, v_s + (size_t)(kk * 16 + (mat & 1) * 8 + (lane & 7)) * ROWB + (j + (mat >> 1)) * 16);
+            ldmatrix_x4_trans(bv, v_s + (size_t)((mat & 1) * 8 + (lane & 7)) * ROWB + (j + (mat >> 1)) * 16);
             mma_bf16(o[j], ah, bv[0], bv[1]);
             mma_bf16(o[j], al, bv[0], bv[1]);
             mma_bf16(o[j + 1], ah, bv[2], bv[3]);
@@ -458,9 +453,13 @@ __device__ __forceinline__ void attn2_phase(const Attn2Args& a, uint8_t* scratch
           }
         }
         __syncwarp();
-        if (lane == 0) {                                     // this warp alone read the stage
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(&pipe->empty[sslot]);
+        if (lane == 0) {                                     // the stage's last unit hands it back
+          const int old = atomicAdd(tdone + sslot, 1);
+          if (old == SPLIT - 1) {
+            tdone[sslot] = 0;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&pipe->empty[sslot]);
+          }
         }
       }
       pipe->it += (uint32_t)nst;                             // producer and consumers count alike
