@@ -149,7 +149,8 @@ def leg_long_context(cfg, eng, dev, cached=32768, steps=12):
 
 
 def leg_verify(cfg, eng, dev, cache=1024, iters=3):
-    """Tree-verify configuration: static trees of 16 / 26 / 64 nodes over a 1024-token cache; ms per verify pass."""
+    """Tree-verify configuration: static trees of 8 / 16 / 26 / 64 nodes over a 1024-token cache; ms per verify pass
+    (eager launches; one tree size per GEMM implementation the library chooses from)."""
     from flint_b200.tree import static_tree, tree_mask
     shape = (cfg.n_layer, cache + 128, cfg.n_local_heads, cfg.head_dim)
     g = torch.Generator(device=dev).manual_seed(7)
@@ -158,7 +159,7 @@ def leg_verify(cfg, eng, dev, cache=1024, iters=3):
     old = (eng.kc, eng.vc)
     eng.bind_kv(kc, vc)
     out = {"cache": cache}
-    for M in (16, 26, 64):
+    for M in (8, 16, 26, 64):
         parent, depth = static_tree(M)
         am = torch.from_numpy(tree_mask(parent)).to(dev)
         dp = torch.tensor(depth, dtype=torch.int32, device=dev)
