@@ -56,7 +56,8 @@ cudaError_t launch_linear_tt(const DLin& p, int t0, int sms, cudaStream_t st) {
   return launch_pdl(d_linear<TT, MODE>, dim3(grid), dim3(256), smem, st, p, t0);
 }
 
-// all T tokens, in blocks of up to 8 (fewer tokens per block where 8 rows of inputs do not fit shared memory)
+// all T tokens, in blocks of up to 16 where two CTAs of 16 input rows still share an SM, else up to 8 (fewer tokens per
+// block where 8 rows of inputs do not fit shared memory): the weights are read once per block
 template <int MODE>
 cudaError_t launch_linear(const DLin& p, int sms, cudaStream_t st) {
   const int K = p.k0 + p.k1;
@@ -65,7 +66,8 @@ cudaError_t launch_linear(const DLin& p, int sms, cudaStream_t st) {
   for (int t0 = 0; t0 < p.T;) {
     const int left = p.T - t0;
     cudaError_t e;
-    if (left >= 8 && cap >= 8) { e = launch_linear_tt<8, MODE>(p, t0, sms, st); t0 += 8; }
+    if (left >= 16 && K * 2 * 16 <= 100 * 1024) { e = launch_linear_tt<16, MODE>(p, t0, sms, st); t0 += 16; }
+    else if (left >= 8 && cap >= 8) { e = launch_linear_tt<8, MODE>(p, t0, sms, st); t0 += 8; }
     else if (left >= 4 && cap >= 4) { e = launch_linear_tt<4, MODE>(p, t0, sms, st); t0 += 4; }
     else if (left >= 2 && cap >= 2) { e = launch_linear_tt<2, MODE>(p, t0, sms, st); t0 += 2; }
     else { e = launch_linear_tt<1, MODE>(p, t0, sms, st); t0 += 1; }
@@ -205,7 +207,7 @@ int fb_draft_forward(fb_draft* r, const void* d_feat, const void* d_emb, const i
     p.W = (const uint16_t*)qkvw[i]; p.x0 = r->h; p.ldx0 = D; p.k0 = D; p.N = qkvn[i]; p.T = T; p.y = qkvo[i]; p.ldy = qkvn[i];
     FB_DCUDA(r, launch_linear<DL_STORE>(p, sms, st));
   }
-  FB_DCUDA(r, launch_pdl(d_rope_store, dim3(T), dim3(128), 0, st, r->q, (const uint16_t*)r->k, (const uint16_t*)r->v, d_positions,
+  FB_DCUDA(r, launch_pdl(d_rope_store, dim3(T, d.n_head + d.n_kv_head), dim3(64), 0, st, r->q, (const uint16_t*)r->k, (const uint16_t*)r->v, d_positions,
                          d_slots, r->kc, r->vc, d.n_head, d.n_kv_head, hd, d.rope_base, d.max_roll));
   FB_DCUDA(r, launch_pdl(d_attn, dim3(T, d.n_head), dim3(128), (size_t)d.max_roll * 4, st, (const uint16_t*)r->q, d_slots,
                          (const uint16_t*)r->kc, (const uint16_t*)r->vc, r->att, d.n_head, d.n_kv_head, hd, d.max_roll));

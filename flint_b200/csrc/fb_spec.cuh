@@ -260,7 +260,9 @@ __global__ void __launch_bounds__(256) d_linear(const DLin P, int t0) {
     for (int t = 0; t < TT; t++) acc[t] = acc2[t] = 0.f;
     const uint4* wr = reinterpret_cast<const uint4*>(P.W + (size_t)n * K);
     const uint4* wr2 = MODE == DL_SWIGLU ? reinterpret_cast<const uint4*>(P.W2 + (size_t)n * K) : nullptr;
-#pragma unroll 2
+    // few tokens leave registers for more loads in flight per warp: a GEMV of 2560 rows gives an SM only ~17 warps
+    constexpr int UNR = TT <= 2 ? 8 : (TT <= 4 ? 4 : 2);
+#pragma unroll UNR
     for (int c = lane; c < KV; c += 32) {
       const uint4 w = __ldg(wr + c);
       uint4 w2 = make_uint4(0, 0, 0, 0);
@@ -327,17 +329,17 @@ __global__ void __launch_bounds__(256) d_rmsnorm(const uint16_t* x, int ldx, con
 
 // Half-split rotation of q and k (bf16 cos / sin tables as the reference casts them, reference:
 // train/draft_model.py:12-22) and the cache write: token t's rotated k and its v go to cache slot slots[t].
-// grid (T), 128 threads. q is rotated in place.
+// grid (T, n_head + n_kv), 64 threads: one CTA per (token, head), a thread per rotation pair (the angle's powf / cosf /
+// sinf are the slow part: one per thread). q is rotated in place; a kv-head CTA also copies its v row.
 __global__ void d_rope_store(uint16_t* q, const uint16_t* k, const uint16_t* v, const int32_t* positions, const int32_t* slots,
                              uint16_t* kc, uint16_t* vc, int nh, int nkv, int hd, float rope_base, int max_roll) {
-  const int t = blockIdx.x, half = hd >> 1;
+  const int t = blockIdx.x, head = blockIdx.y, half = hd >> 1;
   pdl_trigger();
   pdl_wait();
   const float pos = (float)positions[t];
   const int slot = slots ? slots[t] : t;
   if (slot < 0 || slot >= max_roll) return;
-  for (int o = threadIdx.x; o < (nh + nkv) * half; o += blockDim.x) {
-    const int head = o / half, i = o % half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float inv = 1.0f / powf(rope_base, (float)(2 * i) / (float)hd);
     const float ang = pos * inv;
     const float c = rbf(cosf(ang)), s = rbf(sinf(ang));
@@ -355,7 +357,11 @@ __global__ void d_rope_store(uint16_t* q, const uint16_t* k, const uint16_t* v, 
       d[i + half] = f2bf(rbf(b * c) + rbf(a * s));
     }
   }
-  for (int o = threadIdx.x; o < nkv * hd; o += blockDim.x) vc[(size_t)slot * nkv * hd + o] = v[(size_t)t * nkv * hd + o];
+  if (head >= nh) {
+    const int kh = head - nh;
+    for (int o = threadIdx.x; o < hd; o += blockDim.x)
+      vc[((size_t)slot * nkv + kh) * hd + o] = v[((size_t)t * nkv + kh) * hd + o];
+  }
 }
 
 // Causal attention of token t over cache slots 0 .. slots[t] (the rows of a lower-triangular mask, reference:
