@@ -843,7 +843,7 @@ int fb_verify(fb_ctx* c, const int32_t* d_tokens, const void* d_h, const int32_t
     FB_CUDA(c, cudaGetLastError());
     return FB_OK;
   }
-  if (c->verify_path == 2 || (c->verify_path == 0 && M > 32) || (c->verify_path != 3 && !vgemm_known(D, QD, FF, HD))) {
+  if (c->verify_path == 2 || (c->verify_path == 0 && M > 16) || (c->verify_path != 3 && !vgemm_known(D, QD, FF, HD))) {
     // ---- tcgen05 path: natural-order activations, the matrices in the TC layout ----
     const size_t tQ = tc_matrix_bytes(QKV, D, hz), tO = tc_matrix_bytes(D, QD, hz), tG = tc_matrix_bytes(2 * FF, D, hz),
                  tF = tc_matrix_bytes(D, FF, hz);

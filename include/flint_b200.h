@@ -230,10 +230,9 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
  *   what 5: 1 = consumers poll the tagged activation words directly; 0 = they wait for the producers' arrival flags first
  *   what 8: decode variant whose attention reads K/V through the weight ring: 0 = from 256 cached positions on (default),
  *           1 = always (shapes built with it: tiny, 3B-class, 8B-class on one GPU), 2 = never
- *   what 7: GEMMs of fb_verify: 0 = chosen by tree size (default: more than 32 tokens, where the contraction is
- *           tensor-bound, run the tcgen05 kernels with accumulators in tensor memory; smaller trees, HBM- and
- *           latency-bound, run the warp-level mma.sync kernels: up to 8 tokens on fp16-subnormal operands, 9 to 32
- *           on bf16 operands), 1 = warp-level on bf16 operands, 2 = tcgen05,
+ *   what 7: GEMMs of fb_verify: 0 = chosen by tree size (default: more than 16 tokens run the tcgen05 kernels with
+ *           accumulators in tensor memory; smaller trees, latency-bound, run the warp-level mma.sync kernels: up to
+ *           8 tokens on fp16-subnormal operands, 9 to 16 on bf16 operands), 1 = warp-level on bf16 operands, 2 = tcgen05,
  *           3 = tcgen05 with four GEMMs chained per launch, 4 = warp-level on fp16-subnormal operands (the decode
  *           kernel's arithmetic; symmetric weights, up to 26 tokens, other cases fall back to 1) */
 int fb_set_option(fb_ctx* ctx, int32_t what, int64_t value);
