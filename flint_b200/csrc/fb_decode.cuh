@@ -918,7 +918,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
       stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, mk_tag(P.tag_base, l - 1, PH_DOWN), P.n1 + (size_t)l * D, D, P.eps,
                             sm, tid_c, wc, l, l == 0, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
       FB_STAMP(1);
-      consume_tiles<CQ, HZ>(pipe, q1 - q0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+      consume_tiles<CQ, HZ, true>(pipe, q1 - q0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
         // lanes 0/8/16/24 hold rows row0..row0+3: two RoPE pairs (or four v dims)
         const float c1 = __shfl_down_sync(0xffffffffu, c, 8);
         if ((lane & 15) == 0 && (lane >> 3) < nvalid) {
@@ -967,7 +967,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
       {
         stage_plain_ll<MAXP_O>(P.ao_ll, P.ao_flags, FKV, tg_att, KOUT, sm, tid_c, wc, l);
         FB_STAMP(4);
-        consume_tiles<CO, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
+        consume_tiles<CO, HZ, true>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_o, 0); });
         if (N > 1) resid_finish(tg_o, 0, l);
         else post_when_cta_done(s_done, P.h_flags + b, tg_o, lane);
@@ -976,7 +976,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
       // ================= gate/up + SwiGLU =================
       stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, tg_o, P.n2 + (size_t)l * D, D, P.eps, sm, tid_c, wc, l, false);
       FB_STAMP(6);
-      consume_tiles<CG, HZ>(pipe, g1 - g0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
+      consume_tiles<CG, HZ, true>(pipe, g1 - g0, xs_, qs_, cw, lane, wc, l, [&](int row0, float c, int nvalid) {
         // rows (g_i, u_i, g_{i+1}, u_{i+1}) -> act[i], act[i+1] -> one tagged word
         const float u = __shfl_down_sync(0xffffffffu, c, 8);
         float av = 0.f;
@@ -995,7 +995,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
       {
         stage_plain_ll<MAXP_F>(P.act_ll, P.act_flags, FG, tg_gu, FF, sm, tid_c, wc, l);
         FB_STAMP(8);
-        consume_tiles<CF, HZ>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
+        consume_tiles<CF, HZ, true>(pipe, o1 - o0, xs_, qs_, cw, lane, wc, l,
                                   [&](int row0, float c, int nvalid) { resid_epi(row0, c, nvalid, tg_dn, 1); });
         if (N > 1) resid_finish(tg_dn, 1, l);
         else post_when_cta_done(s_done, P.h_flags + b, tg_dn, lane, P.prof ? P.prof + ((size_t)b * L + l) * 16 : nullptr);
@@ -1007,7 +1007,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
     stage_norm_ll<MAXP_D>(P.h_ll, P.h_flags, FG, mk_tag(P.tag_base, L - 1, PH_DOWN), P.nf, D, P.eps, sm, tid_c, wc, L, false);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    consume_tiles<CG, HZ>(pipe, l1 - l0, xs_, qs_, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
+    consume_tiles<CG, HZ, true>(pipe, l1 - l0, xs_, qs_, cw, lane, wc, L, [&](int row0, float c, int nvalid) {
       if ((lane & 7) == 0 && (lane >> 3) < nvalid) {
         const int row = P.vocab_base + l0 + row0 + (lane >> 3);     // index in the full vocabulary
         const float y = c / P.logits_scaling;

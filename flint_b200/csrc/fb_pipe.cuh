@@ -129,7 +129,7 @@ struct QueueState {
 // the whole warp, lane r << 3 holding the total of row row0_local + r, so results leave the CTA as soon as they exist.
 // A stage goes back to the producer when its last unit finishes (shared-memory counter); for sliced tiles the warp
 // that finishes the last slice adds the partials in slice order and runs the epilogue.
-template <class C, bool HZ, class Epi>
+template <class C, bool HZ, bool ROLL = false, class Epi>
 __device__ __forceinline__ void consume_tiles(Pipe& p, int nrows, const XStage& x, const QueueState& q, int cw, int lane,
                                               const WaitCtl& wc, int layer, Epi epi, long long* dbg = nullptr) {
   constexpr int RT = C::RT, KS = C::KS, TPS = C::TPS;
@@ -159,7 +159,7 @@ __device__ __forceinline__ void consume_tiles(Pipe& p, int nrows, const XStage& 
       const uint8_t* tile = p.stages + (size_t)s * kStageBytes + (size_t)blk * TILE;
       const int nvalid_tile = min(RT, nrows - tl * RT);
       float lo, hi;
-      tile_dot<C, HZ>(tile, slice, x, lane, lo, hi);
+      tile_dot<C, HZ, ROLL>(tile, slice, x, lane, lo, hi);
       if (dbg && cw == 0 && lane == 0 && tl == 0) dbg[14] = (long long)globaltimer_ns();
       if (KS == 1) {
         if (RT <= 4) {
