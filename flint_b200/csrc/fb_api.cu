@@ -58,7 +58,7 @@ const KernelEntry kDecodeKernels[] = {
 #endif
 };
 constexpr int kNumDecodeKernels = sizeof(kDecodeKernels) / sizeof(kDecodeKernels[0]);
-constexpr int kLongKvMin = 256;                   // cached positions from which the long-cache variant runs (fb_set_option 8 overrides)
+constexpr int kLongKvMin = 1;                     // cached positions from which the long-cache variant runs (fb_set_option 8 overrides)
 
 // columns of the O projection a rank reads: its heads' columns widened to whole int4 groups (a rank of the 3B-class
 // model split 8 ways owns 320 columns = 2.5 groups: it reads 384 and feeds zeros for its neighbour's 64)

@@ -228,7 +228,7 @@ int fb_gemv_static(const void* d_q, const void* d_s, const void* d_z, int32_t ro
  *           builds (reference: kernels/megakernel_decode.cu:15-24)
  *   what 4: bulk weight copies one CTA keeps in flight at once (1..4, default 4)
  *   what 5: 1 = consumers poll the tagged activation words directly; 0 = they wait for the producers' arrival flags first
- *   what 8: decode variant whose attention reads K/V through the weight ring: 0 = from 256 cached positions on (default),
+ *   what 8: decode variant whose attention reads K/V through the weight ring: 0 = always where the shape has it (default),
  *           1 = always (shapes built with it: tiny, 3B-class, 8B-class on one GPU), 2 = never
  *   what 7: GEMMs of fb_verify: 0 = chosen by tree size (default: more than 16 tokens run the tcgen05 kernels with
  *           accumulators in tensor memory; smaller trees, latency-bound, run the warp-level mma.sync kernels: up to

@@ -267,7 +267,7 @@ def test_long_context_prefilled_cache_vs_oracle(variant):
 @pytest.mark.parametrize("T0", [3, 57, 64, 300, 5000])
 def test_tiny_long_cache_variant_vs_oracle(T0):
     """The decode variant whose attention streams K/V through the weight ring as tensor copies and multiplies on the tensor
-    pipe (default from 256 cached positions on), forced at every cached length: a chunk shorter than one stage, exactly one
+    pipe (the default on one GPU), forced at every cached length: a chunk shorter than one stage, exactly one
     stage, the step's own row inside a stage, many stages per CTA."""
     cfg = ModelArgs.from_name("tiny")
     P = packing.synth_packed(cfg, 0)
