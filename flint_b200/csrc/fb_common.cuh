@@ -402,8 +402,8 @@ __device__ __forceinline__ void tile_dot_unrolled(const uint8_t* tile, int slice
 
 // One slice (NB blocks) of one tile against the staged activations. RT <= 8: on return every lane with lane / 4 % RT == r
 // holds the slice's total of tile row r in out_lo. RT == 16: lane 4g holds row g in out_lo and row g + 8 in out_hi.
-// The block loop is ROLLED over rounds (two blocks of four MMA steps and the group's flush per iteration): the product
-// of a tile is ~2 KB of code that every block of every tile reuses, instead of NB fully unrolled blocks (~10 KB per call
+// The block loop is ROLLED over rounds (two rounds = four blocks of four MMA steps and two group flushes per iteration): the
+// product of a tile is ~4 KB of code that every block of every tile reuses, instead of NB fully unrolled blocks (~10 KB per call
 // site, executed once per tile) streaming through the instruction cache.
 template <class C, bool HZ>
 __device__ __forceinline__ void tile_dot_rolled(const uint8_t* tile, int slice, const XStage& x, int lane, float& out_lo,
@@ -481,6 +481,15 @@ __device__ __forceinline__ void tile_dot_rolled(const uint8_t* tile, int slice, 
     block(true, left > 1);
     flush(true);
     left--;
+  }
+#pragma unroll 1
+  for (; left >= 4; left -= 4) {                                 // two rounds per iteration (+1.8 % tokens/s over one)
+    block(true, true);
+    block(false, true);
+    flush(true);
+    block(true, true);
+    block(false, left > 4);
+    flush(true);
   }
 #pragma unroll 1
   for (; left >= 2; left -= 2) {
