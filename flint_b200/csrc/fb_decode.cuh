@@ -763,7 +763,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
   Smem sm = carve_smem(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, b = blockIdx.x;
+  // (cos, sin) of this step's position for every rotation pair: once per launch instead of a full-range sincosf in every
+  // QKV epilogue of every layer
+  __shared__ float2 s_rope[64];
   if (tid == 0) pipe_init(sm);
+  if (tid < HD / 2) {
+    float sn, cs;
+    sincosf((float)P.pos * __ldg(P.invf + tid), &sn, &cs);
+    s_rope[tid] = make_float2(cs, sn);
+  }
   __syncthreads();
   WaitCtl wc{P.status, sm.s_abort, P.spin_limit};
   Pipe pipe{sm.stages, sm.full, sm.empty, sm.landed, 0u, P.max_fly};
@@ -927,8 +935,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega2(const __grid_constan
           if (head < P.n_head + P.n_kv) {
             const int i = within >> 1;
             const float x0 = rbf(c), x1 = rbf(c1);
-            float sn, cs;
-            sincosf((float)P.pos * __ldg(P.invf + i), &sn, &cs);
+            const float cs = s_rope[i].x, sn = s_rope[i].y;
             const uint32_t y0 = f2bf(x0 * cs - x1 * sn), y1 = f2bf(x1 * cs + x0 * sn);
             if (head < P.n_head) {
               ll_store(P.q_ll + (size_t)head * HP + i, y0 | (y1 << 16), tg_qkv);
